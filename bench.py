@@ -1,0 +1,506 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--workload paged_decode|varlen_prefill|int8_decode|contig_decode]
+
+Default workload (the headline): paged GQA decode, B=64, 32 query / 8 KV heads,
+D=128, fp16, 16-token pages, seq_lens uniform in [512, 8192], block table a
+seeded random permutation of the pool.  One "step" is one decode call over the
+whole batch (one new token per sequence).  Under torchrun every rank owns an
+independent batch of the same shape (weak scaling, no collective on the data
+path); the timed region is bracketed by a barrier and a device synchronise and
+the reported time is the maximum over ranks.
+
+One JSON line is printed on stdout by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# DRAM bytes per launch of the split-KV decode kernel on the headline workload, from
+# the ncu capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
+# None until a capture exists for the current kernel.
+NCU_TRAFFIC_BYTES = {"paged_decode": None, "int8_decode": None, "contig_decode": None, "varlen_prefill": None}
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {k: float(d[k]) for k in FALLBACK_PEAKS if k in d}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ----------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.tmp = None
+
+    def start(self):
+        try:
+            self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.tmp.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.tmp.name)
+        except OSError:
+            pass
+        if sm:
+            sm.sort()
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------
+# workloads
+# ----------------------------------------------------------------------------
+def decode_algorithmic_bytes(tokens_attended: int, pages: int, B: int, H_Q: int, H_KV: int, D: int) -> int:
+    """K and V read once per KV head, Q read and O written once, block table and lengths."""
+    return tokens_attended * (2 * H_KV * D * 2) + 2 * (B * H_Q * D * 2) + 4 * pages + 4 * B
+
+
+class PagedDecode:
+    name = "paged_decode"
+    metric = "paged_gqa_decode_tokens_per_s"
+    unit = "tokens/s"
+    bound = "hbm"
+    dtype = "fp16"
+    B, H_Q, H_KV, D = 64, 32, 8, 128
+
+    def __init__(self, device, seed):
+        from flash_attn_v100_b200.synthetic import make_paged_tables
+        self.device = device
+        t = make_paged_tables(self.B, 512, 8192, seed)
+        self.seq_lens_h, self.block_table_h, self.n_pages = t["seq_lens"], t["block_table"], t["n_pages"]
+        self.max_blocks = t["max_num_blocks"]
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.k_cache = torch.empty(self.n_pages, self.H_KV, 16, self.D, dtype=torch.float16, device=device)
+        self.v_cache = torch.empty_like(self.k_cache)
+        chunk = 2048
+        for s in range(0, self.n_pages, chunk):
+            e = min(s + chunk, self.n_pages)
+            self.k_cache[s:e] = torch.randn(e - s, self.H_KV, 16, self.D, generator=g, device=device).half()
+            self.v_cache[s:e] = torch.randn(e - s, self.H_KV, 16, self.D, generator=g, device=device).half()
+        self.q_h = torch.randn(self.B, self.H_Q, 1, self.D, generator=torch.Generator().manual_seed(seed)).half().pin_memory()
+        self.bt_h = self.block_table_h.pin_memory()
+        self.sl_h = self.seq_lens_h.pin_memory()
+        self.q = self.q_h.to(device)
+        self.bt = self.bt_h.to(device)
+        self.sl = self.sl_h.to(device)
+        self.out_h = torch.empty(self.B, self.H_Q, 1, self.D, dtype=torch.float16).pin_memory()
+        self.units_per_step = self.B  # one new token per sequence
+        tokens = int(self.seq_lens_h.sum())
+        pages = int(((self.seq_lens_h + 15) // 16).sum())
+        self.alg_bytes = decode_algorithmic_bytes(tokens, pages, self.B, self.H_Q, self.H_KV, self.D)
+        self.alg_flops = 4 * self.H_Q * self.D * tokens
+        self.launches_per_step = 3  # plan + split-KV main + combine
+
+    def config(self):
+        return {"workload": "paged_gqa_decode B=64 H_Q=32 H_KV=8 D=128 page=16 seq_lens~U[512,8192] (BASELINE configs[1])",
+                "batch_per_gpu": self.B, "tokens_attended_per_gpu": int(self.seq_lens_h.sum()),
+                "kv_bytes_per_gpu": int(self.k_cache.numel() * 4),
+                "l2": "inputs larger than L2 (KV pool >> 126 MB), no flush", "partition": "independent batch per rank"}
+
+    def step(self, fa):
+        return fa.forward_paged_decode_gqa_fp16(self.q, self.k_cache, self.v_cache, self.bt, self.sl, self.max_blocks)
+
+    def step_e2e(self, fa):
+        # per-step inputs of a decode iteration: the new queries, the block table and the lengths;
+        # the KV pool is resident state (it lives on the device in the reference as well)
+        q = self.q_h.to(self.device, non_blocking=True)
+        bt = self.bt_h.to(self.device, non_blocking=True)
+        sl = self.sl_h.to(self.device, non_blocking=True)
+        out = fa.forward_paged_decode_gqa_fp16(q, self.k_cache, self.v_cache, bt, sl, self.max_blocks)
+        self.out_h.copy_(out, non_blocking=True)
+        return out
+
+    def e2e_bytes(self):
+        return (self.q_h.numel() * 2 + self.bt_h.numel() * 4 + self.sl_h.numel() * 4, self.out_h.numel() * 2)
+
+    def host_copy(self):
+        return dict(q=self.q_h.clone(), k_cache=self.k_cache.cpu(), v_cache=self.v_cache.cpu(),
+                    block_table=self.block_table_h, seq_lens=self.seq_lens_h)
+
+    @staticmethod
+    def cpu_reference(host, seqs):
+        from oracle import attention_oracle as orc
+        idx = torch.tensor(seqs)
+        return orc.paged_decode(host["q"][idx], host["k_cache"], host["v_cache"], host["block_table"][idx],
+                                host["seq_lens"][idx])
+
+
+class ContigDecode(PagedDecode):
+    """Continuous-batching decode over a padded contiguous cache (same sizes as the paged workload)."""
+    name = "contig_decode"
+    metric = "continuous_batching_decode_tokens_per_s"
+
+    def __init__(self, device, seed):
+        g = torch.Generator().manual_seed(seed)
+        self.device = device
+        self.B = 32
+        self.max_N = 8192
+        self.cache_lens_h = torch.randint(511, 8192, (self.B,), generator=g, dtype=torch.int32)
+        gd = torch.Generator(device=device).manual_seed(seed)
+        self.k = torch.randn(self.B, self.H_KV, self.max_N, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.v = torch.randn(self.B, self.H_KV, self.max_N, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.q = torch.randn(self.B, self.H_Q, 1, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.cl = self.cache_lens_h.to(device)
+        self.units_per_step = self.B
+        tokens = int((self.cache_lens_h + 1).sum())
+        self.alg_bytes = decode_algorithmic_bytes(tokens, 0, self.B, self.H_Q, self.H_KV, self.D)
+        self.alg_flops = 4 * self.H_Q * self.D * tokens
+        self.launches_per_step = 3
+
+    def config(self):
+        return {"workload": "continuous_batching_decode B=32 H_Q=32 H_KV=8 D=128 max_N=8192 cache_lens~U[511,8191]",
+                "l2": "inputs larger than L2, no flush"}
+
+    def step(self, fa):
+        return fa.forward_continuous_batching_fp16(self.q, self.k, self.v, self.cl, True)
+
+    step_e2e = None
+
+
+class Int8Decode:
+    name = "int8_decode"
+    metric = "int8_gqa_decode_tokens_per_s"
+    unit = "tokens/s"
+    bound = "hbm"
+    dtype = "int8 QK^T (int32 accumulate), fp16 PV"
+    B, H_Q, H_KV, D, N = 32, 32, 8, 128, 4096
+
+    def __init__(self, device, seed):
+        self.device = device
+        gd = torch.Generator(device=device).manual_seed(seed)
+        self.q = torch.randn(self.B, self.H_Q, 1, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.k = torch.randn(self.B, self.H_KV, self.N, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.v = torch.randn(self.B, self.H_KV, self.N, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.qs = (self.q.abs().amax(-1).float().squeeze(-1) / 127).contiguous()
+        self.ks = (self.k.abs().amax(-1).float() / 127).contiguous()
+        self.units_per_step = self.B
+        self.alg_bytes = (self.B * self.H_KV * self.N * self.D * 2 * 2 + self.ks.numel() * 4 +
+                          2 * self.B * self.H_Q * self.D * 2 + self.qs.numel() * 4)
+        self.alg_flops = 4 * self.H_Q * self.D * self.N * self.B
+        self.launches_per_step = 3
+
+    def config(self):
+        return {"workload": "int8_gqa_decode B=32 H_Q=32 H_KV=8 D=128 N=4096 cache_len=4095 (BASELINE configs[3])",
+                "l2": "inputs larger than L2 (K/V 537 MB), no flush"}
+
+    def step(self, fa):
+        return fa.forward_decode_int8_gqa(self.q, self.k, self.v, self.qs, self.ks, self.N - 1)
+
+    step_e2e = None
+
+
+class VarlenPrefill:
+    name = "varlen_prefill"
+    metric = "varlen_causal_gqa_prefill_tflops"
+    unit = "TFLOP/s"
+    bound = "tensor"
+    dtype = "fp16"
+    H_Q, H_KV, D = 32, 8, 128
+
+    def __init__(self, device, seed):
+        self.device = device
+        g = torch.Generator().manual_seed(seed)
+        self.lens = torch.randint(128, 4097, (16,), generator=g).tolist()
+        cu = [0]
+        for n in self.lens:
+            cu.append(cu[-1] + n)
+        self.total = cu[-1]
+        self.cu = torch.tensor(cu, dtype=torch.int32, device=device)
+        gd = torch.Generator(device=device).manual_seed(seed)
+        self.q = torch.randn(self.total, self.H_Q, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.k = torch.randn(self.total, self.H_KV, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.v = torch.randn(self.total, self.H_KV, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.alg_flops = sum(4 * self.H_Q * self.D * n * (n + 1) // 2 for n in self.lens)
+        self.alg_bytes = (self.q.numel() * 2 + self.k.numel() * 2) * 2
+        self.units_per_step = self.alg_flops / 1e12   # TFLOP per step
+        self.launches_per_step = 1
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def config(self):
+        return {"workload": "varlen_causal_gqa_prefill 16 seqs L~U[128,4096] H_Q=32 H_KV=8 D=128 (BASELINE configs[2])",
+                "total_tokens": self.total, "flops": "causal-exact 4*H_Q*D*L(L+1)/2 per sequence",
+                "l2": "256 MB buffer written between timed iterations"}
+
+    def step(self, fa):
+        return fa.forward_varlen_prefill_fp16(self.q, self.k, self.v, self.cu, max(self.lens), True)
+
+    step_e2e = None
+
+
+WORKLOADS = {w.name: w for w in (PagedDecode, ContigDecode, Int8Decode, VarlenPrefill)}
+
+
+# ----------------------------------------------------------------------------
+# timing
+# ----------------------------------------------------------------------------
+def dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def max_over_ranks(x, world, device):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(fn, steps, world, device, flush=None):
+    """Device time of `steps` calls: CUDA events on the launching (current) stream,
+    barrier + synchronise on both sides.  With `flush`, each step is timed separately
+    and an L2-sized write runs between steps outside the events."""
+    torch.cuda.synchronize()
+    barrier(world)
+    torch.cuda.synchronize()
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+    else:
+        evs = []
+        for _ in range(steps):
+            flush.fill_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(b) for a, b in evs)
+    barrier(world)
+    return max_over_ranks(ms, world, device)
+
+
+def run_b200(args):
+    rank, world, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    import flash_attn_v100 as fa
+    import flash_attn_v100_b200
+    peaks, peak_src = load_peaks()
+
+    wl = WORKLOADS[args.workload](device, seed=rank)
+    for _ in range(max(args.warmup, 3)):
+        wl.step(fa)
+    torch.cuda.synchronize()
+    flash_attn_v100_b200.check_async_errors()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    flush = getattr(wl, "flush", None)
+    ms = time_steps(lambda: wl.step(fa), args.steps, world, device, flush)
+    # keep the GPU under load long enough for a few clock samples
+    t_end = time.time() + 1.0
+    while rank == 0 and time.time() < t_end:
+        wl.step(fa)
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+
+    e2e = None
+    if wl.step_e2e is not None:
+        for _ in range(3):
+            wl.step_e2e(fa)
+        ms_e2e = time_steps(lambda: wl.step_e2e(fa), args.steps, world, device)
+        h2d, d2h = wl.e2e_bytes()
+        e2e = {"value": wl.units_per_step * world * args.steps / (ms_e2e * 1e-3), "unit": wl.unit,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps,
+               "note": "q, block_table and seq_lens copied from pinned host memory and the output read back every "
+                       "step through the Python operator API; the KV pool is resident device state"}
+    flash_attn_v100_b200.check_async_errors()
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and args.workload == "paged_decode" and not args.no_cpu_baseline:
+        host = wl.host_copy()
+        torch.set_num_threads(os.cpu_count() or 1)
+        seqs = list(range(0, wl.B, 4))  # 16 of the 64 sequences
+        PagedDecode.cpu_reference(host, seqs[:2])
+        t0 = time.perf_counter()
+        ref = PagedDecode.cpu_reference(host, seqs)
+        dt = time.perf_counter() - t0
+        got = wl.step(fa)[torch.tensor(seqs, device=device)].float().cpu()
+        err = (got - ref.float()).abs().max().item()
+        cpu_baseline = {"value": len(seqs) / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                        "sample": f"{len(seqs)} of {wl.B} sequences of the same batch (every 4th), one pass, "
+                                  f"{dt:.2f} s; PyTorch fp32 CPU restatement of the reference's SDPA decode oracle",
+                        "max_abs_err_vs_gpu": err}
+
+    if rank != 0:
+        return
+    sec = ms * 1e-3
+    ms_per_step = ms / args.steps
+    value = wl.units_per_step * world * args.steps / sec
+    if wl.bound == "hbm":
+        achieved = wl.alg_bytes / (ms_per_step * 1e-3) / 1e9
+        peak = peaks["hbm_gbs"]
+        r_unit = "GB/s"
+    else:
+        achieved = wl.alg_flops / (ms_per_step * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"]
+        r_unit = "TFLOP/s"
+    line = {
+        "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded N(0,1) fp16, random page permutation)",
+        "config": wl.config(),
+        "hbm_gbs_per_gpu": (wl.alg_bytes / (ms_per_step * 1e-3) / 1e9),
+        "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": r_unit, "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": wl.alg_bytes, "algorithmic_flops_per_launch": wl.alg_flops,
+                     "frac_of_nominal": achieved / (8000.0 if wl.bound == "hbm" else 2250.0),
+                     "duration": "CUDA-event time of one step (plan + split-KV + combine launches) on the launching stream"},
+        "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": wl.launches_per_step * args.steps,
+        "clocks": clocks, "impl": "b200",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path: its PyTorch eager fp32 oracle
+    (restated in oracle/, since the reference tree is not present on a GPU box),
+    on all host cores, over a bounded sample of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    from oracle import attention_oracle as orc
+    torch.set_num_threads(os.cpu_count() or 1)
+    B, H_Q, H_KV, D = 64, 32, 8, 128
+    sample = 8
+    w = orc.make_paged_workload(B, H_Q, H_KV, D, 512, 8192, seed=0, fill=False)
+    # materialise only the pages of the sampled sequences (keeps host memory and set-up time bounded)
+    seqs = list(range(0, B, B // sample))
+    g = torch.Generator().manual_seed(0)
+    rows, tables = [], []
+    base = 0
+    for b in seqs:
+        n = (int(w["seq_lens"][b]) + 15) // 16
+        tables.append(torch.arange(base, base + n, dtype=torch.int32))
+        base += n
+    kc = torch.randn(base, H_KV, 16, D, generator=g).half()
+    vc = torch.randn(base, H_KV, 16, D, generator=g).half()
+    bt = torch.full((len(seqs), max(t.numel() for t in tables)), -1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        bt[i, : t.numel()] = t
+    q = w["q"][seqs]
+    sl = w["seq_lens"][seqs]
+    for _ in range(max(args.warmup, 1)):
+        orc.paged_decode(q[:2], kc, vc, bt[:2], sl[:2])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.paged_decode(q, kc, vc, bt, sl)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = len(seqs) / dt
+    cores = torch.get_num_threads()
+    desc = (f"{len(seqs)} of {B} sequences (every {B // sample}th) of the paged-decode batch per step; "
+            "PyTorch fp32 CPU restatement of the reference's SDPA decode oracle (test_decode.py:9-19)")
+    line = {
+        "impl": "reference", "metric": PagedDecode.metric, "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (CPU)", "data": "synthetic",
+        "config": {"workload": "paged_gqa_decode B=64 H_Q=32 H_KV=8 D=128 page=16 seq_lens~U[512,8192] (BASELINE configs[1])",
+                   "sample": desc},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="paged_decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1 and torch.distributed.is_initialized():
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,384 @@
+// C-ABI entry points (see include/fa_b200.h): argument validation, tensor-map
+// construction, launch configuration.  No device memory is allocated here.
+#include "../../include/fa_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "decode_splitkv.cuh"
+#include "prefill.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define FA_REQUIRE(cond, ...) \
+  do {                        \
+    if (!(cond)) return fail(FA_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+  } while (0)
+
+#define FA_CUDA(call)                                                                      \
+  do {                                                                                     \
+    cudaError_t e__ = (call);                                                              \
+    if (e__ != cudaSuccess) return fail(FA_ERR_CUDA, #call " failed: %s", cudaGetErrorString(e__)); \
+  } while (0)
+
+bool supported_d(int D) { return D == 64 || D == 128 || D == 256; }
+
+// ---- per-device facts -------------------------------------------------------
+struct DeviceInfo {
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  bool ok = false;
+};
+DeviceInfo g_dev[64];
+std::mutex g_dev_mu;
+
+int device_info(DeviceInfo* out) {
+  int dev = 0;
+  FA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(FA_ERR_CUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  if (!g_dev[dev].ok) {
+    int major = 0;
+    FA_CUDA(cudaDeviceGetAttribute(&g_dev[dev].sm_count, cudaDevAttrMultiProcessorCount, dev));
+    FA_CUDA(cudaDeviceGetAttribute(&g_dev[dev].max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    FA_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10)
+      return fail(FA_ERR_UNSUPPORTED, "this library is built for sm_100a only; device %d has compute capability %d.x",
+                  dev, major);
+    g_dev[dev].ok = true;
+  }
+  *out = g_dev[dev];
+  return FA_OK;
+}
+
+// ---- tensor maps ------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int get_encode(EncodeTiledFn* fn) {
+  static std::once_flag once;
+  static cudaError_t err = cudaSuccess;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+    if (err == cudaSuccess && qres == cudaDriverEntryPointSuccess) g_encode = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  if (g_encode == nullptr) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  *fn = g_encode;
+  return FA_OK;
+}
+
+// 2-D map over a [rows, D] fp16 tensor: box = 64 columns x box_rows rows, 128-byte swizzle.
+int make_rows_map(CUtensorMap* map, const void* base, long long rows, int D, int box_rows) {
+  EncodeTiledFn enc;
+  int rc = get_encode(&enc);
+  if (rc != FA_OK) return rc;
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return FA_OK;
+}
+
+// ---- decode tuning ----------------------------------------------------------
+fa::DecodeLaunchConfig g_cfg_override = {0, 0, 0};
+
+fa::DecodeLaunchConfig pick_decode_config(int D, int slot_rows, int B, const DeviceInfo& di) {
+  fa::DecodeLaunchConfig c;
+  if (D == 256) c = {4, 2, 1};
+  else if (D == 128) c = {4, 3, 2};
+  else c = {4, 4, 2};
+  if (g_cfg_override.warps > 0) c.warps = g_cfg_override.warps;
+  if (g_cfg_override.stages > 0) c.stages = g_cfg_override.stages;
+  if (g_cfg_override.ctas_per_sm > 0) c.ctas_per_sm = g_cfg_override.ctas_per_sm;
+  if (c.warps > 8) c.warps = 8;
+  if (c.stages > 8) c.stages = 8;
+  // shrink until ctas_per_sm CTAs fit in shared memory
+  const size_t sm_total = (size_t)di.max_smem_optin + 1024;  // per-SM capacity = opt-in max + 1 KB reserve
+  while (true) {
+    const size_t need = fa::decode_smem_bytes(D, c.warps, c.stages, slot_rows, B);
+    if (need <= (size_t)di.max_smem_optin && (need + 1024) * c.ctas_per_sm <= sm_total) break;
+    if (c.ctas_per_sm > 1) --c.ctas_per_sm;
+    else if (c.stages > 2) --c.stages;
+    else if (c.warps > 1) --c.warps;
+    else break;
+  }
+  return c;
+}
+
+constexpr int kMaxDecodeCtas = 148 * 4 * 2;  // bound used to size workspaces on any sm_100 part
+
+struct DecodeCall {
+  const void *q, *k, *v;
+  void* out;
+  const int32_t* block_table;
+  const int32_t* lens;
+  const float *q_scale, *k_scale;
+  int32_t* scores_out;
+  int B, H_Q, H_KV, D, mode, fixed_len, N, bt_stride;
+  long long num_pages, rows_total, max_units;
+  bool int8;
+  void* ws;
+  size_t ws_bytes;
+  cudaStream_t stream;
+};
+
+int run_decode(const DecodeCall& c) {
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != FA_OK) return rc;
+  const int G = c.H_Q / c.H_KV;
+  const int slot_rows = G < 16 ? G : 16;
+  const size_t need_ws = fa::decode_workspace_bytes(c.B, c.H_Q, c.H_KV, c.D, kMaxDecodeCtas);
+  if (c.ws == nullptr || c.ws_bytes < need_ws)
+    return fail(FA_ERR_WORKSPACE, "decode workspace too small: need %zu bytes, got %zu", need_ws, c.ws_bytes);
+  if ((reinterpret_cast<uintptr_t>(c.ws) & 255) != 0)
+    return fail(FA_ERR_WORKSPACE, "decode workspace must be 256-byte aligned");
+  if (c.rows_total >= (1ll << 31)) return fail(FA_ERR_UNSUPPORTED, "KV cache has too many rows for one tensor map");
+
+  fa::DecodeLaunchConfig cfg = pick_decode_config(c.D, slot_rows, c.B, di);
+  fa::DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = static_cast<const __half*>(c.q);
+  p.out = static_cast<__half*>(c.out);
+  p.block_table = c.block_table;
+  p.lens = c.lens;
+  p.q_scale = c.q_scale;
+  p.k_scale = c.k_scale;
+  p.scores_out = c.scores_out;
+  uint8_t* ws = static_cast<uint8_t*>(c.ws);
+  p.status = reinterpret_cast<int32_t*>(ws + fa::kWsStatusOffset);
+  p.prefix = reinterpret_cast<int32_t*>(ws + fa::kWsPrefixOffset);
+  p.partials = reinterpret_cast<float*>(ws + fa::kWsPrefixOffset + (((size_t)(c.B + 1) * 4 + 255) & ~(size_t)255));
+  p.B = c.B; p.H_Q = c.H_Q; p.H_KV = c.H_KV; p.G = G;
+  p.n_gblk = (G + 15) / 16;
+  p.HV = c.H_KV * p.n_gblk;
+  p.mode = c.mode; p.fixed_len = c.fixed_len; p.N = c.N;
+  p.bt_stride = c.bt_stride;
+  p.num_pages = c.num_pages;
+  p.stages = cfg.stages;
+  p.slot_rows = slot_rows;
+  p.scale = 1.0f / sqrtf((float)c.D);
+  p.scale_log2 = p.scale * 1.4426950408889634f;
+  long long n_cta = (long long)di.sm_count * cfg.ctas_per_sm;
+  if (n_cta > kMaxDecodeCtas) n_cta = kMaxDecodeCtas;
+  if (c.max_units > 0 && c.max_units < n_cta) n_cta = c.max_units;
+  if (n_cta < 1) n_cta = 1;
+  p.n_cta = (int)n_cta;
+
+  CUtensorMap kmap, vmap;
+  rc = make_rows_map(&kmap, c.k, c.rows_total, c.D, 16);
+  if (rc != FA_OK) return rc;
+  rc = make_rows_map(&vmap, c.v, c.rows_total, c.D, 16);
+  if (rc != FA_OK) return rc;
+  const size_t smem = fa::decode_smem_bytes(c.D, cfg.warps, cfg.stages, slot_rows, c.B);
+  cudaError_t e = fa::launch_decode(kmap, vmap, p, c.D, c.int8, cfg.warps, smem, c.stream);
+  if (e != cudaSuccess) return fail(FA_ERR_CUDA, "decode launch failed: %s", cudaGetErrorString(e));
+  return FA_OK;
+}
+
+int check_decode_common(const void* q, const void* k, const void* v, const void* out, int B, int H_Q, int H_KV,
+                        int D) {
+  FA_REQUIRE(q && k && v && out, "null tensor pointer");
+  FA_REQUIRE(B > 0 && H_Q > 0 && H_KV > 0 && D > 0, "B, H_Q, H_KV and D must be positive");
+  FA_REQUIRE(H_Q >= H_KV, "H_Q must be >= H_KV");
+  FA_REQUIRE(H_Q % H_KV == 0, "H_Q must be divisible by H_KV");
+  FA_REQUIRE(D <= 256, "D must be <= 256");
+  if (!supported_d(D)) return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (supported: 64, 128, 256)", D);
+  FA_REQUIRE((reinterpret_cast<uintptr_t>(k) & 15) == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0,
+             "k and v must be 16-byte aligned");
+  FA_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+             "q and out must be 16-byte aligned");
+  return FA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fa_version(void) { return 100; }
+
+const char* fa_last_error(void) { return g_err; }
+
+size_t fa_decode_workspace_bytes(int B, int H_Q, int H_KV, int D) {
+  if (B <= 0 || H_Q <= 0 || H_KV <= 0 || H_Q % H_KV != 0 || !supported_d(D)) return 0;
+  return fa::decode_workspace_bytes(B, H_Q, H_KV, D, kMaxDecodeCtas);
+}
+
+int fa_decode_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  FA_REQUIRE(workspace != nullptr && workspace_bytes >= 256, "workspace missing");
+  FA_CUDA(cudaMemsetAsync(workspace, 0, 256, static_cast<cudaStream_t>(stream)));
+  return FA_OK;
+}
+
+int fa_decode_status(const void* workspace, void* stream, int* host_status_out) {
+  FA_REQUIRE(workspace != nullptr && host_status_out != nullptr, "null pointer");
+  int32_t v = 0;
+  FA_CUDA(cudaMemcpyAsync(&v, static_cast<const uint8_t*>(workspace) + fa::kWsStatusOffset, 4, cudaMemcpyDeviceToHost,
+                          static_cast<cudaStream_t>(stream)));
+  FA_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  *host_status_out = v;
+  if (v != 0) return fail(FA_ERR_DEVICE_STATUS, "decode kernel recorded device status 0x%x", v);
+  return FA_OK;
+}
+
+int fa_decode_set_tuning(int warps, int stages, int ctas_per_sm) {
+  g_cfg_override = {warps, stages, ctas_per_sm};
+  return FA_OK;
+}
+
+int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                            const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q, int H_KV, int D,
+                            int64_t num_pages, int block_table_stride, int64_t max_seq_len, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  int rc = check_decode_common(q, k_cache, v_cache, out, B, H_Q, H_KV, D);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(block_table && seq_lens, "null block_table / seq_lens");
+  FA_REQUIRE(num_pages > 0, "num_pages must be positive");
+  FA_REQUIRE(block_table_stride > 0, "block_table_stride must be positive");
+  DecodeCall c{};
+  c.q = q; c.k = k_cache; c.v = v_cache; c.out = out;
+  c.block_table = block_table; c.lens = seq_lens;
+  c.B = B; c.H_Q = H_Q; c.H_KV = H_KV; c.D = D;
+  c.mode = fa::kModePaged; c.N = 0; c.bt_stride = block_table_stride;
+  c.num_pages = num_pages;
+  c.rows_total = (long long)num_pages * H_KV * 16;
+  long long max_pages = block_table_stride;
+  if (max_seq_len > 0 && (max_seq_len + 15) / 16 < max_pages) max_pages = (max_seq_len + 15) / 16;
+  c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * max_pages;
+  c.int8 = false;
+  c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
+  return run_decode(c);
+}
+
+int fa_decode_gqa_f16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N, int D,
+                      int causal, int cache_len, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_decode_common(q, k, v, out, B, H_Q, H_KV, D);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(N > 0, "N must be positive");
+  FA_REQUIRE(cache_len >= 0, "cache_len must be non-negative");
+  FA_REQUIRE(cache_len < N, "cache_len must be less than sequence length");
+  DecodeCall c{};
+  c.q = q; c.k = k; c.v = v; c.out = out;
+  c.B = B; c.H_Q = H_Q; c.H_KV = H_KV; c.D = D;
+  c.mode = fa::kModeContigFixed; c.N = N;
+  c.fixed_len = causal ? cache_len + 1 : N;
+  c.bt_stride = 0; c.num_pages = 0;
+  c.rows_total = (long long)B * H_KV * N;
+  c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * ((c.fixed_len + 15) / 16);
+  c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
+  return run_decode(c);
+}
+
+int fa_decode_varlen_f16(const void* q, const void* k, const void* v, void* out, const int32_t* cache_lens, int B,
+                         int H_Q, int H_KV, int max_N, int D, int causal, void* workspace, size_t workspace_bytes,
+                         void* stream) {
+  (void)causal;
+  int rc = check_decode_common(q, k, v, out, B, H_Q, H_KV, D);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(cache_lens != nullptr, "null cache_lens");
+  FA_REQUIRE(max_N > 0, "max_N must be positive");
+  DecodeCall c{};
+  c.q = q; c.k = k; c.v = v; c.out = out; c.lens = cache_lens;
+  c.B = B; c.H_Q = H_Q; c.H_KV = H_KV; c.D = D;
+  c.mode = fa::kModeContigVarlen; c.N = max_N;
+  c.rows_total = (long long)B * H_KV * max_N;
+  c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * ((max_N + 15) / 16);
+  c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
+  return run_decode(c);
+}
+
+int fa_decode_int8_gqa(const void* q, const void* k, const void* v, void* out, const float* q_scale,
+                       const float* k_scale, int B, int H_Q, int H_KV, int N, int D, int cache_len,
+                       int32_t* scores_i32_out, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_decode_common(q, k, v, out, B, H_Q, H_KV, D);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(q_scale && k_scale, "null q_scale / k_scale");
+  FA_REQUIRE(N > 0, "N must be positive");
+  FA_REQUIRE(cache_len >= 0, "cache_len must be non-negative");
+  FA_REQUIRE(cache_len < N, "cache_len must be less than sequence length");
+  DecodeCall c{};
+  c.q = q; c.k = k; c.v = v; c.out = out;
+  c.q_scale = q_scale; c.k_scale = k_scale; c.scores_out = scores_i32_out;
+  c.B = B; c.H_Q = H_Q; c.H_KV = H_KV; c.D = D;
+  c.mode = fa::kModeContigFixed; c.N = N; c.fixed_len = cache_len + 1;
+  c.rows_total = (long long)B * H_KV * N;
+  c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * ((c.fixed_len + 15) / 16);
+  c.int8 = true;
+  c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
+  return run_decode(c);
+}
+
+static int run_prefill(fa::PrefillParams& p, int D, cudaStream_t stream) {
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != FA_OK) return rc;
+  p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+  cudaError_t e = fa::launch_prefill_mma(p, D, stream);
+  if (e != cudaSuccess) return fail(FA_ERR_CUDA, "prefill launch failed: %s", cudaGetErrorString(e));
+  return FA_OK;
+}
+
+int fa_prefill_dense_f16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N,
+                         int D, int causal, void* stream) {
+  int rc = check_decode_common(q, k, v, out, B, H_Q, H_KV, D);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(N > 0, "N must be positive");
+  FA_REQUIRE(B <= 65535 && H_Q <= 65535, "B and H_Q must be <= 65535");
+  fa::PrefillParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = static_cast<const __half*>(q); p.k = static_cast<const __half*>(k); p.v = static_cast<const __half*>(v);
+  p.out = static_cast<__half*>(out);
+  p.cu_seqlens = nullptr;
+  p.batch = B; p.H_Q = H_Q; p.H_KV = H_KV; p.N = N; p.max_seqlen = N; p.total = (long long)B * N;
+  p.q_batch_stride = (long long)H_Q * N * D; p.q_head_stride = (long long)N * D; p.q_tok_stride = D;
+  p.kv_batch_stride = (long long)H_KV * N * D; p.kv_head_stride = (long long)N * D; p.kv_tok_stride = D;
+  p.causal = causal ? 1 : 0;
+  return run_prefill(p, D, static_cast<cudaStream_t>(stream));
+}
+
+int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
+                          int batch, int64_t total, int H_Q, int H_KV, int D, int max_seqlen, int causal,
+                          void* stream) {
+  int rc = check_decode_common(q, k, v, out, batch, H_Q, H_KV, D);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(cu_seqlens != nullptr, "null cu_seqlens");
+  FA_REQUIRE(total > 0, "total must be positive");
+  FA_REQUIRE(max_seqlen > 0, "max_seqlen must be positive");
+  FA_REQUIRE(batch <= 65535 && H_Q <= 65535, "batch and H_Q must be <= 65535");
+  fa::PrefillParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = static_cast<const __half*>(q); p.k = static_cast<const __half*>(k); p.v = static_cast<const __half*>(v);
+  p.out = static_cast<__half*>(out);
+  p.cu_seqlens = cu_seqlens;
+  p.batch = batch; p.H_Q = H_Q; p.H_KV = H_KV; p.N = 0; p.max_seqlen = max_seqlen; p.total = total;
+  p.q_batch_stride = 0; p.q_head_stride = D; p.q_tok_stride = (long long)H_Q * D;
+  p.kv_batch_stride = 0; p.kv_head_stride = D; p.kv_tok_stride = (long long)H_KV * D;
+  p.causal = causal ? 1 : 0;
+  return run_prefill(p, D, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,609 @@
+// Split-KV GQA decode for sm_100a: paged, contiguous and INT8-QK variants of one kernel.
+//
+// Replaces the reference's one-CTA-per-query-head decode kernels
+// (flash_attn_kernel.cu:1641-1797, 2796-2939, 3391-3514 and
+// continuous_batching_kernel.cu:40-195).
+//
+// Work decomposition.  A "unit" is one 16-token page of one segment, a segment
+// being (sequence b, KV head, block of <=16 query heads sharing that KV head).
+// Units are numbered b-major, then segment, then page; the grid is persistent
+// (a fixed number of CTAs per SM) and CTA c owns the contiguous unit range
+// [c*per, (c+1)*per).  A CTA therefore reads an equal share of the KV bytes
+// whatever the length spread, and a segment is split across CTAs only at range
+// boundaries: at most two partial results per CTA.  A second small kernel
+// merges the partials of split segments by log-sum-exp.
+//
+// Data path.  Inside a CTA each warp streams its own pages (page i of a piece
+// goes to warp i mod W) through a private ring of shared-memory stages filled
+// by TMA (cp.async.bulk.tensor, 128-byte swizzle, completion on an mbarrier).
+// K and V of a page for one KV head are 16 x D fp16 = one contiguous 4 KB block
+// at D = 128.  All query heads of the group are processed together (they are
+// the M rows of the MMA) so each K/V byte is read from HBM exactly once.
+// S = Q K^T and O += P V run on mma.sync m16n8k16 (fp32 accumulate) with
+// ldmatrix from the swizzled tiles; softmax is fp32, base-2, online.
+#include "common.cuh"
+#include "decode_splitkv.cuh"
+
+#include <math.h>
+
+namespace fa {
+
+namespace {
+
+constexpr int kMaxSmemPrefix = 4096;  // B + 1 <= this: prefix sums are staged in shared memory
+
+__device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
+  if (p.mode == kModeContigFixed) return p.fixed_len;
+  int v = __ldg(p.lens + b);
+  if (p.mode == kModePaged) {
+    long long cap = (long long)p.bt_stride * 16;
+    v = v < 0 ? 0 : v;
+    return (long long)v > cap ? (int)cap : v;
+  }
+  // continuous batching: keys [0, min(cache_len + 1, max_N))
+  long long n = (long long)v + 1;
+  if (n > p.N) n = p.N;
+  return n < 0 ? 0 : (int)n;
+}
+
+// ---------------------------------------------------------------------------
+// plan: prefix[b] = number of pages of sequences 0..b-1  (one CTA)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) decode_plan_kernel(const DecodeParams p) {
+  __shared__ int warp_tot[32];
+  __shared__ int carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    carry_s = 0;
+    p.prefix[0] = 0;
+  }
+  __syncthreads();
+  for (int base = 0; base < p.B; base += 1024) {
+    const int b = base + tid;
+    int pages = 0;
+    if (b < p.B) pages = (seq_len_of(p, b) + 15) >> 4;
+    int incl = pages;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int t = warp_tot[lane];
+      int ti = t;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int u = __shfl_up_sync(0xffffffffu, ti, o);
+        if (lane >= o) ti += u;
+      }
+      warp_tot[lane] = ti - t;  // exclusive
+    }
+    __syncthreads();
+    const int carry = carry_s;
+    if (b < p.B) p.prefix[b + 1] = carry + warp_tot[warp] + incl;
+    __syncthreads();
+    if (tid == 1023) carry_s = carry + warp_tot[warp] + incl;
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// main kernel
+// ---------------------------------------------------------------------------
+template <int D, bool INT8>
+__global__ void __launch_bounds__(256)
+decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
+                      const __grid_constant__ CUtensorMap vmap, const DecodeParams p) {
+  constexpr int PAGE_BYTES = 16 * D * 2;
+  constexpr int SLAB_BYTES = 16 * 128;  // 16 rows x 64 columns of fp16
+  constexpr int NSLAB = D / 64;
+  constexpr int NT = D / 8;  // 8-column output tiles
+  constexpr int ROWLEN = D + 2;
+
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  uint8_t* smem = smem_dyn + ((1024u - (raw & 1023u)) & 1023u);
+
+  const int W = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages;
+  const int g = lane >> 2;         // fragment row (query head within the block)
+  const int cq = (lane & 3) * 2;   // fragment column pair
+
+  uint8_t* my_stages = smem + (size_t)(warp * S) * (2 * PAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)W * S * (2 * PAGE_BYTES));
+  float* mbuf = reinterpret_cast<float*>(bars + W * S);
+  int* s_prefix = reinterpret_cast<int*>(mbuf + (size_t)W * p.slot_rows * ROWLEN);
+  const bool prefix_in_smem = (p.B + 1) <= kMaxSmemPrefix;
+  const int* pre = prefix_in_smem ? s_prefix : p.prefix;
+
+  if (prefix_in_smem) {
+    for (int i = threadIdx.x; i <= p.B; i += blockDim.x) s_prefix[i] = p.prefix[i];
+  }
+  if (lane == 0) {
+    for (int s = 0; s < S; ++s) mbar_init(smem_u32(bars + warp * S + s), 1);
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&kmap);
+    tma_prefetch_desc(&vmap);
+  }
+  __syncthreads();
+
+  const long long T = (long long)p.HV * pre[p.B];
+  long long per = (T + p.n_cta - 1) / p.n_cta;
+  if (per < 1) per = 1;
+  long long u = (long long)blockIdx.x * per;
+  const long long u1 = (u + per < T) ? (u + per) : T;
+  if (u >= u1) return;
+
+  const uint64_t policy = l2_policy_evict_first();
+  const uint32_t bar0 = smem_u32(bars + warp * S);
+  const uint32_t stage0 = smem_u32(my_stages);
+  uint32_t it_issue = 0, it_cons = 0;  // running item counters of this warp (ring position / phase)
+
+  // locate the sequence that holds unit u: largest b with HV * pre[b] <= u
+  int b;
+  {
+    int lo = 0, hi = p.B;  // invariant: HV*pre[lo] <= u < HV*pre[hi]
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if ((long long)p.HV * pre[mid] <= u) lo = mid; else hi = mid;
+    }
+    b = lo;
+  }
+
+  int piece = 0;
+  while (u < u1) {
+    while ((long long)p.HV * pre[b + 1] <= u) ++b;  // also skips empty sequences
+    const int np = pre[b + 1] - pre[b];
+    const long long rel = u - (long long)p.HV * pre[b];
+    const int hv = (int)(rel / np);
+    const int p0 = (int)(rel - (long long)hv * np);
+    const long long left = u1 - u;
+    const int cnt = (np - p0) < left ? (np - p0) : (int)left;
+    const bool complete = (p0 == 0) && (cnt == np);
+    const int len = seq_len_of(p, b);
+    const int h_kv = hv / p.n_gblk;
+    const int gb0 = (hv - h_kv * p.n_gblk) * 16;
+    const int Gb = (p.G - gb0) < 16 ? (p.G - gb0) : 16;
+    const int head0 = h_kv * p.G + gb0;
+
+    // ---- this warp's share of the piece: pages p0 + warp + n*W -------------------
+    const int n_my = cnt > warp ? (cnt - warp + W - 1) / W : 0;
+
+    // Q fragments (A operand).  Rows >= Gb are zero.
+    constexpr int QREGS = INT8 ? (D / 32) : (D / 16);
+    uint32_t qa[QREGS][4];
+    float q_s0 = 1.f, q_s1 = 1.f;
+    {
+      const bool v0 = g < Gb, v1 = (g + 8) < Gb;
+      const __half* q0 = p.q + ((size_t)b * p.H_Q + head0 + g) * D;
+      const __half* q1 = q0 + (size_t)8 * D;
+      if constexpr (!INT8) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          qa[kk][0] = v0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + kk * 16 + cq)) : 0u;
+          qa[kk][1] = v1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + kk * 16 + cq)) : 0u;
+          qa[kk][2] = v0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + cq)) : 0u;
+          qa[kk][3] = v1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + cq)) : 0u;
+        }
+      } else {
+        if (v0) q_s0 = __ldg(p.q_scale + (size_t)b * p.H_Q + head0 + g);
+        if (v1) q_s1 = __ldg(p.q_scale + (size_t)b * p.H_Q + head0 + g + 8);
+        auto quant4 = [](const __half* src, float s) -> uint32_t {
+          const uint2 raw2 = __ldg(reinterpret_cast<const uint2*>(src));
+          const __half2 h01 = *reinterpret_cast<const __half2*>(&raw2.x);
+          const __half2 h23 = *reinterpret_cast<const __half2*>(&raw2.y);
+          const float f[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
+          uint32_t packed = 0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float t = fmaxf(-127.f, fminf(127.f, roundf(__fdiv_rn(f[i], s))));
+            packed |= (static_cast<uint32_t>(static_cast<int>(t)) & 0xffu) << (8 * i);
+          }
+          return packed;
+        };
+        const int c4 = (lane & 3) * 4;
+#pragma unroll
+        for (int kk = 0; kk < D / 32; ++kk) {
+          qa[kk][0] = v0 ? quant4(q0 + kk * 32 + c4, q_s0) : 0u;
+          qa[kk][1] = v1 ? quant4(q1 + kk * 32 + c4, q_s1) : 0u;
+          qa[kk][2] = v0 ? quant4(q0 + kk * 32 + 16 + c4, q_s0) : 0u;
+          qa[kk][3] = v1 ? quant4(q1 + kk * 32 + 16 + c4, q_s1) : 0u;
+        }
+      }
+    }
+
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    // Block-table entries of this warp's pages, 32 at a time, one batch ahead.
+    const int32_t* bt_row = p.block_table + (size_t)b * p.bt_stride;
+    int tbl_cur = 0, tbl_next = 0;
+    auto load_tbl = [&](int batch) -> int {
+      const int n = batch * 32 + lane;
+      if (p.mode != kModePaged || n >= n_my) return 0;
+      return __ldg(bt_row + p0 + warp + n * W);
+    };
+    tbl_cur = load_tbl(0);
+    tbl_next = load_tbl(1);
+
+    const long long contig_row0 = ((long long)b * p.H_KV + h_kv) * (long long)p.N;
+
+    auto issue = [&](int n) {
+      // every lane takes part in the shuffle; lane 0 issues the copies
+      int pid = __shfl_sync(0xffffffffu, tbl_cur, n & 31);
+      if (lane == 0) {
+        const int page = p0 + warp + n * W;
+        long long row;
+        if (p.mode == kModePaged) {
+          if (pid < 0 || (long long)pid >= p.num_pages) {
+            atomicOr(p.status, kStatusBadPageId);
+            pid = 0;
+          }
+          row = ((long long)pid * p.H_KV + h_kv) * 16;
+        } else {
+          row = contig_row0 + (long long)page * 16;
+        }
+        const uint32_t st = it_issue % (uint32_t)S;
+        const uint32_t bar = bar0 + st * 8;
+        const uint32_t dst = stage0 + st * (2 * PAGE_BYTES);
+        mbar_expect_tx(bar, 2 * PAGE_BYTES);
+#pragma unroll
+        for (int sl = 0; sl < NSLAB; ++sl) {
+          tma_load_2d(dst + sl * SLAB_BYTES, &kmap, sl * 64, (int)row, bar, policy);
+          tma_load_2d(dst + PAGE_BYTES + sl * SLAB_BYTES, &vmap, sl * 64, (int)row, bar, policy);
+        }
+      }
+      ++it_issue;
+    };
+
+    int issued = 0;
+    for (; issued < S && issued < n_my; ++issued) issue(issued);
+
+    // INT8: per-token K scales of the next page, fetched one page ahead.
+    float ks_cur = 1.f, ks_next = 1.f;
+    auto load_ks = [&](int n) -> float {
+      if (n >= n_my) return 1.f;
+      const int tok = (p0 + warp + n * W) * 16 + (lane & 15);
+      if (tok >= p.N) return 1.f;
+      return __ldg(p.k_scale + ((size_t)b * p.H_KV + h_kv) * p.N + tok);
+    };
+    if constexpr (INT8) ks_next = load_ks(0);
+
+    for (int n = 0; n < n_my; ++n) {
+      if constexpr (INT8) {
+        ks_cur = ks_next;
+        ks_next = load_ks(n + 1);
+      }
+      const uint32_t st = it_cons % (uint32_t)S;
+      const uint32_t parity = (it_cons / (uint32_t)S) & 1u;
+      ++it_cons;
+      if (!mbar_wait(bar0 + st * 8, parity)) {
+        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+      }
+      const uint32_t kbase = stage0 + st * (2 * PAGE_BYTES);
+      const uint32_t vbase = kbase + PAGE_BYTES;
+      const int page = p0 + warp + n * W;
+      const int nvalid = (len - page * 16) < 16 ? (len - page * 16) : 16;
+
+      if (nvalid < 16) {
+        // zero the V rows of tokens past the end so that 0 * garbage cannot make NaN
+        uint8_t* vptr = my_stages + (size_t)st * (2 * PAGE_BYTES) + PAGE_BYTES;
+        const int per_slab = (16 - nvalid) * 8;
+        for (int i = lane; i < per_slab * NSLAB; i += 32) {
+          const int sl = i / per_slab, r = i - sl * per_slab;
+          *reinterpret_cast<uint4*>(vptr + sl * SLAB_BYTES + (nvalid + (r >> 3)) * 128 + (r & 7) * 16) =
+              make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+      }
+
+      // ---- S = Q K^T : [16 heads x 16 tokens] ------------------------------------
+      float s[2][4];
+      if constexpr (!INT8) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        const int mi = lane >> 3;
+        const int r = (lane & 7) + (mi >> 1) * 8;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const int chunk = 2 * kk + (mi & 1);
+          const uint32_t addr = kbase + (chunk >> 3) * SLAB_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+          uint32_t kb[4];
+          ldmatrix_x4(kb, addr);
+          mma_f16_16816(s[0], qa[kk], kb[0], kb[1]);
+          mma_f16_16816(s[1], qa[kk], kb[2], kb[3]);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[j][e] *= p.scale_log2;
+      } else {
+        int si[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) si[j][0] = si[j][1] = si[j][2] = si[j][3] = 0;
+        const uint8_t* kptr = my_stages + (size_t)st * (2 * PAGE_BYTES);
+        auto quant_k4 = [&](int row, int d, float ksr) -> uint32_t {
+          const int chunk = d >> 3;  // 16-byte chunk within the row
+          const uint8_t* src = kptr + (chunk >> 3) * SLAB_BYTES + row * 128 +
+                               (((chunk & 7) ^ (row & 7)) << 4) + (d & 7) * 2;
+          const uint2 raw2 = *reinterpret_cast<const uint2*>(src);
+          const __half2 h01 = *reinterpret_cast<const __half2*>(&raw2.x);
+          const __half2 h23 = *reinterpret_cast<const __half2*>(&raw2.y);
+          const float f[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
+          uint32_t packed = 0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float t = fmaxf(-127.f, fminf(127.f, roundf(__fdiv_rn(f[i], ksr))));
+            packed |= (static_cast<uint32_t>(static_cast<int>(t)) & 0xffu) << (8 * i);
+          }
+          return packed;
+        };
+        const int c4 = (lane & 3) * 4;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int row = 8 * j + g;  // token within the page owned by this lane in the B fragment
+          const float ksr = __shfl_sync(0xffffffffu, ks_cur, row);
+#pragma unroll
+          for (int kk = 0; kk < D / 32; ++kk) {
+            const uint32_t b0 = quant_k4(row, kk * 32 + c4, ksr);
+            const uint32_t b1 = quant_k4(row, kk * 32 + 16 + c4, ksr);
+            mma_s8_16832(si[j], qa[kk], b0, b1);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const float ks_a = __shfl_sync(0xffffffffu, ks_cur, 8 * j + cq);
+          const float ks_b = __shfl_sync(0xffffffffu, ks_cur, 8 * j + cq + 1);
+          // score = float(dot) * q_s * k_s * scale, then to base 2
+          s[j][0] = ((static_cast<float>(si[j][0]) * q_s0) * ks_a) * p.scale * 1.4426950408889634f;
+          s[j][1] = ((static_cast<float>(si[j][1]) * q_s0) * ks_b) * p.scale * 1.4426950408889634f;
+          s[j][2] = ((static_cast<float>(si[j][2]) * q_s1) * ks_a) * p.scale * 1.4426950408889634f;
+          s[j][3] = ((static_cast<float>(si[j][3]) * q_s1) * ks_b) * p.scale * 1.4426950408889634f;
+          if (p.scores_out != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int row = g + (e >> 1) * 8;
+              const int tin = 8 * j + cq + (e & 1);
+              if (row < Gb && tin < nvalid)
+                p.scores_out[((size_t)b * p.H_Q + head0 + row) * p.N + page * 16 + tin] = si[j][e];
+            }
+          }
+        }
+      }
+
+      if (nvalid < 16) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (8 * j + cq + (e & 1) >= nvalid) s[j][e] = -INFINITY;
+      }
+
+      // ---- online softmax (base 2) ----------------------------------------------
+      float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+      float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
+      m0 = mn0;
+      m1 = mn1;
+      float pr[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        pr[j][0] = fast_exp2(s[j][0] - mn0);
+        pr[j][1] = fast_exp2(s[j][1] - mn0);
+        pr[j][2] = fast_exp2(s[j][2] - mn1);
+        pr[j][3] = fast_exp2(s[j][3] - mn1);
+      }
+      l0 = l0 * a0 + (pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1]);
+      l1 = l1 * a1 + (pr[0][2] + pr[0][3] + pr[1][2] + pr[1][3]);
+      uint32_t pa[4];
+      pa[0] = pack_half2(pr[0][0], pr[0][1]);
+      pa[1] = pack_half2(pr[0][2], pr[0][3]);
+      pa[2] = pack_half2(pr[1][0], pr[1][1]);
+      pa[3] = pack_half2(pr[1][2], pr[1][3]);
+      if (__any_sync(0xffffffffu, (a0 != 1.f) || (a1 != 1.f))) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          acc[i][0] *= a0;
+          acc[i][1] *= a0;
+          acc[i][2] *= a1;
+          acc[i][3] *= a1;
+        }
+      }
+
+      // ---- O += P V --------------------------------------------------------------
+      {
+        const int mi = lane >> 3;
+        const int r = (lane & 7) + (mi & 1) * 8;
+#pragma unroll
+        for (int c2 = 0; c2 < D / 16; ++c2) {
+          const int chunk = 2 * c2 + (mi >> 1);
+          const uint32_t addr = vbase + (chunk >> 3) * SLAB_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, addr);
+          mma_f16_16816(acc[2 * c2], pa, vb[0], vb[1]);
+          mma_f16_16816(acc[2 * c2 + 1], pa, vb[2], vb[3]);
+        }
+      }
+
+      if (nvalid < 16) fence_proxy_async();  // generic writes to this stage precede its next TMA fill
+      __syncwarp();
+      if (issued < n_my) {
+        if ((issued & 31) == 0) {
+          tbl_cur = tbl_next;
+          tbl_next = load_tbl((issued >> 5) + 1);
+        }
+        issue(issued);
+        ++issued;
+      }
+    }
+
+    // ---- merge the warps of this CTA ---------------------------------------------
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    {
+      float* mb = mbuf + (size_t)warp * p.slot_rows * ROWLEN;
+      if (g < Gb) {
+        float* rowp = mb + g * ROWLEN;
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+          *reinterpret_cast<float2*>(rowp + i * 8 + cq) = make_float2(acc[i][0], acc[i][1]);
+        if ((lane & 3) == 0) {
+          rowp[D] = m0;
+          rowp[D + 1] = l0;
+        }
+      }
+      if (g + 8 < Gb) {
+        float* rowp = mb + (g + 8) * ROWLEN;
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+          *reinterpret_cast<float2*>(rowp + i * 8 + cq) = make_float2(acc[i][2], acc[i][3]);
+        if ((lane & 3) == 0) {
+          rowp[D] = m1;
+          rowp[D + 1] = l1;
+        }
+      }
+    }
+    __syncthreads();
+    {
+      const int slot = (piece == 0) ? 0 : 1;
+      float* part = p.partials + ((size_t)blockIdx.x * 2 + slot) * p.slot_rows * ROWLEN;
+      for (int e = threadIdx.x; e < Gb * D; e += blockDim.x) {
+        const int row = e / D, d = e - row * D;
+        float M = -INFINITY;
+        for (int w = 0; w < W; ++w) M = fmaxf(M, mbuf[((size_t)w * p.slot_rows + row) * ROWLEN + D]);
+        float L = 0.f, O = 0.f;
+        for (int w = 0; w < W; ++w) {
+          const float* rp = mbuf + ((size_t)w * p.slot_rows + row) * ROWLEN;
+          const float f = fast_exp2(rp[D] - M);
+          L += rp[D + 1] * f;
+          O += rp[d] * f;
+        }
+        if (complete) {
+          p.out[((size_t)b * p.H_Q + head0 + row) * D + d] = __float2half_rn(O / L);
+        } else {
+          part[row * ROWLEN + d] = O;
+          if (d == 0) {
+            part[row * ROWLEN + D] = M;
+            part[row * ROWLEN + D + 1] = L;
+          }
+        }
+      }
+    }
+    __syncthreads();
+
+    u += cnt;
+    ++piece;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// combine: one CTA per segment; merges partials of segments split across CTAs,
+// writes zeros for empty sequences.
+// ---------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeParams p) {
+  constexpr int ROWLEN = D + 2;
+  const int seg = blockIdx.x;
+  const int b = seg / p.HV, hv = seg - b * p.HV;
+  const int h_kv = hv / p.n_gblk;
+  const int gb0 = (hv - h_kv * p.n_gblk) * 16;
+  const int Gb = (p.G - gb0) < 16 ? (p.G - gb0) : 16;
+  const int head0 = h_kv * p.G + gb0;
+  const int np = p.prefix[b + 1] - p.prefix[b];
+  __half* outp = p.out + ((size_t)b * p.H_Q + head0) * D;
+  if (np == 0) {
+    for (int e = threadIdx.x; e < Gb * D; e += blockDim.x) outp[e] = __float2half_rn(0.f);
+    return;
+  }
+  const long long T = (long long)p.HV * p.prefix[p.B];
+  long long per = (T + p.n_cta - 1) / p.n_cta;
+  if (per < 1) per = 1;
+  const long long seg_start = (long long)p.HV * p.prefix[b] + (long long)hv * np;
+  const long long seg_end = seg_start + np;
+  const int first = (int)(seg_start / per), last = (int)((seg_end - 1) / per);
+  if (first == last) return;  // written directly by the CTA that owned the whole segment
+  for (int e = threadIdx.x; e < Gb * D; e += blockDim.x) {
+    const int row = e / D, d = e - row * D;
+    float M = -INFINITY;
+    for (int c = first; c <= last; ++c) {
+      const int slot = ((long long)c * per >= seg_start) ? 0 : 1;
+      const float* part = p.partials + ((size_t)c * 2 + slot) * p.slot_rows * ROWLEN;
+      M = fmaxf(M, part[row * ROWLEN + D]);
+    }
+    float L = 0.f, O = 0.f;
+    for (int c = first; c <= last; ++c) {
+      const int slot = ((long long)c * per >= seg_start) ? 0 : 1;
+      const float* part = p.partials + ((size_t)c * 2 + slot) * p.slot_rows * ROWLEN;
+      const float f = fast_exp2(part[row * ROWLEN + D] - M);
+      L += part[row * ROWLEN + D + 1] * f;
+      O += part[row * ROWLEN + d] * f;
+    }
+    outp[(size_t)row * D + d] = __float2half_rn(O / L);
+  }
+}
+
+template <int D, bool INT8>
+cudaError_t launch_t(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p,
+                     int warps, size_t smem_bytes, cudaStream_t stream) {
+  auto kern = decode_splitkv_kernel<D, INT8>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+  if (e != cudaSuccess) return e;
+  decode_plan_kernel<<<1, 1024, 0, stream>>>(p);
+  kern<<<p.n_cta, warps * 32, smem_bytes, stream>>>(kmap, vmap, p);
+  decode_combine_kernel<D><<<p.B * p.HV, 128, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t decode_smem_bytes(int D, int warps, int stages, int slot_rows, int B) {
+  size_t bytes = 1024;  // slack to align the first stage to 1024 B (128-byte swizzle atom)
+  bytes += (size_t)warps * stages * (2 * 16 * D * 2);
+  bytes += (size_t)warps * stages * 8;
+  bytes += (size_t)warps * slot_rows * (D + 2) * 4;
+  if (B + 1 <= kMaxSmemPrefix) bytes += (size_t)(B + 1) * 4;
+  return (bytes + 15) & ~(size_t)15;
+}
+
+size_t decode_workspace_bytes(int B, int H_Q, int H_KV, int D, int max_ctas) {
+  const int G = H_Q / H_KV;
+  const int slot_rows = G < 16 ? G : 16;
+  size_t bytes = kWsPrefixOffset;
+  bytes += ((size_t)(B + 1) * 4 + 255) & ~(size_t)255;
+  bytes += (size_t)max_ctas * 2 * slot_rows * (D + 2) * 4;
+  return (bytes + 255) & ~(size_t)255;
+}
+
+cudaError_t launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p,
+                          int D, bool int8, int warps, size_t smem_bytes, cudaStream_t stream) {
+  switch (D) {
+    case 64:
+      return int8 ? launch_t<64, true>(kmap, vmap, p, warps, smem_bytes, stream)
+                  : launch_t<64, false>(kmap, vmap, p, warps, smem_bytes, stream);
+    case 128:
+      return int8 ? launch_t<128, true>(kmap, vmap, p, warps, smem_bytes, stream)
+                  : launch_t<128, false>(kmap, vmap, p, warps, smem_bytes, stream);
+    case 256:
+      return int8 ? launch_t<256, true>(kmap, vmap, p, warps, smem_bytes, stream)
+                  : launch_t<256, false>(kmap, vmap, p, warps, smem_bytes, stream);
+    default:
+      return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace fa

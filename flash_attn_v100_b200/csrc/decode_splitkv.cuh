@@ -1,0 +1,56 @@
+// Split-KV GQA decode: parameter block and launcher shared by the C-ABI entry points.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fa {
+
+enum DecodeMode : int {
+  kModePaged = 0,         // len = max(lens[b], 0); rows found through block_table
+  kModeContigVarlen = 1,  // len = clamp(lens[b] + 1, 0, N); rows contiguous per (b, h_kv)
+  kModeContigFixed = 2,   // len = fixed_len for every sequence; rows contiguous
+};
+
+struct DecodeParams {
+  const __half* q;             // [B, H_Q, 1, D]
+  __half* out;                 // [B, H_Q, 1, D]
+  const int32_t* block_table;  // paged only
+  const int32_t* lens;         // seq_lens / cache_lens, null in fixed mode
+  const float* q_scale;        // int8 only: [B, H_Q]
+  const float* k_scale;        // int8 only: [B, H_KV, N]
+  int32_t* scores_out;         // int8 only, optional: [B, H_Q, N]
+  int32_t* prefix;             // workspace: [B + 1] running page counts
+  float* partials;             // workspace: [n_cta][2][slot_rows][D + 2]
+  int32_t* status;             // workspace: sticky status word
+  int B, H_Q, H_KV, G;         // G = H_Q / H_KV
+  int n_gblk;                  // ceil(G / 16): query-head blocks per KV head
+  int HV;                      // H_KV * n_gblk
+  int mode, fixed_len, N;      // N: tokens per (b, h_kv) row in contiguous modes
+  int bt_stride;
+  long long num_pages;
+  int n_cta, stages, slot_rows;
+  float scale;                 // 1 / sqrt(D)
+  float scale_log2;            // scale * log2(e)
+};
+
+struct DecodeLaunchConfig {
+  int warps;        // consumer warps per CTA
+  int stages;       // TMA ring depth per warp
+  int ctas_per_sm;  // persistent CTAs per SM
+};
+
+// Workspace layout helpers (host).
+size_t decode_workspace_bytes(int B, int H_Q, int H_KV, int D, int max_ctas);
+constexpr size_t kWsStatusOffset = 0;     // int32 status word (+ padding to 256 B)
+constexpr size_t kWsPrefixOffset = 256;   // int32 prefix[B + 1]
+
+// Launch plan + main + combine on `stream`.  kmap/vmap are 2-D tensor maps over
+// K and V seen as [rows, D] fp16 with a 64-column x 16-row box and 128-byte swizzle.
+cudaError_t launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p,
+                          int D, bool int8, int warps, size_t smem_bytes, cudaStream_t stream);
+
+size_t decode_smem_bytes(int D, int warps, int stages, int slot_rows, int B);
+
+}  // namespace fa

@@ -1,0 +1,29 @@
+// Prefill parameter block shared by the prefill kernels and the C-ABI layer.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fa {
+
+struct PrefillParams {
+  const __half* q;
+  const __half* k;
+  const __half* v;
+  __half* out;
+  const int32_t* cu_seqlens;  // null => dense [B,H,N,D]; else packed [total,H,D]
+  int batch;                  // sequences (dense: B)
+  int H_Q, H_KV;
+  int N;                      // dense sequence length (unused when packed)
+  int max_seqlen;             // packed: grid bound; dense: N
+  long long total;            // packed: rows in q/k/v
+  long long q_batch_stride, q_head_stride, q_tok_stride;     // elements
+  long long kv_batch_stride, kv_head_stride, kv_tok_stride;  // elements
+  int causal;
+  float scale_log2;           // log2(e) / sqrt(D)
+};
+
+cudaError_t launch_prefill_mma(const PrefillParams& p, int D, cudaStream_t stream);
+
+}  // namespace fa

@@ -1,0 +1,168 @@
+/*
+ * fa_b200.h — C ABI of the B200 (sm_100a) attention library.
+ *
+ * This is the boundary a binding of the reference project's operator module
+ * (`flash_attn_v100`, built from flash_attn.cpp) would call instead of that
+ * project's own CUDA wrappers.  Plain pointers and sizes only: no torch types.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer on the CURRENT CUDA device unless it is
+ *    marked "host".  The caller makes the right device current.
+ *  - All tensors are dense/contiguous in the layouts given per function.
+ *  - Calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL is
+ *    the legacy default stream).  Nothing here synchronises the device.
+ *  - No function allocates device memory.  Split-KV decode needs scratch
+ *    ("workspace"); the caller owns it, sizes it with fa_decode_workspace_bytes()
+ *    and may reuse it for calls that are ordered on one stream.  Calls that can
+ *    overlap on the GPU need distinct workspaces.
+ *  - Return value: FA_OK or a negative fa_status; fa_last_error() gives the text
+ *    for the calling thread.  Invalid arguments are rejected before any launch.
+ *  - fp16 tensors are IEEE binary16; softmax scale is always 1/sqrt(D)
+ *    (the reference wrappers compute it themselves, flash_attn_kernel.cu:265).
+ *  - GQA head map everywhere: h_kv = h_q / (H_Q / H_KV) (flash_attn_kernel.cu:1662).
+ *  - Supported head dims: D in {64, 128, 256}.
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum fa_status {
+  FA_OK = 0,
+  FA_ERR_INVALID_ARGUMENT = -1,  /* shape / size / alignment / null pointer      */
+  FA_ERR_UNSUPPORTED = -2,       /* valid in the reference, not built here (D)   */
+  FA_ERR_WORKSPACE = -3,         /* workspace missing or too small               */
+  FA_ERR_CUDA = -4,              /* a CUDA runtime/driver call or launch failed  */
+  FA_ERR_DEVICE_STATUS = -5      /* a kernel recorded a bounded-wait timeout or a
+                                    page id outside the pool (fa_decode_status)   */
+} fa_status;
+
+#define FA_PAGE_SIZE 16 /* tokens per KV page; flash_attn_kernel.cu:3389 PAGE_BLOCK_SIZE */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int fa_version(void);
+
+/* Text of the last error on the calling thread ("" if none). */
+const char* fa_last_error(void);
+
+/* Bytes of scratch the decode entry points need for a batch of B sequences with
+ * H_Q query heads, H_KV KV heads and head dim D on the current device.
+ * Returns 0 on invalid arguments. */
+size_t fa_decode_workspace_bytes(int B, int H_Q, int H_KV, int D);
+
+/* Zero the status word of a workspace (do this once after allocating it). */
+int fa_decode_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Read back (synchronously: it waits for `stream`) the sticky device-side status
+ * word of a workspace: 0 = clean; bit 0 = a bounded wait on a copy barrier ran
+ * out; bit 1 = a block_table entry used by a sequence was outside [0, num_pages).
+ * Results of a launch that set a bit are undefined (but no fault is raised). */
+int fa_decode_status(const void* workspace, void* stream, int* host_status_out);
+
+/* Tuning hook for the decode kernels: consumer warps per CTA, copy-ring depth per
+ * warp and persistent CTAs per SM.  0 keeps the built-in choice for that field.
+ * Process-wide; values that do not fit in shared memory are reduced. */
+int fa_decode_set_tuning(int warps, int stages, int ctas_per_sm);
+
+/*
+ * Paged GQA decode.  Replaces flash_attn_forward_paged_decode_gqa_fp16
+ * (flash_attn_kernel.cu:3516-3584; bound at flash_attn.cpp:238).
+ *   q           [B, H_Q, 1, D] fp16
+ *   k_cache,
+ *   v_cache     [num_pages, H_KV, 16, D] fp16
+ *   block_table [B, >= pages used] int32, row stride = block_table_stride
+ *               elements (the reference passes this as `max_num_blocks`,
+ *               flash_attn_kernel.cu:3438); unused entries are ignored
+ *   seq_lens    [B] int32: tokens to attend, token t of sequence b lives at
+ *               cache[block_table[b][t/16], h_kv, t%16, :]
+ *   out         [B, H_Q, 1, D] fp16 (fully overwritten; seq_len <= 0 gives zeros,
+ *               where the reference divides 0/0)
+ *   max_seq_len upper bound on seq_lens used to size the grid only; pass
+ *               block_table_stride*16 when unknown.
+ */
+int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                            const int32_t* block_table, const int32_t* seq_lens,
+                            int B, int H_Q, int H_KV, int D,
+                            int64_t num_pages, int block_table_stride, int64_t max_seq_len,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * GQA decode over a contiguous cache with one length for the whole batch.
+ * Replaces flash_attn_forward_decode_gqa_fp16 / _out / _stream
+ * (flash_attn_kernel.cu:1800-1861, 3639-3675; flash_attn.cpp:232-233,241) and, with
+ * H_KV == H_Q, flash_attn_forward_decode_fp16 (flash_attn_kernel.cu:1863-1913).
+ *   q [B,H_Q,1,D], k/v [B,H_KV,N,D], out [B,H_Q,1,D], all fp16.
+ *   The query sits at position cache_len (0 <= cache_len < N); key j is visible
+ *   iff !causal || j <= cache_len (flash_attn_kernel.cu:1719).
+ */
+int fa_decode_gqa_f16(const void* q, const void* k, const void* v, void* out,
+                      int B, int H_Q, int H_KV, int N, int D, int causal, int cache_len,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Continuous-batching decode: contiguous cache padded to max_N, one length per
+ * sequence.  Replaces flash_attn_forward_continuous_batching_fp16
+ * (continuous_batching_kernel.cu:338-406; flash_attn.cpp:243).
+ *   cache_lens [B] int32; sequence b attends keys [0, min(cache_lens[b]+1, max_N))
+ *   (continuous_batching_kernel.cu:66-69).  `causal` is accepted for signature
+ *   parity and has no effect, as in the reference (no key in range exceeds the
+ *   query position).  cache_lens[b] < 0 gives zeros.
+ */
+int fa_decode_varlen_f16(const void* q, const void* k, const void* v, void* out,
+                         const int32_t* cache_lens,
+                         int B, int H_Q, int H_KV, int max_N, int D, int causal,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * INT8-QK decode.  Replaces flash_attn_forward_decode_int8_gqa
+ * (flash_attn_kernel.cu:2941-3003, kernel :2796-2939; flash_attn.cpp:239).
+ *   q [B,H_Q,1,D], k/v [B,H_KV,N,D] fp16; q_scale [B,H_Q] fp32;
+ *   k_scale [B,H_KV,N] fp32 (one scale per cached token: README.md:169-171 of the
+ *   reference; its kernel reads a single scalar per (b,h_kv) from that tensor,
+ *   flash_attn_kernel.cu:2825, which this library does not reproduce).
+ *   q^ = clamp(roundf(q/q_s),-127,127), k^ likewise in IEEE fp32 (round half away
+ *   from zero); dot = sum q^*k^ in int32 (exact); score = float(dot)*q_s*k_s/sqrt(D);
+ *   keys j > cache_len masked; fp32 softmax; fp16 V, fp32 accumulation.
+ *   scores_i32_out: optional [B,H_Q,N] int32 receiving the raw int32 dots of the
+ *   visible keys (others left untouched); NULL to skip.
+ */
+int fa_decode_int8_gqa(const void* q, const void* k, const void* v, void* out,
+                       const float* q_scale, const float* k_scale,
+                       int B, int H_Q, int H_KV, int N, int D, int cache_len,
+                       int32_t* scores_i32_out,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Dense causal/non-causal GQA prefill.  Replaces flash_attn_forward_fp16
+ * (flash_attn_kernel.cu:1915-1962; H_KV == H_Q) and
+ * flash_attn_forward_prefill_gqa_fp16 / _out (flash_attn_kernel.cu:2740-2794;
+ * flash_attn.cpp:226,235-236).
+ *   q [B,H_Q,N,D], k/v [B,H_KV,N,D], out [B,H_Q,N,D], all fp16.
+ */
+int fa_prefill_dense_f16(const void* q, const void* k, const void* v, void* out,
+                         int B, int H_Q, int H_KV, int N, int D, int causal, void* stream);
+
+/*
+ * Packed variable-length GQA prefill.  Replaces
+ * flash_attn_forward_varlen_prefill_fp16 / _stream (flash_attn_kernel.cu:3354-3387,
+ * 3677-3712; flash_attn.cpp:240,242).  The reference requires H_KV == H_Q
+ * (flash_attn_kernel.cu:217); this entry point also accepts H_Q % H_KV == 0.
+ *   q [total,H_Q,D], k/v [total,H_KV,D], out [total,H_Q,D] fp16;
+ *   cu_seqlens [batch+1] int32 (device), non-decreasing, cu_seqlens[0] == 0,
+ *   cu_seqlens[batch] <= total; max_seqlen > 0 bounds the longest sequence (it
+ *   sizes the grid; rows of longer sequences beyond it are not computed, as in the
+ *   reference).  Rows not covered by any sequence are left untouched.
+ */
+int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out,
+                          const int32_t* cu_seqlens, int batch, int64_t total,
+                          int H_Q, int H_KV, int D, int max_seqlen, int causal, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */

@@ -268,18 +268,10 @@ def make_paged_workload(B, H_Q, H_KV, D, min_len, max_len, seed=0, dtype=torch.f
                         fill=True):
     """Seeded paged-decode workload: seq_lens uniform in [min_len, max_len],
     pool of sum(ceil(len/16)) pages, block_table a random permutation of it."""
-    g = torch.Generator().manual_seed(seed)
-    seq_lens = torch.randint(min_len, max_len + 1, (B,), generator=g, dtype=torch.int32)
-    pages = (seq_lens + PAGE_BLOCK_SIZE - 1) // PAGE_BLOCK_SIZE
-    n_pages = int(pages.sum())
-    perm = torch.randperm(n_pages, generator=g).to(torch.int32)
-    max_blocks = max(int(pages.max()), 1)
-    block_table = torch.full((B, max_blocks), -1, dtype=torch.int32)
-    cur = 0
-    for b in range(B):
-        n = int(pages[b])
-        block_table[b, :n] = perm[cur:cur + n]
-        cur += n
+    from flash_attn_v100_b200.synthetic import make_paged_tables
+    t = make_paged_tables(B, min_len, max_len, seed)
+    g, seq_lens, block_table = t["generator"], t["seq_lens"], t["block_table"]
+    n_pages, max_blocks = t["n_pages"], t["max_num_blocks"]
     q = torch.randn(B, H_Q, 1, D, generator=g).to(dtype)
     if fill:
         k_cache = torch.randn(max(n_pages, 1), H_KV, PAGE_BLOCK_SIZE, D, generator=g).to(dtype)
