@@ -109,7 +109,7 @@ fa::DecodeLaunchConfig g_cfg_override = {0, 0, 0};
 fa::DecodeLaunchConfig pick_decode_config(int D, int slot_rows, int B, const DeviceInfo& di) {
   fa::DecodeLaunchConfig c;
   if (D == 256) c = {4, 2, 1};
-  else if (D == 128) c = {4, 3, 2};
+  else if (D == 128) c = {4, 2, 2};
   else c = {4, 4, 2};
   if (g_cfg_override.warps > 0) c.warps = g_cfg_override.warps;
   if (g_cfg_override.stages > 0) c.stages = g_cfg_override.stages;

@@ -22,6 +22,7 @@ from . import _lib
 
 PAGE_BLOCK_SIZE = 16  # flash_attn_kernel.cu:3389
 MAX_D_LARGE = 256     # flash_attn_kernel.cu:36
+SUPPORTED_D = (64, 128, 256)
 
 _workspaces: Dict[Tuple[int, int, int], torch.Tensor] = {}
 
@@ -100,6 +101,7 @@ def _workspace(device, stream_int, B, H_Q, H_KV, D):
     (device, stream), grown on demand.  Calls on one stream are ordered, so they
     may share it."""
     lib = _lib.load()
+    _chk(D in SUPPORTED_D, f"head dimension {D} is not built (supported: 64, 128, 256)")
     need = int(lib.fa_decode_workspace_bytes(B, H_Q, H_KV, D))
     _chk(need > 0, f"unsupported decode configuration B={B} H_Q={H_Q} H_KV={H_KV} D={D}")
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream_int)
