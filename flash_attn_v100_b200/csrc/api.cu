@@ -332,6 +332,62 @@ int fa_decode_int8_gqa(const void* q, const void* k, const void* v, void* out, c
   return run_decode(c);
 }
 
+// ---------------------------------------------------------------------------
+// Paged decode for callers that cannot allocate device memory.
+//
+// The split-KV scratch (status word, page prefix sums, per-CTA partial results)
+// lives in a fixed array that is part of the loaded module image, so the call
+// needs no cudaMalloc and no caller-provided workspace.  Every device that loads
+// the library holds these bytes until the process exits.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
+
+namespace {
+// In host code the array's name is only a handle for the runtime, not a device
+// address, so the device address is looked up once per device and cached.
+void* g_static_scratch_ptr[64] = {nullptr};
+std::mutex g_static_scratch_mu;
+
+int static_scratch_for_current_device(void** out, cudaStream_t stream) {
+  int dev = 0;
+  FA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(FA_ERR_CUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_static_scratch_mu);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    FA_CUDA(cudaGetSymbolAddress(&ptr, g_static_decode_scratch));
+    if (ptr == nullptr) return fail(FA_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    // the status word must start at zero; everything else is written before it is read
+    FA_CUDA(cudaMemsetAsync(ptr, 0, 256, stream));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return FA_OK;
+}
+}  // namespace
+
+int fa_paged_decode_gqa_f16_static_scratch(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                           const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q,
+                                           int H_KV, int D, int64_t num_pages, int block_table_stride,
+                                           int64_t max_seq_len, void* stream) {
+  // argument errors first, so that a bad call never touches the device
+  if (B <= 0 || H_Q <= 0 || H_KV <= 0 || H_Q % H_KV != 0)
+    return fail(FA_ERR_INVALID_ARGUMENT, "B, H_Q, H_KV must be positive and H_Q divisible by H_KV");
+  if (!supported_d(D)) return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (supported: 64, 128, 256)", D);
+  const size_t need = fa::decode_workspace_bytes(B, H_Q, H_KV, D, kMaxDecodeCtas);
+  if (need > kStaticScratchBytes)
+    return fail(FA_ERR_WORKSPACE,
+                "this shape needs %zu bytes of decode scratch but the built-in scratch holds %zu: use "
+                "fa_paged_decode_gqa_f16 with a caller-owned workspace",
+                need, (size_t)kStaticScratchBytes);
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch, static_cast<cudaStream_t>(stream));
+  if (rc != FA_OK) return rc;
+  return fa_paged_decode_gqa_f16(q, k_cache, v_cache, out, block_table, seq_lens, B, H_Q, H_KV, D, num_pages,
+                                 block_table_stride, max_seq_len, scratch, kStaticScratchBytes, stream);
+}
+
 static int run_prefill(fa::PrefillParams& p, int D, cudaStream_t stream) {
   DeviceInfo di;
   int rc = device_info(&di);

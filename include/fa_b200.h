@@ -92,6 +92,40 @@ int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_ca
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Paged GQA decode without any caller-provided scratch.  This entry point has no
+ * counterpart in the reference project.
+ *
+ * Who it is for: code that must not, or cannot, obtain device memory at the point
+ * of the call - for example a binding that runs inside a serving process whose
+ * memory pool already owns the whole GPU (a later cudaMalloc would fail), or a
+ * latency-critical call site where the implicit device synchronisation of
+ * cudaMalloc/cudaFree is not acceptable.  Such callers have nowhere to get the
+ * split-KV workspace of fa_paged_decode_gqa_f16 from.
+ *
+ * Same arguments, layouts and results as fa_paged_decode_gqa_f16, minus the
+ * workspace.  The scratch is an 8 MiB array built into the library image: every
+ * GPU that loads the library keeps those 8 MiB until the process exits.
+ *  - Limit: shapes whose fa_decode_workspace_bytes(B, H_Q, H_KV, D) exceeds 8 MiB
+ *    are rejected with FA_ERR_WORKSPACE (nothing is launched).  The benchmark shape
+ *    (B=64, 32/8 heads, D=128) needs 4.7 MiB.
+ *  - The first call on each device looks up the array's device address (and clears
+ *    its status word); make that first call outside of any stream capture.
+ *  - Nothing in this call allocates or frees device memory.
+ *  - All calls on a device share the one array, and it keeps whatever the previous
+ *    call left in it (each call rewrites every part it later reads).  Two calls that
+ *    can overlap on the GPU - different streams without an ordering between them -
+ *    race on it; order them, or give all but one of them a workspace of their own
+ *    through fa_paged_decode_gqa_f16.
+ *  - The device status word of the built-in scratch is not exposed through
+ *    fa_decode_status.
+ */
+int fa_paged_decode_gqa_f16_static_scratch(const void* q, const void* k_cache, const void* v_cache,
+                                           void* out, const int32_t* block_table,
+                                           const int32_t* seq_lens, int B, int H_Q, int H_KV, int D,
+                                           int64_t num_pages, int block_table_stride,
+                                           int64_t max_seq_len, void* stream);
+
+/*
  * GQA decode over a contiguous cache with one length for the whole batch.
  * Replaces flash_attn_forward_decode_gqa_fp16 / _out / _stream
  * (flash_attn_kernel.cu:1800-1861, 3639-3675; flash_attn.cpp:232-233,241) and, with
