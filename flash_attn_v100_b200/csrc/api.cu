@@ -388,12 +388,40 @@ int fa_paged_decode_gqa_f16_static_scratch(const void* q, const void* k_cache, c
                                  block_table_stride, max_seq_len, scratch, kStaticScratchBytes, stream);
 }
 
+static int g_prefill_impl = 0;  // 0 auto, 1 mma.sync kernel, 2 tcgen05 kernel
+
+int fa_prefill_set_impl(int impl) {
+  FA_REQUIRE(impl >= 0 && impl <= 2, "impl must be 0 (auto), 1 (mma.sync) or 2 (tcgen05)");
+  g_prefill_impl = impl;
+  return FA_OK;
+}
+
+int fa_prefill_status(void* stream, int* host_status_out, int clear) {
+  FA_REQUIRE(host_status_out != nullptr, "null pointer");
+  FA_CUDA(fa::prefill_status(host_status_out, static_cast<cudaStream_t>(stream)));
+  if (clear) FA_CUDA(fa::prefill_status_clear(static_cast<cudaStream_t>(stream)));
+  if (*host_status_out != 0)
+    return fail(FA_ERR_DEVICE_STATUS, "prefill kernel recorded device status 0x%x", *host_status_out);
+  return FA_OK;
+}
+
 static int run_prefill(fa::PrefillParams& p, int D, cudaStream_t stream) {
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc != FA_OK) return rc;
   p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
-  cudaError_t e = fa::launch_prefill_mma(p, D, stream);
+  cudaError_t e;
+  const bool tc5_ok = fa::prefill_tc5_supported(p, D);
+  if (g_prefill_impl == 2 && !tc5_ok)
+    return fail(FA_ERR_UNSUPPORTED, "the tcgen05 prefill kernel supports D = 64 and 128 only");
+  if (tc5_ok && g_prefill_impl != 1) {
+    EncodeTiledFn enc;
+    rc = get_encode(&enc);
+    if (rc != FA_OK) return rc;
+    e = fa::launch_prefill_tc5(p, D, reinterpret_cast<void*>(enc), stream);
+  } else {
+    e = fa::launch_prefill_mma(p, D, stream);
+  }
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, "prefill launch failed: %s", cudaGetErrorString(e));
   return FA_OK;
 }

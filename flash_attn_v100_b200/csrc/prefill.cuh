@@ -26,4 +26,10 @@ struct PrefillParams {
 
 cudaError_t launch_prefill_mma(const PrefillParams& p, int D, cudaStream_t stream);
 
+// tcgen05 / TMEM kernel (D = 64 or 128).  `encode_fn` is cuTensorMapEncodeTiled.
+bool prefill_tc5_supported(const PrefillParams& p, int D);
+cudaError_t launch_prefill_tc5(const PrefillParams& p, int D, void* encode_fn, cudaStream_t stream);
+cudaError_t prefill_status(int* host_out, cudaStream_t stream);
+cudaError_t prefill_status_clear(cudaStream_t stream);
+
 }  // namespace fa

@@ -1,0 +1,537 @@
+// Causal / non-causal GQA prefill on 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+// Replaces the reference's prefill kernels (flash_attn_kernel.cu:1138-1299, 2471-2605,
+// 3005-3148) for D = 64 and D = 128, dense [B,H,N,D] and packed varlen [total,H,D].
+//
+// One CTA works on TWO 128-row query tiles that share one KV head and one KV range, so
+// every K/V tile staged in shared memory feeds two score tiles:
+//   - "head pair" mode (even group size): the same 128 rows of two adjacent query heads;
+//   - "row pair" mode: two consecutive 128-row blocks of one query head.
+// Warp roles (12 warps):
+//   warp 0      TMA producer: Q once, then K_j / V_j tiles (128 keys) through a ring
+//   warp 1      MMA issuer (one lane): S_t = Q_t K_j^T and O_t += P_t V_j with tcgen05.mma,
+//               accumulators in tensor memory; completion signalled by tcgen05.commit
+//   warp 2      tensor-memory allocation / release
+//   warps 4-7   softmax of tile 0 (thread = one query row = one TMEM lane)
+//   warps 8-11  softmax of tile 1
+// The two softmax groups ping-pong: while one group turns S_0 into P_0, the tensor core
+// runs the other tile's MMAs.  P is written back to tensor memory as fp16 over the first
+// half of the S columns it came from and is the A operand of the PV MMA (no shared-memory
+// round trip).  Softmax is fp32, base 2, online across KV tiles; O is rescaled in tensor
+// memory only when a row maximum grows by more than 2^8 (stale maxima keep P <= 256, exact
+// in fp16 range and compensated in the fp32 row sum).  Causal tiles above the diagonal are
+// skipped; only the diagonal tile and the ragged last tile are masked per element.
+//
+// Tensor-memory map (512 columns x 128 lanes): S_0 [0,128) S_1 [128,256) O_0 [256,256+D)
+// O_1 [256+D, 256+2D).  Every wait on an mbarrier is bounded; on a timeout the CTA sets an
+// abort flag, records a status bit and runs to completion without further waiting.
+#include "common.cuh"
+#include "prefill.cuh"
+
+namespace fa {
+
+__device__ int g_prefill_status = 0;
+
+namespace {
+
+constexpr uint32_t kTc5MaxPolls = 1u << 21;
+
+struct Tc5Params {
+  __half* out;
+  const int32_t* cu_seqlens;
+  int batch, H_Q, H_KV, N, max_seqlen;
+  long long total;
+  long long o_batch_stride, o_head_stride, o_tok_stride;
+  int causal;
+  int pair_heads;  // 1: two heads x same rows; 0: one head x two row blocks
+  int dense;
+  float scale_log2;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kTc5MaxPolls; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicOr(&g_prefill_status, kStatusWaitTimeout);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const float (&v)[32]) {
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// Shared-memory matrix descriptor for 128-byte-swizzled tiles made of 128-byte rows.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;  // 128-byte swizzle
+  return d;
+}
+
+template <int D>
+__global__ void __launch_bounds__(384, 1)
+prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                   const __grid_constant__ CUtensorMap vmap, const Tc5Params p) {
+  constexpr int BM = 128, BN = 128;
+  constexpr int KV_STAGES = (D == 128) ? 2 : 4;
+  constexpr int SLAB = 128 * 128;            // bytes of a [128 rows][64 cols] fp16 slab
+  constexpr int NSLAB = D / 64;
+  constexpr int TILE_BYTES = NSLAB * SLAB;   // one Q / K / V tile
+  constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t O_COL0 = 256;
+
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  uint8_t* smem = smem_dyn + ((1024u - (raw & 1023u)) & 1023u);
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sK = sQ + 2 * TILE_BYTES;
+  const uint32_t sV = sK + KV_STAGES * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * KV_STAGES) * TILE_BYTES);
+  // barrier indices
+  constexpr int B_QFULL = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + KV_STAGES, B_VFULL = B_KEMPTY + KV_STAGES,
+                B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES, B_PFULL = B_SFULL + 2,
+                B_OFULL = B_PFULL + 2, B_COUNT = B_OFULL + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto bar = [&](int i) -> uint32_t { return smem_u32(bars + i); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- which tiles ----------------------------------------------------------------
+  const int rb = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal blocks first
+  const int seq = blockIdx.z;
+  int head[2], row0[2];
+  if (p.pair_heads) {
+    head[0] = 2 * blockIdx.y; head[1] = head[0] + 1;
+    row0[0] = row0[1] = rb * BM;
+  } else {
+    head[0] = head[1] = blockIdx.y;
+    row0[0] = rb * 2 * BM; row0[1] = row0[0] + BM;
+  }
+  const int h_kv = head[0] / (p.H_Q / p.H_KV);
+  long long tok0;
+  int len;
+  if (p.cu_seqlens != nullptr) {
+    const int a = __ldg(p.cu_seqlens + seq), e = __ldg(p.cu_seqlens + seq + 1);
+    tok0 = a;
+    len = e - a;
+    if ((long long)e > p.total) len = (int)(p.total - a);
+  } else {
+    tok0 = 0;
+    len = p.N;
+  }
+  if (len > p.max_seqlen) len = p.max_seqlen;
+  int n_kv[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    if (row0[t] >= len) n_kv[t] = 0;
+    else {
+      const int kv_end = p.causal ? ((row0[t] + BM) < len ? (row0[t] + BM) : len) : len;
+      n_kv[t] = (kv_end + BN - 1) / BN;
+    }
+  }
+  if (n_kv[0] == 0) return;  // tile 0 holds the earlier rows: nothing to do for this CTA
+  const int n_max = n_kv[0] > n_kv[1] ? n_kv[0] : n_kv[1];
+
+  // TMA coordinates (x, c1, c2)
+  int q_c1[2], q_c2[2], kv_c1, kv_c2;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    if (p.dense) { q_c1[t] = 0; q_c2[t] = (seq * p.H_Q + head[t]) * p.N + row0[t]; }
+    else { q_c1[t] = head[t]; q_c2[t] = (int)tok0 + row0[t]; }
+  }
+  if (p.dense) { kv_c1 = 0; kv_c2 = (seq * p.H_KV + h_kv) * p.N; }
+  else { kv_c1 = h_kv; kv_c2 = (int)tok0; }
+
+  // ---- set-up ---------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    mbar_init(bar(B_QFULL), 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(bar(B_KFULL + s), 1);
+      mbar_init(bar(B_KEMPTY + s), 1);
+      mbar_init(bar(B_VFULL + s), 1);
+      mbar_init(bar(B_VEMPTY + s), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar(B_SFULL + t), 1);
+      mbar_init(bar(B_PFULL + t), 128);
+      mbar_init(bar(B_OFULL + t), 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+    tma_prefetch_desc(&qmap);
+    tma_prefetch_desc(&kmap);
+    tma_prefetch_desc(&vmap);
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ============================ TMA producer ======================================
+    if (lane == 0) {
+      const int n_act = n_kv[1] > 0 ? 2 : 1;
+      mbar_expect_tx(bar(B_QFULL), n_act * TILE_BYTES);
+      for (int t = 0; t < n_act; ++t)
+#pragma unroll
+        for (int sl = 0; sl < NSLAB; ++sl)
+          tma_load_3d(sQ + t * TILE_BYTES + sl * SLAB, &qmap, sl * 64, q_c1[t], q_c2[t], bar(B_QFULL));
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j % KV_STAGES;
+        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+        if (j >= KV_STAGES) wait_or_abort(bar(B_KEMPTY + st), ph ^ 1u, abort_flag);
+        mbar_expect_tx(bar(B_KFULL + st), TILE_BYTES);
+#pragma unroll
+        for (int sl = 0; sl < NSLAB; ++sl)
+          tma_load_3d(sK + st * TILE_BYTES + sl * SLAB, &kmap, sl * 64, kv_c1, kv_c2 + j * BN, bar(B_KFULL + st));
+        if (j >= KV_STAGES) wait_or_abort(bar(B_VEMPTY + st), ph ^ 1u, abort_flag);
+        mbar_expect_tx(bar(B_VFULL + st), TILE_BYTES);
+#pragma unroll
+        for (int sl = 0; sl < NSLAB; ++sl)
+          tma_load_3d(sV + st * TILE_BYTES + sl * SLAB, &vmap, sl * 64, kv_c1, kv_c2 + j * BN, bar(B_VFULL + st));
+      }
+    }
+  } else if (warp == 1) {
+    // ============================ MMA issuer ========================================
+    if (lane == 0) {
+      auto issue_qk = [&](int t, int st) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (uint32_t)(ks >> 2) * SLAB + (uint32_t)(ks & 3) * 32u;
+          const uint64_t a = smem_desc(sQ + t * TILE_BYTES + off, 16, 1024);
+          const uint64_t b = smem_desc(sK + st * TILE_BYTES + off, 16, 1024);
+          tc_mma_ss(tmem_base + (uint32_t)t * 128u, a, b, IDESC_QK, ks > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int t, int st, uint32_t acc) {
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          const uint64_t b = smem_desc(sV + st * TILE_BYTES + (uint32_t)ks * 2048u, SLAB, 1024);
+          tc_mma_ts(tmem_base + O_COL0 + (uint32_t)t * D, tmem_base + (uint32_t)t * 128u + (uint32_t)ks * 8u, b,
+                    IDESC_PV, (acc | (ks > 0 ? 1u : 0u)));
+        }
+      };
+      wait_or_abort(bar(B_QFULL), 0, abort_flag);
+      wait_or_abort(bar(B_KFULL + 0), 0, abort_flag);
+      tc_fence_after();
+      for (int t = 0; t < 2; ++t) {
+        if (n_kv[t] > 0) {
+          issue_qk(t, 0);
+          tc_commit(bar(B_SFULL + t));
+        }
+      }
+      tc_commit(bar(B_KEMPTY + 0));
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j % KV_STAGES;
+        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+        for (int t = 0; t < 2; ++t) {
+          if (j >= n_kv[t]) continue;
+          const bool last_user = (t == 1) || (j >= n_kv[1]);
+          wait_or_abort(bar(B_VFULL + st), ph, abort_flag);
+          wait_or_abort(bar(B_PFULL + t), (uint32_t)j & 1u, abort_flag);
+          tc_fence_after();
+          issue_pv(t, st, j > 0 ? 1u : 0u);
+          tc_commit(bar(B_OFULL + t));
+          if (last_user) tc_commit(bar(B_VEMPTY + st));
+          if (j + 1 < n_kv[t]) {
+            const int st1 = (j + 1) % KV_STAGES;
+            const uint32_t ph1 = (uint32_t)((j + 1) / KV_STAGES) & 1u;
+            const bool last_user1 = (t == 1) || (j + 1 >= n_kv[1]);
+            wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag);
+            tc_fence_after();
+            issue_qk(t, st1);
+            tc_commit(bar(B_SFULL + t));
+            if (last_user1) tc_commit(bar(B_KEMPTY + st1));
+          }
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ============================ softmax groups ====================================
+    const int t = (warp - 4) >> 2;
+    const int wq = warp & 3;                   // TMEM lane quadrant of this warp
+    const int row = wq * 32 + lane;            // row within the tile == TMEM lane
+    const int grow = row0[t] + row;            // row within the sequence
+    const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
+    const uint32_t tS = lane_base + (uint32_t)t * 128u;
+    const uint32_t tO = lane_base + O_COL0 + (uint32_t)t * D;
+    if (n_kv[t] > 0) {
+      float m = -INFINITY, l = 0.f;
+      for (int j = 0; j < n_kv[t]; ++j) {
+        wait_or_abort(bar(B_SFULL + t), (uint32_t)j & 1u, abort_flag);
+        tc_fence_after();
+        const int k0 = j * BN;
+        const bool need_mask = (k0 + BN > len) || (p.causal && (k0 + BN - 1 > row0[t]));
+        // ---- pass 1: row maximum ----
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; c += 2) {
+          float a[32], b[32];
+          tc_ld32(tS + c * 32, a);
+          tc_ld32(tS + (c + 1) * 32, b);
+          tc_wait_ld();
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int ka = k0 + c * 32 + i, kb = ka + 32;
+              if (ka >= len || (p.causal && ka > grow)) a[i] = -INFINITY;
+              if (kb >= len || (p.causal && kb > grow)) b[i] = -INFINITY;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(a[i], b[i]));
+        }
+        const float m_new = fmaxf(m, mx * p.scale_log2);
+        const bool grow_big = m_new > m + 8.f;   // also true for the first tile (m = -inf)
+        const float alpha = grow_big ? fast_exp2(m - m_new) : 1.f;
+        if (j > 0 && __any_sync(0xffffffffu, grow_big)) {
+          // O_t must hold the result of PV(t, j-1) before it is rescaled
+          wait_or_abort(bar(B_OFULL + t), (uint32_t)(j - 1) & 1u, abort_flag);
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            float o[32];
+            tc_ld32(tO + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tc_st32(tO + c * 32, o);
+          }
+          tc_wait_st();
+        }
+        if (grow_big) m = m_new;
+        l *= alpha;
+        // ---- pass 2: P = exp2(S * scale - m), written over the first 64 columns of S ----
+        float rsum = 0.f;
+        const float neg_m = (m == -INFINITY) ? 0.f : -m;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float a[32];
+          tc_ld32(tS + c * 32, a);
+          tc_wait_ld();
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int ka = k0 + c * 32 + i;
+              if (ka >= len || (p.causal && ka > grow)) a[i] = -INFINITY;
+            }
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = fast_exp2(fmaf(a[2 * i], p.scale_log2, neg_m));
+            const float p1 = fast_exp2(fmaf(a[2 * i + 1], p.scale_log2, neg_m));
+            rsum += p0 + p1;
+            pk[i] = pack_half2(p0, p1);
+          }
+          tc_st16(tS + c * 16, pk);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(B_PFULL + t));
+        l += rsum;
+      }
+      // ---- epilogue: O / l -> fp16 -> global ----
+      wait_or_abort(bar(B_OFULL + t), (uint32_t)(n_kv[t] - 1) & 1u, abort_flag);
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __half* orow;
+      if (p.dense) orow = p.out + (long long)seq * p.o_batch_stride + (long long)head[t] * p.o_head_stride +
+                          (long long)grow * p.o_tok_stride;
+      else orow = p.out + (tok0 + grow) * p.o_tok_stride + (long long)head[t] * p.o_head_stride;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        tc_ld32(tO + c * 32, o);
+        tc_wait_ld();
+        if (grow < len) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_half2(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
+            w.y = pack_half2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+            w.z = pack_half2(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+            w.w = pack_half2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
+          }
+        }
+      }
+    }
+  }
+
+  // ---- tear-down ------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// 3-D map {D, heads, rows} with a {64, 1, 128} box and 128-byte swizzle.
+bool make_map3(EncodeTiledFn enc, CUtensorMap* map, const void* base, int D, long long heads, long long rows,
+               long long head_stride_elems, long long row_stride_elems) {
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)heads, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)head_stride_elems * 2, (cuuint64_t)row_stride_elems * 2};
+  cuuint32_t box[3] = {64, 1, 128};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D>
+cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t stream) {
+  EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(encode_fn);
+  const bool dense = pp.cu_seqlens == nullptr;
+  CUtensorMap qmap, kmap, vmap;
+  bool ok;
+  if (dense) {
+    const long long qrows = (long long)pp.batch * pp.H_Q * pp.N, krows = (long long)pp.batch * pp.H_KV * pp.N;
+    ok = make_map3(enc, &qmap, pp.q, D, 1, qrows, D, D) && make_map3(enc, &kmap, pp.k, D, 1, krows, D, D) &&
+         make_map3(enc, &vmap, pp.v, D, 1, krows, D, D);
+  } else {
+    ok = make_map3(enc, &qmap, pp.q, D, pp.H_Q, pp.total, D, (long long)pp.H_Q * D) &&
+         make_map3(enc, &kmap, pp.k, D, pp.H_KV, pp.total, D, (long long)pp.H_KV * D) &&
+         make_map3(enc, &vmap, pp.v, D, pp.H_KV, pp.total, D, (long long)pp.H_KV * D);
+  }
+  if (!ok) return cudaErrorInvalidValue;
+  Tc5Params p;
+  p.out = pp.out;
+  p.cu_seqlens = pp.cu_seqlens;
+  p.batch = pp.batch; p.H_Q = pp.H_Q; p.H_KV = pp.H_KV; p.N = pp.N; p.max_seqlen = pp.max_seqlen;
+  p.total = pp.total;
+  p.o_batch_stride = pp.q_batch_stride; p.o_head_stride = pp.q_head_stride; p.o_tok_stride = pp.q_tok_stride;
+  p.causal = pp.causal;
+  p.pair_heads = ((pp.H_Q / pp.H_KV) % 2 == 0) ? 1 : 0;
+  p.dense = dense ? 1 : 0;
+  p.scale_log2 = pp.scale_log2;
+  constexpr int KV_STAGES = (D == 128) ? 2 : 4;
+  constexpr size_t TILE = (size_t)(D / 64) * 128 * 128;
+  const size_t smem = 1024 + (2 + 2 * KV_STAGES) * TILE + 64 * 8 + 16;
+  auto kern = prefill_tc5_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int max_len = dense ? pp.N : pp.max_seqlen;
+  dim3 grid;
+  if (p.pair_heads) grid = dim3((max_len + 127) / 128, pp.H_Q / 2, pp.batch);
+  else grid = dim3((max_len + 255) / 256, pp.H_Q, pp.batch);
+  kern<<<grid, 384, smem, stream>>>(qmap, kmap, vmap, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool prefill_tc5_supported(const PrefillParams& p, int D) {
+  if (D != 64 && D != 128) return false;
+  const long long qrows = p.cu_seqlens ? p.total : (long long)p.batch * p.H_Q * p.N;
+  if (qrows >= (1ll << 31)) return false;
+  return true;
+}
+
+cudaError_t launch_prefill_tc5(const PrefillParams& p, int D, void* encode_fn, cudaStream_t stream) {
+  if (D == 128) return launch_tc5_t<128>(p, encode_fn, stream);
+  if (D == 64) return launch_tc5_t<64>(p, encode_fn, stream);
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t prefill_status(int* host_out, cudaStream_t stream) {
+  cudaError_t e = cudaMemcpyFromSymbolAsync(host_out, g_prefill_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return e;
+  return cudaStreamSynchronize(stream);
+}
+
+cudaError_t prefill_status_clear(cudaStream_t stream) {
+  int zero = 0;
+  return cudaMemcpyToSymbolAsync(g_prefill_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+}
+
+}  // namespace fa

@@ -125,6 +125,21 @@ def check_async_errors(device=None) -> None:
             _lib.check(lib.fa_decode_status(_ptr(ws), ctypes.c_void_p(stream_int), ctypes.byref(st)))
 
 
+def set_prefill_impl(impl: int = 0) -> None:
+    """0 = automatic, 1 = mma.sync kernel, 2 = tcgen05 kernel (tests and measurements)."""
+    _lib.check(_lib.load().fa_prefill_set_impl(int(impl)))
+
+
+def check_prefill_errors(device=None, clear: bool = True) -> None:
+    """Synchronise and raise RuntimeError if a prefill kernel on `device` recorded a bounded-wait timeout."""
+    lib = _lib.load()
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    with torch.cuda.device(dev):
+        st = ctypes.c_int(0)
+        s = torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(lib.fa_prefill_status(ctypes.c_void_p(s), ctypes.byref(st), 1 if clear else 0))
+
+
 def set_decode_tuning(warps: int = 0, stages: int = 0, ctas_per_sm: int = 0) -> None:
     _lib.check(_lib.load().fa_decode_set_tuning(int(warps), int(stages), int(ctas_per_sm)))
 

@@ -196,6 +196,16 @@ int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out
                           const int32_t* cu_seqlens, int batch, int64_t total,
                           int H_Q, int H_KV, int D, int max_seqlen, int causal, void* stream);
 
+/* Kernel choice for the prefill entry points: 0 = automatic (tcgen05 kernel for
+ * D = 64/128, mma.sync kernel otherwise), 1 = always the mma.sync kernel, 2 = require
+ * the tcgen05 kernel.  Process-wide; meant for tests and measurements. */
+int fa_prefill_set_impl(int impl);
+
+/* Read back (synchronously on `stream`) the sticky status word of the prefill kernels
+ * on the current device: 0 = clean, bit 0 = a bounded wait ran out (results of that
+ * launch are undefined, no fault is raised).  `clear` != 0 resets it afterwards. */
+int fa_prefill_status(void* stream, int* host_status_out, int clear);
+
 #ifdef __cplusplus
 }
 #endif

@@ -11,6 +11,18 @@ TOL = 2e-3
 TOL_FP16_FIXTURE = 4e-3
 
 
+@pytest.fixture(autouse=True, params=["auto", "mma"])
+def prefill_impl(request):
+    """Every prefill test runs twice: with the automatic kernel choice (tcgen05 kernel for
+    D = 64/128) and with the mma.sync kernel forced."""
+    import flash_attn_v100_b200 as pkg
+    pkg.set_prefill_impl(0 if request.param == "auto" else 1)
+    yield request.param
+    torch.cuda.synchronize()
+    pkg.set_prefill_impl(0)
+    pkg.check_prefill_errors()
+
+
 def _err(a, b):
     return (a.detach().float().cpu() - torch.as_tensor(np.asarray(b)).float()).abs().max().item()
 
