@@ -391,8 +391,9 @@ int fa_paged_decode_gqa_f16_static_scratch(const void* q, const void* k_cache, c
 static int g_prefill_impl = 0;  // 0 auto, 1 mma.sync kernel, 2 tcgen05 kernel
 
 int fa_prefill_set_impl(int impl) {
-  FA_REQUIRE(impl >= 0 && impl <= 2, "impl must be 0 (auto), 1 (mma.sync) or 2 (tcgen05)");
-  g_prefill_impl = impl;
+  FA_REQUIRE(impl >= 0 && impl <= 3, "impl must be 0 (auto), 1 (mma.sync), 2 (tcgen05) or 3 (tcgen05, half of exp2 as FMA polynomial)");
+  fa::prefill_tc5_set_poly(impl == 3);
+  g_prefill_impl = impl == 3 ? 0 : impl;  // 3: automatic choice, polynomial variant when the tcgen05 kernel runs
   return FA_OK;
 }
 

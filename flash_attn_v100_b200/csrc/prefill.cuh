@@ -29,6 +29,7 @@ cudaError_t launch_prefill_mma(const PrefillParams& p, int D, cudaStream_t strea
 // tcgen05 / TMEM kernel (D = 64 or 128).  `encode_fn` is cuTensorMapEncodeTiled.
 bool prefill_tc5_supported(const PrefillParams& p, int D);
 cudaError_t launch_prefill_tc5(const PrefillParams& p, int D, void* encode_fn, cudaStream_t stream);
+void prefill_tc5_set_poly(bool on);
 cudaError_t prefill_status(int* host_out, cudaStream_t stream);
 cudaError_t prefill_status_clear(cudaStream_t stream);
 

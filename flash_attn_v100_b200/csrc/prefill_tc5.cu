@@ -9,8 +9,9 @@
 //   - "row pair" mode: two consecutive 128-row blocks of one query head.
 // Warp roles (12 warps):
 //   warp 0      TMA producer: Q once, then K_j / V_j tiles (128 keys) through a ring
-//   warp 1      MMA issuer (one lane): S_t = Q_t K_j^T and O_t += P_t V_j with tcgen05.mma,
-//               accumulators in tensor memory; completion signalled by tcgen05.commit
+//   warps 1, 3  MMA issuers (one lane each, warp 1 for tile 0 and warp 3 for tile 1):
+//               S_t = Q_t K_j^T and O_t += P_t V_j with tcgen05.mma, accumulators in tensor
+//               memory; completion signalled by tcgen05.commit; a token alternates the two
 //   warp 2      tensor-memory allocation / release
 //   warps 4-7   softmax of tile 0 (thread = one query row = one TMEM lane)
 //   warps 8-11  softmax of tile 1
@@ -32,6 +33,17 @@ namespace fa {
 
 __device__ int g_prefill_status = 0;
 
+#ifdef FA_TC5_TRACE
+// Debug build only: clock64() timeline of one CTA (events per role, KV step and phase).
+__device__ long long g_tc5_trace[8 * 64 * 8];
+#define TC5_TRACE(role, step, ev)                                                     \
+  do {                                                                                \
+    if (trace_on && (step) < 64) g_tc5_trace[((role) * 64 + (step)) * 8 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define TC5_TRACE(role, step, ev) do { } while (0)
+#endif
+
 namespace {
 
 constexpr uint32_t kTc5MaxPolls = 1u << 21;
@@ -49,6 +61,7 @@ struct Tc5Params {
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;  // cheap probe: the phase is usually complete already
   for (uint32_t i = 0; i < kTc5MaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *abort_flag) return false;
@@ -131,6 +144,41 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16])
       : "memory");
 }
 
+// Packed fp32x2 arithmetic (one issue slot for two lanes of work).
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  uint64_t ra = *reinterpret_cast<uint64_t*>(&a), rb = *reinterpret_cast<uint64_t*>(&b),
+           rc = *reinterpret_cast<uint64_t*>(&c), rd;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  return *reinterpret_cast<float2*>(&rd);
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  uint64_t ra = *reinterpret_cast<uint64_t*>(&a), rb = *reinterpret_cast<uint64_t*>(&b), rd;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  return *reinterpret_cast<float2*>(&rd);
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for x <= ~8 on the FMA/ALU pipes (keeps the MUFU free for the other half of the row):
+// round-to-nearest split x = n + f with the 1.5*2^23 trick, degree-3 minimax polynomial for 2^f on
+// [-0.5, 0.5] (relative error 7.7e-5, below fp16 resolution), exponent added through the integer bits.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float kMagic = 12582912.f;
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 t = fadd2(x, make_float2(kMagic, kMagic));
+  const float2 n = fadd2(t, make_float2(-kMagic, -kMagic));
+  const float2 f = fadd2(x, make_float2(-n.x, -n.y));
+  float2 r = ffma2(make_float2(0.05508868f, 0.05508868f), f, make_float2(0.24260405f, 0.24260405f));
+  r = ffma2(r, f, make_float2(0.69327623f, 0.69327623f));
+  r = ffma2(r, f, make_float2(0.99992895f, 0.99992895f));
+  r.x = __int_as_float(__float_as_int(r.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
+
 // Shared-memory matrix descriptor for 128-byte-swizzled tiles made of 128-byte rows.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t d = 0;
@@ -142,7 +190,7 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
-template <int D>
+template <int D, bool POLY>
 __global__ void __launch_bounds__(384, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                    const __grid_constant__ CUtensorMap vmap, const Tc5Params p) {
@@ -165,23 +213,28 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * KV_STAGES) * TILE_BYTES);
   // barrier indices
   constexpr int B_QFULL = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + KV_STAGES, B_VFULL = B_KEMPTY + KV_STAGES,
-                B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES, B_PFULL = B_SFULL + 2,
-                B_OFULL = B_PFULL + 2, B_COUNT = B_OFULL + 2;
+                B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES, B_PLO = B_SFULL + 2,
+                B_PHI = B_PLO + 2, B_OFULL = B_PHI + 2, B_TOKEN = B_OFULL + 2, B_COUNT = B_TOKEN + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   auto bar = [&](int i) -> uint32_t { return smem_u32(bars + i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef FA_TC5_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 1 && blockIdx.z == 2 && lane == 0;
+#endif
 
   // ---- which tiles ----------------------------------------------------------------
-  const int rb = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal blocks first
-  const int seq = blockIdx.z;
+  // the row block is the slowest grid dimension and runs backwards, so the CTAs with the most
+  // KV tiles (late causal blocks of the long sequences) are scheduled first across the whole grid
+  const int rb = gridDim.z - 1 - blockIdx.z;
+  const int seq = blockIdx.y;
   int head[2], row0[2];
   if (p.pair_heads) {
-    head[0] = 2 * blockIdx.y; head[1] = head[0] + 1;
+    head[0] = 2 * blockIdx.x; head[1] = head[0] + 1;
     row0[0] = row0[1] = rb * BM;
   } else {
-    head[0] = head[1] = blockIdx.y;
+    head[0] = head[1] = blockIdx.x;
     row0[0] = rb * 2 * BM; row0[1] = row0[0] + BM;
   }
   const int h_kv = head[0] / (p.H_Q / p.H_KV);
@@ -224,14 +277,16 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     mbar_init(bar(B_QFULL), 1);
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(bar(B_KFULL + s), 1);
-      mbar_init(bar(B_KEMPTY + s), 1);
+      mbar_init(bar(B_KEMPTY + s), n_kv[1] > 0 ? 2 : 1);
       mbar_init(bar(B_VFULL + s), 1);
-      mbar_init(bar(B_VEMPTY + s), 1);
+      mbar_init(bar(B_VEMPTY + s), n_kv[1] > 0 ? 2 : 1);
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar(B_SFULL + t), 1);
-      mbar_init(bar(B_PFULL + t), 128);
+      mbar_init(bar(B_PLO + t), 128);
+      mbar_init(bar(B_PHI + t), 128);
       mbar_init(bar(B_OFULL + t), 1);
+      mbar_init(bar(B_TOKEN + t), 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -251,7 +306,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // warps 0-3 (copy / MMA issue / allocation) need few registers; they hand the rest to the softmax groups
   if (warp == 0) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     // ============================ TMA producer ======================================
     if (lane == 0) {
       const int n_act = n_kv[1] > 0 ? 2 : 1;
@@ -263,74 +320,116 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       for (int j = 0; j < n_max; ++j) {
         const int st = j % KV_STAGES;
         const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+        TC5_TRACE(3, j, 0);
         if (j >= KV_STAGES) wait_or_abort(bar(B_KEMPTY + st), ph ^ 1u, abort_flag);
+        TC5_TRACE(3, j, 1);
         mbar_expect_tx(bar(B_KFULL + st), TILE_BYTES);
 #pragma unroll
         for (int sl = 0; sl < NSLAB; ++sl)
           tma_load_3d(sK + st * TILE_BYTES + sl * SLAB, &kmap, sl * 64, kv_c1, kv_c2 + j * BN, bar(B_KFULL + st));
         if (j >= KV_STAGES) wait_or_abort(bar(B_VEMPTY + st), ph ^ 1u, abort_flag);
+        TC5_TRACE(3, j, 2);
         mbar_expect_tx(bar(B_VFULL + st), TILE_BYTES);
 #pragma unroll
         for (int sl = 0; sl < NSLAB; ++sl)
           tma_load_3d(sV + st * TILE_BYTES + sl * SLAB, &vmap, sl * 64, kv_c1, kv_c2 + j * BN, bar(B_VFULL + st));
       }
     }
-  } else if (warp == 1) {
-    // ============================ MMA issuer ========================================
-    if (lane == 0) {
-      auto issue_qk = [&](int t, int st) {
+  } else if (warp == 1 || warp == 3) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    // ============================ MMA issuers =======================================
+    // One issuing lane per query tile (warp 1: tile 0, warp 3: tile 1).  A token passed
+    // between the two lanes keeps the issue order  QK(0,0) QK(1,0) | PV(0,j) QK(0,j+1) |
+    // PV(1,j) QK(1,j+1) | ...  so the tiles stay half a period apart (one tile's softmax
+    // overlaps the other tile's MMAs) while each lane's barrier waits, fences and commits
+    // overlap the other lane's MMAs.
+    const int t = warp == 1 ? 0 : 1;
+    if (lane == 0 && n_kv[t] > 0) {
+      const bool other_active = n_kv[1] > 0;     // tile 0 is always active here
+      constexpr uint32_t TILE16 = TILE_BYTES >> 4;
+      const uint64_t qd = smem_desc(sQ + (uint32_t)t * TILE_BYTES, 16, 1024);
+      const uint64_t kd0 = smem_desc(sK, 16, 1024);
+      const uint64_t vd0 = smem_desc(sV, SLAB, 1024);
+      const uint32_t dS = tmem_base + (uint32_t)t * 128u;
+      const uint32_t dO = tmem_base + O_COL0 + (uint32_t)t * D;
+      auto issue_qk = [&](int st) {
+        const uint64_t b0 = kd0 + (uint64_t)((uint32_t)st * TILE16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (uint32_t)(ks >> 2) * SLAB + (uint32_t)(ks & 3) * 32u;
-          const uint64_t a = smem_desc(sQ + t * TILE_BYTES + off, 16, 1024);
-          const uint64_t b = smem_desc(sK + st * TILE_BYTES + off, 16, 1024);
-          tc_mma_ss(tmem_base + (uint32_t)t * 128u, a, b, IDESC_QK, ks > 0 ? 1u : 0u);
+          constexpr uint32_t kSlab16 = SLAB >> 4;
+          const uint32_t off = (uint32_t)(ks >> 2) * kSlab16 + (uint32_t)(ks & 3) * 2u;
+          tc_mma_ss(dS, qd + off, b0 + off, IDESC_QK, ks > 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int t, int st, uint32_t acc) {
+      auto issue_pv = [&](int st, uint32_t acc, int half) {
+        const uint64_t b0 = vd0 + (uint64_t)((uint32_t)st * TILE16);
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          const uint64_t b = smem_desc(sV + st * TILE_BYTES + (uint32_t)ks * 2048u, SLAB, 1024);
-          tc_mma_ts(tmem_base + O_COL0 + (uint32_t)t * D, tmem_base + (uint32_t)t * 128u + (uint32_t)ks * 8u, b,
-                    IDESC_PV, (acc | (ks > 0 ? 1u : 0u)));
+        for (int ks = half * (BN / 32); ks < (half + 1) * (BN / 32); ++ks) {
+          tc_mma_ts(dO, dS + (uint32_t)ks * 8u, b0 + (uint32_t)ks * 128u, IDESC_PV, (acc | (ks > 0 ? 1u : 0u)));
         }
+      };
+      // token protocol: block b of tile 0 precedes block b of tile 1, which precedes block b+1 of tile 0
+      uint32_t tok_waits = 0;   // completed waits on my token barrier
+      auto take_token = [&]() {
+        if (!other_active) return;
+        wait_or_abort(bar(B_TOKEN + t), tok_waits & 1u, abort_flag);
+        ++tok_waits;
+      };
+      auto pass_token = [&]() {
+        if (other_active) mbar_arrive(bar(B_TOKEN + (t ^ 1)));
       };
       wait_or_abort(bar(B_QFULL), 0, abort_flag);
       wait_or_abort(bar(B_KFULL + 0), 0, abort_flag);
       tc_fence_after();
-      for (int t = 0; t < 2; ++t) {
-        if (n_kv[t] > 0) {
-          issue_qk(t, 0);
-          tc_commit(bar(B_SFULL + t));
-        }
-      }
+      if (t == 1) take_token();
+      issue_qk(0);
+      pass_token();
+      tc_commit(bar(B_SFULL + t));
       tc_commit(bar(B_KEMPTY + 0));
-      for (int j = 0; j < n_max; ++j) {
+      for (int j = 0; j < n_kv[t]; ++j) {
         const int st = j % KV_STAGES;
         const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-        for (int t = 0; t < 2; ++t) {
-          if (j >= n_kv[t]) continue;
-          const bool last_user = (t == 1) || (j >= n_kv[1]);
-          wait_or_abort(bar(B_VFULL + st), ph, abort_flag);
-          wait_or_abort(bar(B_PFULL + t), (uint32_t)j & 1u, abort_flag);
-          tc_fence_after();
-          issue_pv(t, st, j > 0 ? 1u : 0u);
-          tc_commit(bar(B_OFULL + t));
-          if (last_user) tc_commit(bar(B_VEMPTY + st));
-          if (j + 1 < n_kv[t]) {
-            const int st1 = (j + 1) % KV_STAGES;
-            const uint32_t ph1 = (uint32_t)((j + 1) / KV_STAGES) & 1u;
-            const bool last_user1 = (t == 1) || (j + 1 >= n_kv[1]);
-            wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag);
-            tc_fence_after();
-            issue_qk(t, st1);
-            tc_commit(bar(B_SFULL + t));
-            if (last_user1) tc_commit(bar(B_KEMPTY + st1));
-          }
+        const bool more = j + 1 < n_kv[t];
+        const int st1 = (j + 1) % KV_STAGES;
+        const uint32_t ph1 = (uint32_t)((j + 1) / KV_STAGES) & 1u;
+        TC5_TRACE(4 + 2 * t, j, 0);
+        wait_or_abort(bar(B_VFULL + st), ph, abort_flag);
+        if (more) wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag);
+        wait_or_abort(bar(B_PLO + t), (uint32_t)j & 1u, abort_flag);
+        TC5_TRACE(4 + 2 * t, j, 1);
+        // tile 1's block j follows tile 0's block j; tile 0's block j follows tile 1's block j-1,
+        // which exists unless tile 1 has already run out of KV tiles
+        if (t == 1 || j <= n_kv[1]) take_token();
+        TC5_TRACE(4 + 2 * t, j, 2);
+        tc_fence_after();
+        issue_pv(st, j > 0 ? 1u : 0u, 0);
+        TC5_TRACE(4 + 2 * t, j, 3);
+        wait_or_abort(bar(B_PHI + t), (uint32_t)j & 1u, abort_flag);
+        tc_fence_after();
+        TC5_TRACE(4 + 2 * t, j, 4);
+        issue_pv(st, 1u, 1);
+        if (more) issue_qk(st1);
+        TC5_TRACE(4 + 2 * t, j, 5);
+        pass_token();
+        tc_commit(bar(B_OFULL + t));
+        tc_commit(bar(B_VEMPTY + st));
+        if (more) {
+          tc_commit(bar(B_SFULL + t));
+          tc_commit(bar(B_KEMPTY + st1));
         }
+        TC5_TRACE(4 + 2 * t, j, 6);
+      }
+      // tile 1 may own one more block than tile 0 (causal, row-pair mode): hand it the token it waits
+      // for, but only after it has taken the previous one (one arrival per barrier phase)
+      if (t == 0 && n_kv[1] > n_kv[0]) {
+        take_token();
+        pass_token();
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp == 2) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ============================ softmax groups ====================================
     const int t = (warp - 4) >> 2;
     const int wq = warp & 3;                   // TMEM lane quadrant of this warp
@@ -342,29 +441,41 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     if (n_kv[t] > 0) {
       float m = -INFINITY, l = 0.f;
       for (int j = 0; j < n_kv[t]; ++j) {
+        TC5_TRACE(t, j, 0);
         wait_or_abort(bar(B_SFULL + t), (uint32_t)j & 1u, abort_flag);
+        TC5_TRACE(t, j, 1);
         tc_fence_after();
         const int k0 = j * BN;
         const bool need_mask = (k0 + BN > len) || (p.causal && (k0 + BN - 1 > row0[t]));
-        // ---- pass 1: row maximum ----
-        float mx = -INFINITY;
+        // ---- the whole score row of this thread: 128 fp32 values, one round trip ----
+        float sv[4][32];
+        tc_ld32(tS, sv[0]);
+        tc_ld32(tS + 32, sv[1]);
+        tc_ld32(tS + 64, sv[2]);
+        tc_ld32(tS + 96, sv[3]);
+        tc_wait_ld();
+        TC5_TRACE(t, j, 2);
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; c += 2) {
-          float a[32], b[32];
-          tc_ld32(tS + c * 32, a);
-          tc_ld32(tS + (c + 1) * 32, b);
-          tc_wait_ld();
-          if (need_mask) {
+          for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const int ka = k0 + c * 32 + i, kb = ka + 32;
-              if (ka >= len || (p.causal && ka > grow)) a[i] = -INFINITY;
-              if (kb >= len || (p.causal && kb > grow)) b[i] = -INFINITY;
+              const int kk = k0 + c * 32 + i;
+              if (kk >= len || (p.causal && kk > grow)) sv[c][i] = -INFINITY;
             }
-          }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(a[i], b[i]));
         }
+        float mxc[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float a0 = fmaxf(sv[c][0], sv[c][1]), a1 = fmaxf(sv[c][2], sv[c][3]);
+#pragma unroll
+          for (int i = 4; i < 32; i += 4) {
+            a0 = fmax3(a0, sv[c][i], sv[c][i + 1]);
+            a1 = fmax3(a1, sv[c][i + 2], sv[c][i + 3]);
+          }
+          mxc[c] = fmaxf(a0, a1);
+        }
+        const float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
         const float m_new = fmaxf(m, mx * p.scale_log2);
         const bool grow_big = m_new > m + 8.f;   // also true for the first tile (m = -inf)
         const float alpha = grow_big ? fast_exp2(m - m_new) : 1.f;
@@ -385,35 +496,38 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         }
         if (grow_big) m = m_new;
         l *= alpha;
-        // ---- pass 2: P = exp2(S * scale - m), written over the first 64 columns of S ----
-        float rsum = 0.f;
+        TC5_TRACE(t, j, 3);
+        // ---- P = exp2(S * scale - m), fp16, written over the first 64 columns of S ----
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
+        float2 rs2[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          float a[32];
-          tc_ld32(tS + c * 32, a);
-          tc_wait_ld();
-          if (need_mask) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int ka = k0 + c * 32 + i;
-              if (ka >= len || (p.causal && ka > grow)) a[i] = -INFINITY;
-            }
-          }
+          rs2[c] = make_float2(0.f, 0.f);
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(fmaf(a[2 * i], p.scale_log2, neg_m));
-            const float p1 = fast_exp2(fmaf(a[2 * i + 1], p.scale_log2, neg_m));
-            rsum += p0 + p1;
-            pk[i] = pack_half2(p0, p1);
+            const float2 x = ffma2(make_float2(sv[c][2 * i], sv[c][2 * i + 1]), sc2, nm2);
+            float2 e;
+            if (POLY && (i & 1)) {
+              e = exp2_poly2(x);
+            } else {
+              e.x = fast_exp2(x.x);
+              e.y = fast_exp2(x.y);
+            }
+            rs2[c] = fadd2(rs2[c], e);
+            pk[i] = pack_half2(e.x, e.y);
           }
           tc_st16(tS + c * 16, pk);
+          if (c == 1 || c == 3) {
+            // keys [0,64) / [64,128) of P are in tensor memory: let the PV MMA start on that half
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar((c == 1 ? B_PLO : B_PHI) + t));
+            TC5_TRACE(t, j, c == 1 ? 4 : 5);
+          }
         }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar(B_PFULL + t));
-        l += rsum;
+        l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
       }
       // ---- epilogue: O / l -> fp16 -> global ----
       wait_or_abort(bar(B_OFULL + t), (uint32_t)(n_kv[t] - 1) & 1u, abort_flag);
@@ -468,6 +582,8 @@ bool make_map3(EncodeTiledFn enc, CUtensorMap* map, const void* base, int D, lon
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool g_tc5_poly = false;  // true: every other pair of exp2 runs as a polynomial on the FMA pipes
+
 template <int D>
 cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t stream) {
   EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(encode_fn);
@@ -497,13 +613,13 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   constexpr int KV_STAGES = (D == 128) ? 2 : 4;
   constexpr size_t TILE = (size_t)(D / 64) * 128 * 128;
   const size_t smem = 1024 + (2 + 2 * KV_STAGES) * TILE + 64 * 8 + 16;
-  auto kern = prefill_tc5_kernel<D>;
+  auto kern = g_tc5_poly ? prefill_tc5_kernel<D, true> : prefill_tc5_kernel<D, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int max_len = dense ? pp.N : pp.max_seqlen;
   dim3 grid;
-  if (p.pair_heads) grid = dim3((max_len + 127) / 128, pp.H_Q / 2, pp.batch);
-  else grid = dim3((max_len + 255) / 256, pp.H_Q, pp.batch);
+  if (p.pair_heads) grid = dim3(pp.H_Q / 2, pp.batch, (max_len + 127) / 128);
+  else grid = dim3(pp.H_Q, pp.batch, (max_len + 255) / 256);
   kern<<<grid, 384, smem, stream>>>(qmap, kmap, vmap, p);
   return cudaGetLastError();
 }
@@ -522,6 +638,14 @@ cudaError_t launch_prefill_tc5(const PrefillParams& p, int D, void* encode_fn, c
   if (D == 64) return launch_tc5_t<64>(p, encode_fn, stream);
   return cudaErrorInvalidValue;
 }
+
+#ifdef FA_TC5_TRACE
+extern "C" int fa_debug_read_tc5_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_tc5_trace, sizeof(long long) * n);
+}
+#endif
+
+void prefill_tc5_set_poly(bool on) { g_tc5_poly = on; }
 
 cudaError_t prefill_status(int* host_out, cudaStream_t stream) {
   cudaError_t e = cudaMemcpyFromSymbolAsync(host_out, g_prefill_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);

@@ -198,7 +198,8 @@ int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out
 
 /* Kernel choice for the prefill entry points: 0 = automatic (tcgen05 kernel for
  * D = 64/128, mma.sync kernel otherwise), 1 = always the mma.sync kernel, 2 = require
- * the tcgen05 kernel.  Process-wide; meant for tests and measurements. */
+ * the tcgen05 kernel, 3 = tcgen05 kernel with every other pair of exp2 evaluated as a
+ * polynomial on the FMA pipes.  Process-wide; meant for tests and measurements. */
 int fa_prefill_set_impl(int impl);
 
 /* Read back (synchronously on `stream`) the sticky status word of the prefill kernels

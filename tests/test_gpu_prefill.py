@@ -11,12 +11,12 @@ TOL = 2e-3
 TOL_FP16_FIXTURE = 4e-3
 
 
-@pytest.fixture(autouse=True, params=["auto", "mma"])
+@pytest.fixture(autouse=True, params=["auto", "mma", "tc5_poly"])
 def prefill_impl(request):
-    """Every prefill test runs twice: with the automatic kernel choice (tcgen05 kernel for
-    D = 64/128) and with the mma.sync kernel forced."""
+    """Every prefill test runs with the automatic kernel choice (tcgen05 kernel for D = 64/128),
+    with the mma.sync kernel forced, and with the tcgen05 kernel's polynomial-exp2 variant."""
     import flash_attn_v100_b200 as pkg
-    pkg.set_prefill_impl(0 if request.param == "auto" else 1)
+    pkg.set_prefill_impl({"auto": 0, "mma": 1, "tc5_poly": 3}[request.param])
     yield request.param
     torch.cuda.synchronize()
     pkg.set_prefill_impl(0)
