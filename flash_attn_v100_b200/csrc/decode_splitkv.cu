@@ -30,6 +30,17 @@ namespace fa {
 
 namespace {
 
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  uint64_t ra = *reinterpret_cast<uint64_t*>(&a), rb = *reinterpret_cast<uint64_t*>(&b), rd;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  return *reinterpret_cast<float2*>(&rd);
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  uint64_t ra = *reinterpret_cast<uint64_t*>(&a), rb = *reinterpret_cast<uint64_t*>(&b), rd;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  return *reinterpret_cast<float2*>(&rd);
+}
+
 constexpr int kMaxSmemPrefix = 4096;  // B + 1 <= this: prefix sums are staged in shared memory
 
 __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
@@ -330,14 +341,41 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
         for (int j = 0; j < 2; ++j) si[j][0] = si[j][1] = si[j][2] = si[j][3] = 0;
         const uint8_t* kptr = my_stages + (size_t)st * (2 * PAGE_BYTES);
-        auto quant_k4 = [&](int row, int d, float ksr) -> uint32_t {
+        // Quantise four consecutive K values of one token: clamp(roundf(k / k_s), -127, 127) in IEEE
+        // fp32, bit for bit.  Fast path: multiply by the reciprocal and round with the 1.5*2^23
+        // trick.  For |t| < 127.5 the product differs from the correctly rounded quotient by < 2.3e-5,
+        // which changes the result only next to a rounding boundary (x.5); those values, exact ties
+        // (round-half-away differs from the trick's round-half-even) and values beyond the clamp
+        // range are flagged and redone exactly.  The fast path is branch-free so that the sixteen
+        // independent quantisations of a page interleave.
+        auto load_k4 = [&](int row, int d, float (&f)[4]) {
           const int chunk = d >> 3;  // 16-byte chunk within the row
           const uint8_t* src = kptr + (chunk >> 3) * SLAB_BYTES + row * 128 +
                                (((chunk & 7) ^ (row & 7)) << 4) + (d & 7) * 2;
           const uint2 raw2 = *reinterpret_cast<const uint2*>(src);
-          const __half2 h01 = *reinterpret_cast<const __half2*>(&raw2.x);
-          const __half2 h23 = *reinterpret_cast<const __half2*>(&raw2.y);
-          const float f[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
+          const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&raw2.x));
+          const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&raw2.y));
+          f[0] = f01.x; f[1] = f01.y; f[2] = f23.x; f[3] = f23.y;
+        };
+        auto quant_fast = [&](int row, int d, float rcp, bool& flagged) -> uint32_t {
+          float f[4];
+          load_k4(row, d, f);
+          const float2 t01 = fmul2(make_float2(f[0], f[1]), make_float2(rcp, rcp));
+          const float2 t23 = fmul2(make_float2(f[2], f[3]), make_float2(rcp, rcp));
+          const float2 mg = make_float2(12582912.f, 12582912.f), ng = make_float2(-12582912.f, -12582912.f);
+          const float2 y01 = fadd2(t01, mg), y23 = fadd2(t23, mg);
+          const float2 r01 = fadd2(y01, ng), r23 = fadd2(y23, ng);          // rint(t)
+          const float2 u01 = fadd2(t01, make_float2(-r01.x, -r01.y));
+          const float2 u23 = fadd2(t23, make_float2(-r23.x, -r23.y));
+          const float umax = fmaxf(fmaxf(fabsf(u01.x), fabsf(u01.y)), fmaxf(fabsf(u23.x), fabsf(u23.y)));
+          const float tmax = fmaxf(fmaxf(fabsf(t01.x), fabsf(t01.y)), fmaxf(fabsf(t23.x), fabsf(t23.y)));
+          flagged = !(umax <= 0.49997f) || !(tmax <= 127.4f);   // also catches NaN / Inf
+          return __byte_perm(__byte_perm(__float_as_uint(y01.x), __float_as_uint(y01.y), 0x0040),
+                             __byte_perm(__float_as_uint(y23.x), __float_as_uint(y23.y), 0x0040), 0x5410);
+        };
+        auto quant_exact = [&](int row, int d, float ksr) -> uint32_t {
+          float f[4];
+          load_k4(row, d, f);
           uint32_t packed = 0;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -347,17 +385,38 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           return packed;
         };
         const int c4 = (lane & 3) * 4;
+        uint32_t bq[2][D / 32][2];
+        float ksr[2];
+        uint32_t tie_mask = 0;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int row = 8 * j + g;  // token within the page owned by this lane in the B fragment
-          const float ksr = __shfl_sync(0xffffffffu, ks_cur, row);
+          ksr[j] = __shfl_sync(0xffffffffu, ks_cur, row);
+          const float rcp = __frcp_rn(ksr[j]);
 #pragma unroll
           for (int kk = 0; kk < D / 32; ++kk) {
-            const uint32_t b0 = quant_k4(row, kk * 32 + c4, ksr);
-            const uint32_t b1 = quant_k4(row, kk * 32 + 16 + c4, ksr);
-            mma_s8_16832(si[j], qa[kk], b0, b1);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              bool fl;
+              bq[j][kk][h] = quant_fast(row, kk * 32 + h * 16 + c4, rcp, fl);
+              tie_mask |= (fl ? 1u : 0u) << ((j * (D / 32) + kk) * 2 + h);
+            }
           }
         }
+        if (tie_mask != 0) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int kk = 0; kk < D / 32; ++kk)
+#pragma unroll
+              for (int h = 0; h < 2; ++h)
+                if ((tie_mask >> ((j * (D / 32) + kk) * 2 + h)) & 1u)
+                  bq[j][kk][h] = quant_exact(8 * j + g, kk * 32 + h * 16 + c4, ksr[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int kk = 0; kk < D / 32; ++kk) mma_s8_16832(si[j], qa[kk], bq[j][kk][0], bq[j][kk][1]);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const float ks_a = __shfl_sync(0xffffffffu, ks_cur, 8 * j + cq);
