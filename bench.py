@@ -147,7 +147,7 @@ class PagedDecode:
         pages = int(((self.seq_lens_h + 15) // 16).sum())
         self.alg_bytes = decode_algorithmic_bytes(tokens, pages, self.B, self.H_Q, self.H_KV, self.D)
         self.alg_flops = 4 * self.H_Q * self.D * tokens
-        self.launches_per_step = 3  # plan + split-KV main + combine
+        self.launches_per_step = 1  # one fused split-KV kernel (scan + work + merge)
 
     def config(self):
         return {"workload": "paged_gqa_decode B=64 H_Q=32 H_KV=8 D=128 page=16 seq_lens~U[512,8192] (BASELINE configs[1])",
@@ -203,7 +203,7 @@ class ContigDecode(PagedDecode):
         tokens = int((self.cache_lens_h + 1).sum())
         self.alg_bytes = decode_algorithmic_bytes(tokens, 0, self.B, self.H_Q, self.H_KV, self.D)
         self.alg_flops = 4 * self.H_Q * self.D * tokens
-        self.launches_per_step = 3
+        self.launches_per_step = 1
 
     def config(self):
         return {"workload": "continuous_batching_decode B=32 H_Q=32 H_KV=8 D=128 max_N=8192 cache_lens~U[511,8191]",
@@ -235,7 +235,7 @@ class Int8Decode:
         self.alg_bytes = (self.B * self.H_KV * self.N * self.D * 2 * 2 + self.ks.numel() * 4 +
                           2 * self.B * self.H_Q * self.D * 2 + self.qs.numel() * 4)
         self.alg_flops = 4 * self.H_Q * self.D * self.N * self.B
-        self.launches_per_step = 3
+        self.launches_per_step = 1
 
     def config(self):
         return {"workload": "int8_gqa_decode B=32 H_Q=32 H_KV=8 D=128 N=4096 cache_len=4095 (BASELINE configs[3])",
@@ -427,7 +427,7 @@ def run_b200(args):
                      "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": wl.alg_bytes, "algorithmic_flops_per_launch": wl.alg_flops,
                      "frac_of_nominal": achieved / (8000.0 if wl.bound == "hbm" else 2250.0),
-                     "duration": "CUDA-event time of one step (plan + split-KV + combine launches) on the launching stream"},
+                     "duration": "CUDA-event time of one step on the launching stream"},
         "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": wl.launches_per_step * args.steps,
         "clocks": clocks, "impl": "b200",
     }

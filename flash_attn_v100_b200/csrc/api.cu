@@ -9,6 +9,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "decode_splitkv.cuh"
@@ -129,6 +130,15 @@ fa::DecodeLaunchConfig pick_decode_config(int D, int slot_rows, int B, const Dev
   return c;
 }
 
+// Arrival counters in a workspace are tagged with the launch's epoch; epoch 0 is never used, so
+// zero-filled or stale memory reads as "no arrivals".
+unsigned int next_epoch() {
+  static std::atomic<unsigned int> e{0};
+  unsigned int v = ++e;
+  if (v == 0) v = ++e;
+  return v;
+}
+
 constexpr int kMaxDecodeCtas = 148 * 4 * 2;  // bound used to size workspaces on any sm_100 part
 
 struct DecodeCall {
@@ -172,7 +182,11 @@ int run_decode(const DecodeCall& c) {
   uint8_t* ws = static_cast<uint8_t*>(c.ws);
   p.status = reinterpret_cast<int32_t*>(ws + fa::kWsStatusOffset);
   p.prefix = reinterpret_cast<int32_t*>(ws + fa::kWsPrefixOffset);
-  p.partials = reinterpret_cast<float*>(ws + fa::kWsPrefixOffset + (((size_t)(c.B + 1) * 4 + 255) & ~(size_t)255));
+  const size_t prefix_bytes = (((size_t)(c.B + 1) * 4 + 255) & ~(size_t)255);
+  const size_t counter_bytes = (((size_t)c.B * c.H_KV * ((G + 15) / 16) * 8 + 255) & ~(size_t)255);
+  p.counters = reinterpret_cast<unsigned long long*>(ws + fa::kWsPrefixOffset + prefix_bytes);
+  p.partials = reinterpret_cast<float*>(ws + fa::kWsPrefixOffset + prefix_bytes + counter_bytes);
+  p.epoch = next_epoch();
   p.B = c.B; p.H_Q = c.H_Q; p.H_KV = c.H_KV; p.G = G;
   p.n_gblk = (G + 15) / 16;
   p.HV = c.H_KV * p.n_gblk;

@@ -10,8 +10,11 @@
 // (a fixed number of CTAs per SM) and CTA c owns the contiguous unit range
 // [c*per, (c+1)*per).  A CTA therefore reads an equal share of the KV bytes
 // whatever the length spread, and a segment is split across CTAs only at range
-// boundaries: at most two partial results per CTA.  A second small kernel
-// merges the partials of split segments by log-sum-exp.
+// boundaries: at most two partial results per CTA.  The CTA that delivers the
+// last partial of a split segment (an arrival counter per segment, tagged with
+// a per-launch epoch so that it never needs clearing) merges them by
+// log-sum-exp.  The page prefix sums that define the unit numbering are
+// recomputed by every CTA in shared memory: the whole decode is one launch.
 //
 // Data path.  Inside a CTA each warp streams its own pages (page i of a piece
 // goes to warp i mod W) through a private ring of shared-memory stages filled
@@ -130,8 +133,30 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
   const bool prefix_in_smem = (p.B + 1) <= kMaxSmemPrefix;
   const int* pre = prefix_in_smem ? s_prefix : p.prefix;
 
+  __shared__ int s_scan[8];
+  __shared__ int s_last_flag;
   if (prefix_in_smem) {
-    for (int i = threadIdx.x; i <= p.B; i += blockDim.x) s_prefix[i] = p.prefix[i];
+    // block-wide inclusive scan of pages per sequence: s_prefix[i + 1] = pages of sequences 0..i
+    const int nthr = blockDim.x;
+    const int chunk = (p.B + nthr - 1) / nthr;
+    const int i0 = threadIdx.x * chunk, i1 = (i0 + chunk < p.B) ? (i0 + chunk) : p.B;
+    int local = 0;
+    for (int i = i0; i < i1; ++i) {
+      local += (seq_len_of(p, i) + 15) >> 4;
+      s_prefix[i + 1] = local;
+    }
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_scan[warp] = incl;
+    __syncthreads();
+    int offset = incl - local;
+    for (int w = 0; w < warp; ++w) offset += s_scan[w];
+    for (int i = i0; i < i1; ++i) s_prefix[i + 1] += offset;
+    if (threadIdx.x == 0) s_prefix[0] = 0;
   }
   if (lane == 0) {
     for (int s = 0; s < S; ++s) mbar_init(smem_u32(bars + warp * S + s), 1);
@@ -144,6 +169,14 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
   }
   __syncthreads();
 
+  if (blockIdx.x == 0) {
+    // sequences with nothing to attend: zeros by definition (no unit ever touches their output)
+    for (int bb = 0; bb < p.B; ++bb) {
+      if (pre[bb + 1] != pre[bb]) continue;
+      __half* o = p.out + (size_t)bb * p.H_Q * D;
+      for (int e = threadIdx.x; e < p.H_Q * D; e += blockDim.x) o[e] = __float2half_rn(0.f);
+    }
+  }
   const long long T = (long long)p.HV * pre[p.B];
   long long per = (T + p.n_cta - 1) / p.n_cta;
   if (per < 1) per = 1;
@@ -563,56 +596,56 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         }
       }
     }
+    if (!complete) {
+      // The segment is shared with neighbouring CTAs.  Publish the partial, count the arrival;
+      // whoever arrives last merges all partials of the segment.
+      const long long seg_start = (long long)p.HV * pre[b] + (long long)hv * np;
+      const int first = (int)(seg_start / per), last = (int)((seg_start + np - 1) / per);
+      const unsigned int n_parts = (unsigned int)(last - first + 1);
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        unsigned long long* cnt = p.counters + ((size_t)b * p.HV + hv);
+        unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(cnt);
+        unsigned int arrivals;
+        while (true) {
+          const unsigned int have = ((unsigned int)(seen >> 32) == p.epoch) ? (unsigned int)seen : 0u;
+          arrivals = have + 1u;
+          const unsigned long long want = ((unsigned long long)p.epoch << 32) | arrivals;
+          const unsigned long long prev = atomicCAS(cnt, seen, want);
+          if (prev == seen) break;
+          seen = prev;
+        }
+        s_last_flag = (arrivals == n_parts) ? 1 : 0;
+      }
+      __syncthreads();
+      if (s_last_flag) {
+        __threadfence();
+        __half* outp = p.out + ((size_t)b * p.H_Q + head0) * D;
+        for (int e = threadIdx.x; e < Gb * D; e += blockDim.x) {
+          const int row = e / D, d = e - row * D;
+          float M = -INFINITY;
+          for (int c = first; c <= last; ++c) {
+            const int slot = ((long long)c * per >= seg_start) ? 0 : 1;
+            const float* part = p.partials + ((size_t)c * 2 + slot) * p.slot_rows * ROWLEN;
+            M = fmaxf(M, __ldcg(part + row * ROWLEN + D));
+          }
+          float L = 0.f, O = 0.f;
+          for (int c = first; c <= last; ++c) {
+            const int slot = ((long long)c * per >= seg_start) ? 0 : 1;
+            const float* part = p.partials + ((size_t)c * 2 + slot) * p.slot_rows * ROWLEN;
+            const float f = fast_exp2(__ldcg(part + row * ROWLEN + D) - M);
+            L += __ldcg(part + row * ROWLEN + D + 1) * f;
+            O += __ldcg(part + row * ROWLEN + d) * f;
+          }
+          outp[(size_t)row * D + d] = __float2half_rn(O / L);
+        }
+      }
+    }
     __syncthreads();
 
     u += cnt;
     ++piece;
-  }
-}
-
-// ---------------------------------------------------------------------------
-// combine: one CTA per segment; merges partials of segments split across CTAs,
-// writes zeros for empty sequences.
-// ---------------------------------------------------------------------------
-template <int D>
-__global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeParams p) {
-  constexpr int ROWLEN = D + 2;
-  const int seg = blockIdx.x;
-  const int b = seg / p.HV, hv = seg - b * p.HV;
-  const int h_kv = hv / p.n_gblk;
-  const int gb0 = (hv - h_kv * p.n_gblk) * 16;
-  const int Gb = (p.G - gb0) < 16 ? (p.G - gb0) : 16;
-  const int head0 = h_kv * p.G + gb0;
-  const int np = p.prefix[b + 1] - p.prefix[b];
-  __half* outp = p.out + ((size_t)b * p.H_Q + head0) * D;
-  if (np == 0) {
-    for (int e = threadIdx.x; e < Gb * D; e += blockDim.x) outp[e] = __float2half_rn(0.f);
-    return;
-  }
-  const long long T = (long long)p.HV * p.prefix[p.B];
-  long long per = (T + p.n_cta - 1) / p.n_cta;
-  if (per < 1) per = 1;
-  const long long seg_start = (long long)p.HV * p.prefix[b] + (long long)hv * np;
-  const long long seg_end = seg_start + np;
-  const int first = (int)(seg_start / per), last = (int)((seg_end - 1) / per);
-  if (first == last) return;  // written directly by the CTA that owned the whole segment
-  for (int e = threadIdx.x; e < Gb * D; e += blockDim.x) {
-    const int row = e / D, d = e - row * D;
-    float M = -INFINITY;
-    for (int c = first; c <= last; ++c) {
-      const int slot = ((long long)c * per >= seg_start) ? 0 : 1;
-      const float* part = p.partials + ((size_t)c * 2 + slot) * p.slot_rows * ROWLEN;
-      M = fmaxf(M, part[row * ROWLEN + D]);
-    }
-    float L = 0.f, O = 0.f;
-    for (int c = first; c <= last; ++c) {
-      const int slot = ((long long)c * per >= seg_start) ? 0 : 1;
-      const float* part = p.partials + ((size_t)c * 2 + slot) * p.slot_rows * ROWLEN;
-      const float f = fast_exp2(part[row * ROWLEN + D] - M);
-      L += part[row * ROWLEN + D + 1] * f;
-      O += part[row * ROWLEN + d] * f;
-    }
-    outp[(size_t)row * D + d] = __float2half_rn(O / L);
   }
 }
 
@@ -622,9 +655,8 @@ cudaError_t launch_t(const CUtensorMap& kmap, const CUtensorMap& vmap, const Dec
   auto kern = decode_splitkv_kernel<D, INT8>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
   if (e != cudaSuccess) return e;
-  decode_plan_kernel<<<1, 1024, 0, stream>>>(p);
+  if (p.B + 1 > kMaxSmemPrefix) decode_plan_kernel<<<1, 1024, 0, stream>>>(p);  // else scanned in-kernel
   kern<<<p.n_cta, warps * 32, smem_bytes, stream>>>(kmap, vmap, p);
-  decode_combine_kernel<D><<<p.B * p.HV, 128, 0, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -642,8 +674,10 @@ size_t decode_smem_bytes(int D, int warps, int stages, int slot_rows, int B) {
 size_t decode_workspace_bytes(int B, int H_Q, int H_KV, int D, int max_ctas) {
   const int G = H_Q / H_KV;
   const int slot_rows = G < 16 ? G : 16;
+  const int HV = H_KV * ((G + 15) / 16);
   size_t bytes = kWsPrefixOffset;
   bytes += ((size_t)(B + 1) * 4 + 255) & ~(size_t)255;
+  bytes += ((size_t)B * HV * 8 + 255) & ~(size_t)255;
   bytes += (size_t)max_ctas * 2 * slot_rows * (D + 2) * 4;
   return (bytes + 255) & ~(size_t)255;
 }

@@ -23,6 +23,8 @@ struct DecodeParams {
   int32_t* scores_out;         // int8 only, optional: [B, H_Q, N]
   int32_t* prefix;             // workspace: [B + 1] running page counts
   float* partials;             // workspace: [n_cta][2][slot_rows][D + 2]
+  unsigned long long* counters;  // workspace: [B * HV] (epoch << 32 | arrivals) per segment
+  unsigned int epoch;          // unique per launch; counters of other epochs read as zero
   int32_t* status;             // workspace: sticky status word
   int B, H_Q, H_KV, G;         // G = H_Q / H_KV
   int n_gblk;                  // ceil(G / 16): query-head blocks per KV head
@@ -46,7 +48,8 @@ size_t decode_workspace_bytes(int B, int H_Q, int H_KV, int D, int max_ctas);
 constexpr size_t kWsStatusOffset = 0;     // int32 status word (+ padding to 256 B)
 constexpr size_t kWsPrefixOffset = 256;   // int32 prefix[B + 1]
 
-// Launch plan + main + combine on `stream`.  kmap/vmap are 2-D tensor maps over
+// Launch the decode on `stream` (one kernel; a prefix-sum pre-pass only when B is too large for
+// the in-kernel scan).  kmap/vmap are 2-D tensor maps over
 // K and V seen as [rows, D] fp16 with a 64-column x 16-row box and 128-byte swizzle.
 cudaError_t launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p,
                           int D, bool int8, int warps, size_t smem_bytes, cudaStream_t stream);
