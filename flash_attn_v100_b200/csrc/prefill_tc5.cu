@@ -23,11 +23,18 @@
 // in fp16 range and compensated in the fp32 row sum).  Causal tiles above the diagonal are
 // skipped; only the diagonal tile and the ragged last tile are masked per element.
 //
+// The kernel is persistent: one CTA per SM claims work items (tile pairs, heaviest first) from
+// a global counter; barrier phases are running counters, so the copy and MMA lanes start the
+// next item while the softmax groups still write the previous item's output.
+//
 // Tensor-memory map (512 columns x 128 lanes): S_0 [0,128) S_1 [128,256) O_0 [256,256+D)
 // O_1 [256+D, 256+2D).  Every wait on an mbarrier is bounded; on a timeout the CTA sets an
 // abort flag, records a status bit and runs to completion without further waiting.
 #include "common.cuh"
 #include "prefill.cuh"
+
+#include <atomic>
+#include <mutex>
 
 namespace fa {
 
@@ -57,6 +64,8 @@ struct Tc5Params {
   int causal;
   int pair_heads;  // 1: two heads x same rows; 0: one head x two row blocks
   int dense;
+  int n_hg, n_rb;  // head groups and row blocks of the item grid (items = n_rb * batch * n_hg)
+  unsigned long long* item_counter;  // next unclaimed item of this launch (zeroed in-stream before it)
   float scale_log2;
 };
 
@@ -190,6 +199,61 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+// Work item = one pair of query tiles.  Items are numbered with the row block as the slowest
+// index, running backwards, so the items with the most KV tiles (late causal blocks of the long
+// sequences) come first.  CTAs claim items from a global counter (heaviest-first greedy
+// scheduling): the copy lane claims, skips empty items, and publishes the item number to the
+// other roles of its CTA through a small shared-memory queue.
+struct Tc5Item {
+  int head[2], row0[2], n_kv[2];
+  int q_c1[2], q_c2[2], kv_c1, kv_c2;
+  int seq, len, n_max;
+  long long tok0;
+};
+
+__device__ __forceinline__ bool tc5_decode_item(const Tc5Params& p, long long item, Tc5Item& it) {
+  constexpr int BM = 128, BN = 128;
+  const int hg = (int)(item % p.n_hg);
+  const long long r1 = item / p.n_hg;
+  const int seq = (int)(r1 % p.batch);
+  const int rb = p.n_rb - 1 - (int)(r1 / p.batch);
+  if (p.pair_heads) {
+    it.head[0] = 2 * hg; it.head[1] = it.head[0] + 1;
+    it.row0[0] = it.row0[1] = rb * BM;
+  } else {
+    it.head[0] = it.head[1] = hg;
+    it.row0[0] = rb * 2 * BM; it.row0[1] = it.row0[0] + BM;
+  }
+  const int h_kv = it.head[0] / (p.H_Q / p.H_KV);
+  int len;
+  if (p.cu_seqlens != nullptr) {
+    const int a = __ldg(p.cu_seqlens + seq), e = __ldg(p.cu_seqlens + seq + 1);
+    it.tok0 = a;
+    len = e - a;
+    if ((long long)e > p.total) len = (int)(p.total - a);
+  } else {
+    it.tok0 = 0;
+    len = p.N;
+  }
+  if (len > p.max_seqlen) len = p.max_seqlen;
+  it.len = len;
+  it.seq = seq;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    if (it.row0[t] >= len) it.n_kv[t] = 0;
+    else {
+      const int kv_end = p.causal ? ((it.row0[t] + BM) < len ? (it.row0[t] + BM) : len) : len;
+      it.n_kv[t] = (kv_end + BN - 1) / BN;
+    }
+    if (p.dense) { it.q_c1[t] = 0; it.q_c2[t] = (seq * p.H_Q + it.head[t]) * p.N + it.row0[t]; }
+    else { it.q_c1[t] = it.head[t]; it.q_c2[t] = (int)it.tok0 + it.row0[t]; }
+  }
+  if (p.dense) { it.kv_c1 = 0; it.kv_c2 = (seq * p.H_KV + h_kv) * p.N; }
+  else { it.kv_c1 = h_kv; it.kv_c2 = (int)it.tok0; }
+  it.n_max = it.n_kv[0] > it.n_kv[1] ? it.n_kv[0] : it.n_kv[1];
+  return it.n_kv[0] > 0;  // tile 0 holds the earlier rows: if it is empty the item is empty
+}
+
 template <int D, bool POLY>
 __global__ void __launch_bounds__(384, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
@@ -203,6 +267,8 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t O_COL0 = 256;
+  constexpr int kItemQ = 4;                  // depth of the per-CTA item queue
+  constexpr int kItemConsumers = 2 + 256;    // two MMA lanes + every softmax thread
 
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
@@ -212,81 +278,41 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   const uint32_t sV = sK + KV_STAGES * TILE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * KV_STAGES) * TILE_BYTES);
   // barrier indices
-  constexpr int B_QFULL = 0, B_KFULL = 1, B_KEMPTY = B_KFULL + KV_STAGES, B_VFULL = B_KEMPTY + KV_STAGES,
-                B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES, B_PLO = B_SFULL + 2,
-                B_PHI = B_PLO + 2, B_OFULL = B_PHI + 2, B_TOKEN = B_OFULL + 2, B_COUNT = B_TOKEN + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+  constexpr int B_QFULL = 0, B_QEMPTY = 2, B_KFULL = B_QEMPTY + 2, B_KEMPTY = B_KFULL + KV_STAGES,
+                B_VFULL = B_KEMPTY + KV_STAGES, B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES,
+                B_PLO = B_SFULL + 2, B_PHI = B_PLO + 2, B_OFULL = B_PHI + 2, B_TOKEN = B_OFULL + 2,
+                B_IFULL = B_TOKEN + 2, B_IEMPTY = B_IFULL + kItemQ, B_COUNT = B_IEMPTY + kItemQ;
+  volatile long long* item_slot = reinterpret_cast<volatile long long*>(bars + B_COUNT);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT + kItemQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   auto bar = [&](int i) -> uint32_t { return smem_u32(bars + i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long n_items = (long long)p.n_rb * p.batch * p.n_hg;
 #ifdef FA_TC5_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 1 && blockIdx.z == 2 && lane == 0;
+  const bool trace_on = false;
 #endif
 
-  // ---- which tiles ----------------------------------------------------------------
-  // the row block is the slowest grid dimension and runs backwards, so the CTAs with the most
-  // KV tiles (late causal blocks of the long sequences) are scheduled first across the whole grid
-  const int rb = gridDim.z - 1 - blockIdx.z;
-  const int seq = blockIdx.y;
-  int head[2], row0[2];
-  if (p.pair_heads) {
-    head[0] = 2 * blockIdx.x; head[1] = head[0] + 1;
-    row0[0] = row0[1] = rb * BM;
-  } else {
-    head[0] = head[1] = blockIdx.x;
-    row0[0] = rb * 2 * BM; row0[1] = row0[0] + BM;
-  }
-  const int h_kv = head[0] / (p.H_Q / p.H_KV);
-  long long tok0;
-  int len;
-  if (p.cu_seqlens != nullptr) {
-    const int a = __ldg(p.cu_seqlens + seq), e = __ldg(p.cu_seqlens + seq + 1);
-    tok0 = a;
-    len = e - a;
-    if ((long long)e > p.total) len = (int)(p.total - a);
-  } else {
-    tok0 = 0;
-    len = p.N;
-  }
-  if (len > p.max_seqlen) len = p.max_seqlen;
-  int n_kv[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    if (row0[t] >= len) n_kv[t] = 0;
-    else {
-      const int kv_end = p.causal ? ((row0[t] + BM) < len ? (row0[t] + BM) : len) : len;
-      n_kv[t] = (kv_end + BN - 1) / BN;
-    }
-  }
-  if (n_kv[0] == 0) return;  // tile 0 holds the earlier rows: nothing to do for this CTA
-  const int n_max = n_kv[0] > n_kv[1] ? n_kv[0] : n_kv[1];
-
-  // TMA coordinates (x, c1, c2)
-  int q_c1[2], q_c2[2], kv_c1, kv_c2;
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    if (p.dense) { q_c1[t] = 0; q_c2[t] = (seq * p.H_Q + head[t]) * p.N + row0[t]; }
-    else { q_c1[t] = head[t]; q_c2[t] = (int)tok0 + row0[t]; }
-  }
-  if (p.dense) { kv_c1 = 0; kv_c2 = (seq * p.H_KV + h_kv) * p.N; }
-  else { kv_c1 = h_kv; kv_c2 = (int)tok0; }
-
-  // ---- set-up ---------------------------------------------------------------------
+  // ---- set-up (once per CTA) --------------------------------------------------------
   if (threadIdx.x == 0) {
-    mbar_init(bar(B_QFULL), 1);
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(bar(B_KFULL + s), 1);
-      mbar_init(bar(B_KEMPTY + s), n_kv[1] > 0 ? 2 : 1);
+      mbar_init(bar(B_KEMPTY + s), 2);   // one arrival per issuing lane and use (see the MMA issuers)
       mbar_init(bar(B_VFULL + s), 1);
-      mbar_init(bar(B_VEMPTY + s), n_kv[1] > 0 ? 2 : 1);
+      mbar_init(bar(B_VEMPTY + s), 2);
     }
     for (int t = 0; t < 2; ++t) {
+      mbar_init(bar(B_QFULL + t), 1);
+      mbar_init(bar(B_QEMPTY + t), 1);
       mbar_init(bar(B_SFULL + t), 1);
       mbar_init(bar(B_PLO + t), 128);
       mbar_init(bar(B_PHI + t), 128);
       mbar_init(bar(B_OFULL + t), 1);
       mbar_init(bar(B_TOKEN + t), 1);
+    }
+    for (int i = 0; i < kItemQ; ++i) {
+      mbar_init(bar(B_IFULL + i), 1);
+      mbar_init(bar(B_IEMPTY + i), kItemConsumers);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -306,33 +332,59 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // warps 0-3 (copy / MMA issue / allocation) need few registers; they hand the rest to the softmax groups
+  // Running counters (identical in every role because every role walks the same item list):
+  //   kv_it   KV tiles of all items so far        -> ring stage and phase of K/V barriers
+  //   blk[t]  KV steps of tile t so far           -> phase of S / P / O barriers of tile t
+  //   q_cnt / q_used[t]  items in which tile t was active -> phase of the Q barriers of tile t
   if (warp == 0) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     // ============================ TMA producer ======================================
     if (lane == 0) {
-      const int n_act = n_kv[1] > 0 ? 2 : 1;
-      mbar_expect_tx(bar(B_QFULL), n_act * TILE_BYTES);
-      for (int t = 0; t < n_act; ++t)
+      uint32_t kv_it = 0;
+      uint32_t q_used[2] = {0, 0};   // how often each Q buffer has been filled
+      for (uint32_t ic = 0;; ++ic) {
+        if (*abort_flag) break;
+        // claim the next non-empty item and publish it (-1: no more items)
+        Tc5Item it;
+        long long item;
+        bool have = false;
+        while (true) {
+          item = (long long)atomicAdd(p.item_counter, 1ULL);
+          if (item >= n_items) break;
+          if (tc5_decode_item(p, item, it)) { have = true; break; }
+        }
+        const int slot = ic % kItemQ;
+        if (ic >= kItemQ) wait_or_abort(bar(B_IEMPTY + slot), ((ic / kItemQ) & 1u) ^ 1u, abort_flag);
+        item_slot[slot] = have ? item : -1;
+        mbar_arrive(bar(B_IFULL + slot));
+        if (!have) break;
+        const int n_act = it.n_kv[1] > 0 ? 2 : 1;
+        // Q buffers are free once the last QK of their previous item has completed
+        for (int t = 0; t < n_act; ++t) {
+          if (q_used[t] > 0) wait_or_abort(bar(B_QEMPTY + t), (q_used[t] - 1) & 1u, abort_flag);
+          mbar_expect_tx(bar(B_QFULL + t), TILE_BYTES);
 #pragma unroll
-        for (int sl = 0; sl < NSLAB; ++sl)
-          tma_load_3d(sQ + t * TILE_BYTES + sl * SLAB, &qmap, sl * 64, q_c1[t], q_c2[t], bar(B_QFULL));
-      for (int j = 0; j < n_max; ++j) {
-        const int st = j % KV_STAGES;
-        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-        TC5_TRACE(3, j, 0);
-        if (j >= KV_STAGES) wait_or_abort(bar(B_KEMPTY + st), ph ^ 1u, abort_flag);
-        TC5_TRACE(3, j, 1);
-        mbar_expect_tx(bar(B_KFULL + st), TILE_BYTES);
+          for (int sl = 0; sl < NSLAB; ++sl)
+            tma_load_3d(sQ + t * TILE_BYTES + sl * SLAB, &qmap, sl * 64, it.q_c1[t], it.q_c2[t],
+                        bar(B_QFULL + t));
+          ++q_used[t];
+        }
+        for (int j = 0; j < it.n_max; ++j, ++kv_it) {
+          const int st = kv_it % KV_STAGES;
+          const uint32_t ph = (kv_it / KV_STAGES) & 1u;
+          if (kv_it >= KV_STAGES) wait_or_abort(bar(B_KEMPTY + st), ph ^ 1u, abort_flag);
+          mbar_expect_tx(bar(B_KFULL + st), TILE_BYTES);
 #pragma unroll
-        for (int sl = 0; sl < NSLAB; ++sl)
-          tma_load_3d(sK + st * TILE_BYTES + sl * SLAB, &kmap, sl * 64, kv_c1, kv_c2 + j * BN, bar(B_KFULL + st));
-        if (j >= KV_STAGES) wait_or_abort(bar(B_VEMPTY + st), ph ^ 1u, abort_flag);
-        TC5_TRACE(3, j, 2);
-        mbar_expect_tx(bar(B_VFULL + st), TILE_BYTES);
+          for (int sl = 0; sl < NSLAB; ++sl)
+            tma_load_3d(sK + st * TILE_BYTES + sl * SLAB, &kmap, sl * 64, it.kv_c1, it.kv_c2 + j * BN,
+                        bar(B_KFULL + st));
+          if (kv_it >= KV_STAGES) wait_or_abort(bar(B_VEMPTY + st), ph ^ 1u, abort_flag);
+          mbar_expect_tx(bar(B_VFULL + st), TILE_BYTES);
 #pragma unroll
-        for (int sl = 0; sl < NSLAB; ++sl)
-          tma_load_3d(sV + st * TILE_BYTES + sl * SLAB, &vmap, sl * 64, kv_c1, kv_c2 + j * BN, bar(B_VFULL + st));
+          for (int sl = 0; sl < NSLAB; ++sl)
+            tma_load_3d(sV + st * TILE_BYTES + sl * SLAB, &vmap, sl * 64, it.kv_c1, it.kv_c2 + j * BN,
+                        bar(B_VFULL + st));
+        }
       }
     }
   } else if (warp == 1 || warp == 3) {
@@ -342,10 +394,10 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     // between the two lanes keeps the issue order  QK(0,0) QK(1,0) | PV(0,j) QK(0,j+1) |
     // PV(1,j) QK(1,j+1) | ...  so the tiles stay half a period apart (one tile's softmax
     // overlaps the other tile's MMAs) while each lane's barrier waits, fences and commits
-    // overlap the other lane's MMAs.
+    // overlap the other lane's MMAs.  K/V stages are released when BOTH lanes have committed
+    // (a lane whose tile does not use a stage arrives on it directly).
     const int t = warp == 1 ? 0 : 1;
-    if (lane == 0 && n_kv[t] > 0) {
-      const bool other_active = n_kv[1] > 0;     // tile 0 is always active here
+    if (lane == 0) {
       constexpr uint32_t TILE16 = TILE_BYTES >> 4;
       const uint64_t qd = smem_desc(sQ + (uint32_t)t * TILE_BYTES, 16, 1024);
       const uint64_t kd0 = smem_desc(sK, 16, 1024);
@@ -368,62 +420,95 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           tc_mma_ts(dO, dS + (uint32_t)ks * 8u, b0 + (uint32_t)ks * 128u, IDESC_PV, (acc | (ks > 0 ? 1u : 0u)));
         }
       };
-      // token protocol: block b of tile 0 precedes block b of tile 1, which precedes block b+1 of tile 0
-      uint32_t tok_waits = 0;   // completed waits on my token barrier
-      auto take_token = [&]() {
-        if (!other_active) return;
-        wait_or_abort(bar(B_TOKEN + t), tok_waits & 1u, abort_flag);
-        ++tok_waits;
-      };
-      auto pass_token = [&]() {
-        if (other_active) mbar_arrive(bar(B_TOKEN + (t ^ 1)));
-      };
-      wait_or_abort(bar(B_QFULL), 0, abort_flag);
-      wait_or_abort(bar(B_KFULL + 0), 0, abort_flag);
-      tc_fence_after();
-      if (t == 1) take_token();
-      issue_qk(0);
-      pass_token();
-      tc_commit(bar(B_SFULL + t));
-      tc_commit(bar(B_KEMPTY + 0));
-      for (int j = 0; j < n_kv[t]; ++j) {
-        const int st = j % KV_STAGES;
-        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-        const bool more = j + 1 < n_kv[t];
-        const int st1 = (j + 1) % KV_STAGES;
-        const uint32_t ph1 = (uint32_t)((j + 1) / KV_STAGES) & 1u;
-        TC5_TRACE(4 + 2 * t, j, 0);
-        wait_or_abort(bar(B_VFULL + st), ph, abort_flag);
-        if (more) wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag);
-        wait_or_abort(bar(B_PLO + t), (uint32_t)j & 1u, abort_flag);
-        TC5_TRACE(4 + 2 * t, j, 1);
-        // tile 1's block j follows tile 0's block j; tile 0's block j follows tile 1's block j-1,
-        // which exists unless tile 1 has already run out of KV tiles
-        if (t == 1 || j <= n_kv[1]) take_token();
-        TC5_TRACE(4 + 2 * t, j, 2);
-        tc_fence_after();
-        issue_pv(st, j > 0 ? 1u : 0u, 0);
-        TC5_TRACE(4 + 2 * t, j, 3);
-        wait_or_abort(bar(B_PHI + t), (uint32_t)j & 1u, abort_flag);
-        tc_fence_after();
-        TC5_TRACE(4 + 2 * t, j, 4);
-        issue_pv(st, 1u, 1);
-        if (more) issue_qk(st1);
-        TC5_TRACE(4 + 2 * t, j, 5);
-        pass_token();
-        tc_commit(bar(B_OFULL + t));
-        tc_commit(bar(B_VEMPTY + st));
-        if (more) {
-          tc_commit(bar(B_SFULL + t));
-          tc_commit(bar(B_KEMPTY + st1));
+      uint32_t kv_it = 0, q_cnt = 0, blk = 0, tok_waits = 0;
+      for (uint32_t ic = 0;; ++ic) {
+        if (*abort_flag) break;
+        const int slot = ic % kItemQ;
+        wait_or_abort(bar(B_IFULL + slot), (ic / kItemQ) & 1u, abort_flag);
+        const long long item = item_slot[slot];
+        mbar_arrive(bar(B_IEMPTY + slot));
+        if (item < 0 || item >= n_items) break;
+        Tc5Item it;
+        tc5_decode_item(p, item, it);
+        const bool other_active = it.n_kv[1] > 0;   // tile 0 is always active in a non-empty item
+        const int n_mine = it.n_kv[t];
+        auto take_token = [&]() {
+          if (!other_active) return;
+          wait_or_abort(bar(B_TOKEN + t), tok_waits & 1u, abort_flag);
+          ++tok_waits;
+        };
+        auto pass_token = [&]() {
+          if (other_active) mbar_arrive(bar(B_TOKEN + (t ^ 1)));
+        };
+        if (n_mine > 0) {
+          // block 0: S = Q K_0^T
+          wait_or_abort(bar(B_QFULL + t), q_cnt & 1u, abort_flag);
+          ++q_cnt;
+          {
+            const int st = kv_it % KV_STAGES;
+            wait_or_abort(bar(B_KFULL + st), (kv_it / KV_STAGES) & 1u, abort_flag);
+            tc_fence_after();
+            if (t == 1) take_token();
+            issue_qk(st);
+            pass_token();
+            tc_commit(bar(B_SFULL + t));
+            tc_commit(bar(B_KEMPTY + st));
+            if (n_mine == 1) tc_commit(bar(B_QEMPTY + t));
+          }
+          for (int j = 0; j < n_mine; ++j, ++blk) {
+            const uint32_t g = kv_it + (uint32_t)j;
+            const int st = g % KV_STAGES;
+            const uint32_t ph = (g / KV_STAGES) & 1u;
+            const bool more = j + 1 < n_mine;
+            const int st1 = (g + 1) % KV_STAGES;
+            const uint32_t ph1 = ((g + 1) / KV_STAGES) & 1u;
+            wait_or_abort(bar(B_VFULL + st), ph, abort_flag);
+            if (more) wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag);
+            wait_or_abort(bar(B_PLO + t), blk & 1u, abort_flag);
+            // tile 1's block j+1 follows tile 0's block j+1; tile 0's block j+1 follows tile 1's
+            // block j, which exists unless tile 1 has already run out of KV tiles
+            if (t == 1 || j <= it.n_kv[1]) take_token();
+            tc_fence_after();
+            issue_pv(st, j > 0 ? 1u : 0u, 0);
+            wait_or_abort(bar(B_PHI + t), blk & 1u, abort_flag);
+            tc_fence_after();
+            issue_pv(st, 1u, 1);
+            if (more) issue_qk(st1);
+            pass_token();
+            tc_commit(bar(B_OFULL + t));
+            tc_commit(bar(B_VEMPTY + st));
+            if (more) {
+              tc_commit(bar(B_SFULL + t));
+              tc_commit(bar(B_KEMPTY + st1));
+              if (j + 2 == n_mine) tc_commit(bar(B_QEMPTY + t));   // that was the last QK of this item
+            }
+          }
+          if (other_active) {
+            // balance the token barriers before the next item: tile 0 hands tile 1 the token for a
+            // block that tile 0 does not have (one more KV tile under causal masking in row-pair
+            // mode) and then takes tile 1's final pass; each barrier sees one arrival per wait
+            if (t == 0) {
+              if (it.n_kv[1] > it.n_kv[0]) {
+                take_token();
+                pass_token();
+              }
+              take_token();
+            }
+          }
         }
-        TC5_TRACE(4 + 2 * t, j, 6);
-      }
-      // tile 1 may own one more block than tile 0 (causal, row-pair mode): hand it the token it waits
-      // for, but only after it has taken the previous one (one arrival per barrier phase)
-      if (t == 0 && n_kv[1] > n_kv[0]) {
-        take_token();
-        pass_token();
+        // Stages of this item that my tile does not use still need my arrival to be released.  The
+        // arrival is made only after the stage's data has landed, i.e. after the barrier's previous
+        // phase has completed, so that it can never be counted for the stage's previous use.
+        for (int j = n_mine; j < it.n_max; ++j) {
+          const uint32_t g = kv_it + (uint32_t)j;
+          const int st = g % KV_STAGES;
+          const uint32_t ph = (g / KV_STAGES) & 1u;
+          wait_or_abort(bar(B_KFULL + st), ph, abort_flag);
+          mbar_arrive(bar(B_KEMPTY + st));
+          wait_or_abort(bar(B_VFULL + st), ph, abort_flag);
+          mbar_arrive(bar(B_VEMPTY + st));
+        }
+        kv_it += (uint32_t)it.n_max;
       }
     }
   } else if (warp == 2) {
@@ -434,19 +519,29 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     const int t = (warp - 4) >> 2;
     const int wq = warp & 3;                   // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;            // row within the tile == TMEM lane
-    const int grow = row0[t] + row;            // row within the sequence
     const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
     const uint32_t tS = lane_base + (uint32_t)t * 128u;
     const uint32_t tO = lane_base + O_COL0 + (uint32_t)t * D;
-    if (n_kv[t] > 0) {
+    uint32_t blk = 0;
+    for (uint32_t ic = 0;; ++ic) {
+      if (*abort_flag) break;
+      const int slot = ic % kItemQ;
+      wait_or_abort(bar(B_IFULL + slot), (ic / kItemQ) & 1u, abort_flag);
+      const long long item = item_slot[slot];
+      mbar_arrive(bar(B_IEMPTY + slot));
+      if (item < 0 || item >= n_items) break;
+      Tc5Item it;
+      tc5_decode_item(p, item, it);
+      const int n_mine = it.n_kv[t];
+      if (n_mine == 0) continue;
+      const int len = it.len;
+      const int grow = it.row0[t] + row;       // row within the sequence
       float m = -INFINITY, l = 0.f;
-      for (int j = 0; j < n_kv[t]; ++j) {
-        TC5_TRACE(t, j, 0);
-        wait_or_abort(bar(B_SFULL + t), (uint32_t)j & 1u, abort_flag);
-        TC5_TRACE(t, j, 1);
+      for (int j = 0; j < n_mine; ++j, ++blk) {
+        wait_or_abort(bar(B_SFULL + t), blk & 1u, abort_flag);
         tc_fence_after();
         const int k0 = j * BN;
-        const bool need_mask = (k0 + BN > len) || (p.causal && (k0 + BN - 1 > row0[t]));
+        const bool need_mask = (k0 + BN > len) || (p.causal && (k0 + BN - 1 > it.row0[t]));
         // ---- the whole score row of this thread: 128 fp32 values, one round trip ----
         float sv[4][32];
         tc_ld32(tS, sv[0]);
@@ -454,7 +549,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         tc_ld32(tS + 64, sv[2]);
         tc_ld32(tS + 96, sv[3]);
         tc_wait_ld();
-        TC5_TRACE(t, j, 2);
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -481,7 +575,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         const float alpha = grow_big ? fast_exp2(m - m_new) : 1.f;
         if (j > 0 && __any_sync(0xffffffffu, grow_big)) {
           // O_t must hold the result of PV(t, j-1) before it is rescaled
-          wait_or_abort(bar(B_OFULL + t), (uint32_t)(j - 1) & 1u, abort_flag);
+          wait_or_abort(bar(B_OFULL + t), (blk - 1) & 1u, abort_flag);
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
@@ -496,7 +590,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         }
         if (grow_big) m = m_new;
         l *= alpha;
-        TC5_TRACE(t, j, 3);
         // ---- P = exp2(S * scale - m), fp16, written over the first 64 columns of S ----
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
@@ -524,19 +617,19 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar((c == 1 ? B_PLO : B_PHI) + t));
-            TC5_TRACE(t, j, c == 1 ? 4 : 5);
           }
         }
         l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
       }
-      // ---- epilogue: O / l -> fp16 -> global ----
-      wait_or_abort(bar(B_OFULL + t), (uint32_t)(n_kv[t] - 1) & 1u, abort_flag);
+      // ---- epilogue: O / l -> fp16 -> global.  The next item's first PV of this tile cannot be
+      // issued before these threads have produced its P, i.e. after these loads have completed.
+      wait_or_abort(bar(B_OFULL + t), (blk - 1) & 1u, abort_flag);
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __half* orow;
-      if (p.dense) orow = p.out + (long long)seq * p.o_batch_stride + (long long)head[t] * p.o_head_stride +
+      if (p.dense) orow = p.out + (long long)it.seq * p.o_batch_stride + (long long)it.head[t] * p.o_head_stride +
                           (long long)grow * p.o_tok_stride;
-      else orow = p.out + (tok0 + grow) * p.o_tok_stride + (long long)head[t] * p.o_head_stride;
+      else orow = p.out + (it.tok0 + grow) * p.o_tok_stride + (long long)it.head[t] * p.o_head_stride;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         float o[32];
@@ -554,6 +647,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           }
         }
       }
+      tc_fence_before();
     }
   }
 
@@ -580,6 +674,35 @@ bool make_map3(EncodeTiledFn enc, CUtensorMap* map, const void* base, int D, lon
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Item counters of in-flight launches (one per launch, used round-robin, zeroed in-stream before
+// the kernel).  More than kCounterPool prefill launches in flight at once on one device would share
+// a counter; launches ordered on one stream never do.
+constexpr int kCounterPool = 64;
+__device__ unsigned long long g_tc5_item_counters[kCounterPool];
+unsigned long long* g_counter_base[64] = {nullptr};
+std::atomic<unsigned int> g_counter_next{0};
+std::mutex g_counter_mu;
+
+cudaError_t next_item_counter(unsigned long long** out, cudaStream_t stream) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  {
+    std::lock_guard<std::mutex> lk(g_counter_mu);
+    if (g_counter_base[dev] == nullptr) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_tc5_item_counters);
+      if (e != cudaSuccess) return e;
+      g_counter_base[dev] = static_cast<unsigned long long*>(ptr);
+    }
+  }
+  unsigned long long* c = g_counter_base[dev] + (g_counter_next.fetch_add(1) % kCounterPool);
+  e = cudaMemsetAsync(c, 0, sizeof(unsigned long long), stream);
+  *out = c;
+  return e;
 }
 
 bool g_tc5_poly = false;  // true: every other pair of exp2 runs as a polynomial on the FMA pipes
@@ -612,14 +735,21 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   p.scale_log2 = pp.scale_log2;
   constexpr int KV_STAGES = (D == 128) ? 2 : 4;
   constexpr size_t TILE = (size_t)(D / 64) * 128 * 128;
-  const size_t smem = 1024 + (2 + 2 * KV_STAGES) * TILE + 64 * 8 + 16;
+  const size_t smem = 1024 + (2 + 2 * KV_STAGES) * TILE + 64 * 8 + 16;  // tiles + barriers, item queue, flags
   auto kern = g_tc5_poly ? prefill_tc5_kernel<D, true> : prefill_tc5_kernel<D, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int max_len = dense ? pp.N : pp.max_seqlen;
   dim3 grid;
-  if (p.pair_heads) grid = dim3(pp.H_Q / 2, pp.batch, (max_len + 127) / 128);
-  else grid = dim3(pp.H_Q, pp.batch, (max_len + 255) / 256);
+  if (p.pair_heads) { p.n_hg = pp.H_Q / 2; p.n_rb = (max_len + 127) / 128; }
+  else { p.n_hg = pp.H_Q; p.n_rb = (max_len + 255) / 256; }
+  const long long n_items = (long long)p.n_rb * pp.batch * p.n_hg;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  grid = dim3((unsigned)(n_items < sms ? n_items : sms));
+  e = next_item_counter(&p.item_counter, stream);
+  if (e != cudaSuccess) return e;
   kern<<<grid, 384, smem, stream>>>(qmap, kmap, vmap, p);
   return cudaGetLastError();
 }
