@@ -33,9 +33,12 @@ if ROOT not in sys.path:
 
 # DRAM bytes per launch of the split-KV decode kernel on the headline workload, from
 # the ncu capture summarised in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
-# The paged-decode figure is the B=16 capture (304.6 MB for 73,364 tokens) scaled by tokens to
-# the benchmark launch (275,479 tokens); traffic grows in proportion to tokens.  None = no capture yet.
-NCU_TRAFFIC_BYTES = {"paged_decode": 1_143_800_000, "int8_decode": None, "contig_decode": None, "varlen_prefill": None}
+# The paged-decode figure is the B=16 capture (304.8 MB for 73,364 tokens) scaled by tokens to
+# the benchmark launch (275,479 tokens); the INT8 figure is the B=16 capture (274.8 MB) scaled to
+# B=32; traffic grows in proportion to tokens.  None = no DRAM-traffic figure (tensor-bound kernel
+# or no capture).
+NCU_TRAFFIC_BYTES = {"paged_decode": 1_144_600_000, "int8_decode": 549_700_000, "contig_decode": None,
+                     "varlen_prefill": None}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -300,7 +303,19 @@ def dist_setup(n_gpus):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29500")
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # NCCL announces its version on stdout at the first communicator set-up; stdout carries the
+        # one JSON line only, so point fd 1 at stderr until the communicator exists.
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
     return rank, world, local
 
 

@@ -267,6 +267,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t O_COL0 = 256;
+  constexpr int kPSplit = 2;                 // P is handed to the PV MMA in two parts: 32*kPSplit keys, then the rest
   constexpr int kItemQ = 4;                  // depth of the per-CTA item queue
   constexpr int kItemConsumers = 2 + 256;    // two MMA lanes + every softmax thread
 
@@ -415,8 +416,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       };
       auto issue_pv = [&](int st, uint32_t acc, int half) {
         const uint64_t b0 = vd0 + (uint64_t)((uint32_t)st * TILE16);
+        // first part: the keys whose P arrives with the first barrier (kPSplit chunks of 32 keys)
 #pragma unroll
-        for (int ks = half * (BN / 32); ks < (half + 1) * (BN / 32); ++ks) {
+        for (int ks = half ? 2 * kPSplit : 0; ks < (half ? BN / 16 : 2 * kPSplit); ++ks) {
           tc_mma_ts(dO, dS + (uint32_t)ks * 8u, b0 + (uint32_t)ks * 128u, IDESC_PV, (acc | (ks > 0 ? 1u : 0u)));
         }
       };
@@ -602,7 +604,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           for (int i = 0; i < 16; ++i) {
             const float2 x = ffma2(make_float2(sv[c][2 * i], sv[c][2 * i + 1]), sc2, nm2);
             float2 e;
-            if (POLY && (i & 1)) {
+            if (POLY && (i & 3) == 3) {
               e = exp2_poly2(x);
             } else {
               e.x = fast_exp2(x.x);
@@ -612,11 +614,11 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             pk[i] = pack_half2(e.x, e.y);
           }
           tc_st16(tS + c * 16, pk);
-          if (c == 1 || c == 3) {
-            // keys [0,64) / [64,128) of P are in tensor memory: let the PV MMA start on that half
+          if (c == kPSplit - 1 || c == 3) {
+            // the first kPSplit chunks / the rest of P are in tensor memory: let the PV MMA start on them
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(bar((c == 1 ? B_PLO : B_PHI) + t));
+            mbar_arrive(bar((c == 3 ? B_PHI : B_PLO) + t));
           }
         }
         l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
@@ -705,7 +707,7 @@ cudaError_t next_item_counter(unsigned long long** out, cudaStream_t stream) {
   return e;
 }
 
-bool g_tc5_poly = false;  // true: every other pair of exp2 runs as a polynomial on the FMA pipes
+bool g_tc5_poly = false;  // true: every fourth pair of exp2 runs as a polynomial on the FMA pipes
 
 template <int D>
 cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t stream) {
