@@ -291,7 +291,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long n_items = (long long)p.n_rb * p.batch * p.n_hg;
 #ifdef FA_TC5_TRACE
-  const bool trace_on = false;
+  bool trace_on = false;   // set by each role while it processes the first item of CTA 0
 #endif
 
   // ---- set-up (once per CTA) --------------------------------------------------------
@@ -434,6 +434,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         tc5_decode_item(p, item, it);
         const bool other_active = it.n_kv[1] > 0;   // tile 0 is always active in a non-empty item
         const int n_mine = it.n_kv[t];
+#ifdef FA_TC5_TRACE
+        trace_on = (blockIdx.x == 0 && ic == 0);
+#endif
         auto take_token = [&]() {
           if (!other_active) return;
           wait_or_abort(bar(B_TOKEN + t), tok_waits & 1u, abort_flag);
@@ -464,18 +467,24 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             const bool more = j + 1 < n_mine;
             const int st1 = (g + 1) % KV_STAGES;
             const uint32_t ph1 = ((g + 1) / KV_STAGES) & 1u;
+            TC5_TRACE(4 + 2 * t, j, 0);
             wait_or_abort(bar(B_VFULL + st), ph, abort_flag);
             if (more) wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag);
             wait_or_abort(bar(B_PLO + t), blk & 1u, abort_flag);
+            TC5_TRACE(4 + 2 * t, j, 1);
             // tile 1's block j+1 follows tile 0's block j+1; tile 0's block j+1 follows tile 1's
             // block j, which exists unless tile 1 has already run out of KV tiles
             if (t == 1 || j <= it.n_kv[1]) take_token();
+            TC5_TRACE(4 + 2 * t, j, 2);
             tc_fence_after();
             issue_pv(st, j > 0 ? 1u : 0u, 0);
+            TC5_TRACE(4 + 2 * t, j, 3);
             wait_or_abort(bar(B_PHI + t), blk & 1u, abort_flag);
             tc_fence_after();
+            TC5_TRACE(4 + 2 * t, j, 4);
             issue_pv(st, 1u, 1);
             if (more) issue_qk(st1);
+            TC5_TRACE(4 + 2 * t, j, 5);
             pass_token();
             tc_commit(bar(B_OFULL + t));
             tc_commit(bar(B_VEMPTY + st));
@@ -484,6 +493,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
               tc_commit(bar(B_KEMPTY + st1));
               if (j + 2 == n_mine) tc_commit(bar(B_QEMPTY + t));   // that was the last QK of this item
             }
+            TC5_TRACE(4 + 2 * t, j, 6);
           }
           if (other_active) {
             // balance the token barriers before the next item: tile 0 hands tile 1 the token for a
@@ -536,11 +546,16 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       tc5_decode_item(p, item, it);
       const int n_mine = it.n_kv[t];
       if (n_mine == 0) continue;
+#ifdef FA_TC5_TRACE
+      trace_on = (blockIdx.x == 0 && ic == 0 && lane == 0 && wq == 0);
+#endif
       const int len = it.len;
       const int grow = it.row0[t] + row;       // row within the sequence
       float m = -INFINITY, l = 0.f;
       for (int j = 0; j < n_mine; ++j, ++blk) {
+        TC5_TRACE(t, j, 0);
         wait_or_abort(bar(B_SFULL + t), blk & 1u, abort_flag);
+        TC5_TRACE(t, j, 1);
         tc_fence_after();
         const int k0 = j * BN;
         const bool need_mask = (k0 + BN > len) || (p.causal && (k0 + BN - 1 > it.row0[t]));
@@ -551,6 +566,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         tc_ld32(tS + 64, sv[2]);
         tc_ld32(tS + 96, sv[3]);
         tc_wait_ld();
+        TC5_TRACE(t, j, 2);
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -592,6 +608,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         }
         if (grow_big) m = m_new;
         l *= alpha;
+        TC5_TRACE(t, j, 3);
         // ---- P = exp2(S * scale - m), fp16, written over the first 64 columns of S ----
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
@@ -603,22 +620,30 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float2 x = ffma2(make_float2(sv[c][2 * i], sv[c][2 * i + 1]), sc2, nm2);
-            float2 e;
-            if (POLY && (i & 3) == 3) {
-              e = exp2_poly2(x);
+            if (POLY) {
+              // two exponentials per MUFU instruction: round the argument to fp16, exp2 on the
+              // half2; the row sum is taken from the very values the PV MMA will multiply
+              const uint32_t xh = pack_half2(x.x, x.y);
+              uint32_t eh;
+              asm("ex2.approx.f16x2 %0, %1;" : "=r"(eh) : "r"(xh));
+              pk[i] = eh;
+              rs2[c] = fadd2(rs2[c], __half22float2(*reinterpret_cast<const __half2*>(&eh)));
             } else {
+              float2 e;
               e.x = fast_exp2(x.x);
               e.y = fast_exp2(x.y);
+              rs2[c] = fadd2(rs2[c], e);
+              pk[i] = pack_half2(e.x, e.y);
             }
-            rs2[c] = fadd2(rs2[c], e);
-            pk[i] = pack_half2(e.x, e.y);
           }
           tc_st16(tS + c * 16, pk);
           if (c == kPSplit - 1 || c == 3) {
             // the first kPSplit chunks / the rest of P are in tensor memory: let the PV MMA start on them
+            TC5_TRACE(t, j, c == 3 ? 6 : 4);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar((c == 3 ? B_PHI : B_PLO) + t));
+            TC5_TRACE(t, j, c == 3 ? 7 : 5);
           }
         }
         l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
@@ -707,7 +732,7 @@ cudaError_t next_item_counter(unsigned long long** out, cudaStream_t stream) {
   return e;
 }
 
-bool g_tc5_poly = false;  // true: every fourth pair of exp2 runs as a polynomial on the FMA pipes
+bool g_tc5_poly = false;  // true: exp2 evaluated on half2 (two results per MUFU instruction)
 
 template <int D>
 cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t stream) {
