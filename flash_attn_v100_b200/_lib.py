@@ -27,6 +27,7 @@ SIGNATURES = {
     "fa_decode_gqa_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "fa_decode_varlen_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "fa_decode_int8_gqa": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
+    "fa_rope_append_paged_f16": (_i, [_vp] * 12 + [_i, _i, _i, _i, _i, _i, _i64, _i, _vp]),
     "fa_prefill_set_impl": (_i, [_i]),
     "fa_prefill_status": (_i, [_vp, _c.POINTER(_i), _i]),
     "fa_prefill_dense_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),

@@ -14,6 +14,7 @@
 
 #include "decode_splitkv.cuh"
 #include "prefill.cuh"
+#include "rope_append.cuh"
 
 namespace {
 
@@ -478,6 +479,42 @@ int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out
   p.kv_batch_stride = 0; p.kv_head_stride = D; p.kv_tok_stride = (long long)H_KV * D;
   p.causal = causal ? 1 : 0;
   return run_prefill(p, D, static_cast<cudaStream_t>(stream));
+}
+
+int fa_rope_append_paged_f16(const void* q, const void* k, const void* v, const float* cos, const float* sin,
+                             void* q_out, void* k_out, void* k_cache, void* v_cache, const int32_t* block_table,
+                             const int32_t* positions, const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV,
+                             int D, int rot_dim, int64_t num_pages, int block_table_stride, void* stream) {
+  FA_REQUIRE(q && k && v && cos && sin && q_out, "null tensor pointer");
+  FA_REQUIRE(T >= 0 && batch > 0 && H_Q > 0 && H_KV > 0, "T must be >= 0; batch, H_Q, H_KV positive");
+  FA_REQUIRE(D > 0 && D <= 256 && D % 8 == 0, "D must be a multiple of 8, at most 256");
+  FA_REQUIRE(rot_dim > 0 && rot_dim <= D && rot_dim % 16 == 0 && (D - rot_dim) % 8 == 0,
+             "rot_dim must be a multiple of 16, at most D, with D - rot_dim a multiple of 8");
+  FA_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "k_cache and v_cache must be given together");
+  if (k_cache != nullptr) {
+    FA_REQUIRE(block_table != nullptr && block_table_stride > 0 && num_pages > 0,
+               "block_table, its stride and num_pages are required with a cache");
+  }
+  FA_REQUIRE(cu_seqlens != nullptr || (positions != nullptr && T == batch),
+             "without cu_seqlens there is one token per sequence (T == batch) and positions is required");
+  for (const void* ptr : {q, k, v, (const void*)q_out, (const void*)k_out, (const void*)k_cache, (const void*)v_cache})
+    FA_REQUIRE((reinterpret_cast<uintptr_t>(ptr) & 15) == 0, "tensor pointers must be 16-byte aligned");
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != FA_OK) return rc;
+  fa::RopeAppendParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = static_cast<const __half*>(q); p.k = static_cast<const __half*>(k); p.v = static_cast<const __half*>(v);
+  p.cos = cos; p.sin = sin;
+  p.q_out = static_cast<__half*>(q_out); p.k_out = static_cast<__half*>(k_out);
+  p.k_cache = static_cast<__half*>(k_cache); p.v_cache = static_cast<__half*>(v_cache);
+  p.block_table = block_table; p.positions = positions; p.cu_seqlens = cu_seqlens;
+  p.T = T; p.batch = batch; p.H_Q = H_Q; p.H_KV = H_KV; p.D = D; p.rot_dim = rot_dim;
+  p.bt_stride = block_table_stride; p.num_pages = num_pages;
+  FA_CUDA(fa::prefill_status_ptr(&p.status));
+  cudaError_t e = fa::launch_rope_append(p, di.sm_count, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(FA_ERR_CUDA, "rope/append launch failed: %s", cudaGetErrorString(e));
+  return FA_OK;
 }
 
 }  // extern "C"

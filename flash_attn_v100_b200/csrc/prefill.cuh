@@ -31,6 +31,7 @@ bool prefill_tc5_supported(const PrefillParams& p, int D);
 cudaError_t launch_prefill_tc5(const PrefillParams& p, int D, void* encode_fn, cudaStream_t stream);
 void prefill_tc5_set_poly(bool on);
 cudaError_t prefill_status(int* host_out, cudaStream_t stream);
+cudaError_t prefill_status_ptr(int** out);  // device address of the status word (current device)
 cudaError_t prefill_status_clear(cudaStream_t stream);
 
 }  // namespace fa

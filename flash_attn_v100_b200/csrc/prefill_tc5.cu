@@ -804,6 +804,13 @@ extern "C" int fa_debug_read_tc5_trace(long long* host, int n) {
 
 void prefill_tc5_set_poly(bool on) { g_tc5_poly = on; }
 
+cudaError_t prefill_status_ptr(int** out) {
+  void* ptr = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&ptr, g_prefill_status);
+  *out = static_cast<int*>(ptr);
+  return e;
+}
+
 cudaError_t prefill_status(int* host_out, cudaStream_t stream) {
   cudaError_t e = cudaMemcpyFromSymbolAsync(host_out, g_prefill_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
   if (e != cudaSuccess) return e;

@@ -1,0 +1,29 @@
+// Fused rotary embedding + KV append into pages: parameter block and launcher.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fa {
+
+struct RopeAppendParams {
+  const __half* q;            // [T, H_Q, D]
+  const __half* k;            // [T, H_KV, D]
+  const __half* v;            // [T, H_KV, D]
+  const float* cos;           // [T, rot_dim] fp32 (angles repeat over the two halves)
+  const float* sin;           // [T, rot_dim]
+  __half* q_out;              // [T, H_Q, D] rotated queries
+  __half* k_out;              // optional [T, H_KV, D] rotated keys (prefill attention reads them)
+  __half* k_cache;            // optional [pages, H_KV, 16, D]
+  __half* v_cache;
+  const int32_t* block_table; // [batch, bt_stride]
+  const int32_t* positions;   // decode: slot of the new token per sequence; packed: first slot per sequence (or null = 0)
+  const int32_t* cu_seqlens;  // null: token i belongs to sequence i (T == batch); else packed [batch + 1]
+  int32_t* status;            // sticky status word (page id outside the pool / no slot)
+  int T, batch, H_Q, H_KV, D, rot_dim, bt_stride;
+  long long num_pages;
+};
+
+cudaError_t launch_rope_append(const RopeAppendParams& p, int sm_count, cudaStream_t stream);
+
+}  // namespace fa

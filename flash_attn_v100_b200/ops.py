@@ -421,6 +421,79 @@ def forward_varlen_prefill_fp16_stream(q, k, v, cu_seqlens, max_seqlen, causal, 
 
 
 # --------------------------------------------------------------------------
+# write side of the paged cache (an addition: the reference does this in Python)
+# --------------------------------------------------------------------------
+def rope_append_paged_fp16(q, k, v, cos, sin, k_cache, v_cache, block_table, positions, max_num_blocks,
+                           cu_seqlens=None, return_k=False):
+    """Rotary embedding of q and k plus the append of k / v into the paged cache, in one launch.
+
+    Replaces the reference's `apply_rotary_emb` (flash_attn_llm/models/rope.py:302-348, half rotation,
+    partial rotary when cos/sin are narrower than D) followed by its per-token cache copies
+    (flash_attn_llm/kv_cache/manager.py:350-357, tensor_parallel.py:285-327).  Results are bit-identical
+    to the reference's fp16 PyTorch expression.
+
+    Decode step (cu_seqlens is None): q [B,H_Q,1,D], k/v [B,H_KV,1,D]; cos/sin [B,1,1,R] or [B,R] fp32 as
+    `RotaryEmbedding.forward(1, position_ids)` returns them; positions [B] int32 = slot of the new token.
+    Packed prompts: q [total,H_Q,D], k/v [total,H_KV,D], cos/sin [total,R], cu_seqlens [batch+1] int32;
+    token j of sequence s is stored at slot positions[s] + j (positions None = 0).
+    k_cache / v_cache [pages,H_KV,16,D] are updated in place (both None: rotation only);
+    block_table [batch, *] int32 with row stride `max_num_blocks`.
+    Returns q_rot (same shape as q), or (q_rot, k_rot) with return_k=True.
+    """
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (cos, "cos"), (sin, "sin")):
+        _check_input(t, n)
+    _chk(q.dtype == torch.float16 and k.dtype == torch.float16 and v.dtype == torch.float16, "q, k, v must be float16")
+    _chk(cos.dtype == torch.float32 and sin.dtype == torch.float32, "cos and sin must be float32")
+    _chk(k.shape == v.shape, "k and v must have the same shape")
+    packed = cu_seqlens is not None
+    if packed:
+        _check_dim(q, 3, "q"); _check_dim(k, 3, "k")
+        T, H_Q, D = q.shape
+        H_KV = k.size(1)
+        _chk(k.size(0) == T and k.size(2) == D, "k must match q in tokens and head dimension")
+        _check_input(cu_seqlens, "cu_seqlens")
+        _chk(cu_seqlens.dtype == torch.int32 and cu_seqlens.dim() == 1, "cu_seqlens must be a 1D int32 tensor")
+        batch = cu_seqlens.size(0) - 1
+    else:
+        _check_dim(q, 4, "q"); _check_dim(k, 4, "k")
+        _chk(q.size(2) == 1 and k.size(2) == 1, "q and k sequence length must be 1 for a decode step")
+        T, H_Q, _, D = q.shape
+        H_KV = k.size(1)
+        _chk(k.size(0) == T and k.size(3) == D, "k must match q in batch size and head dimension")
+        batch = T
+        _chk(positions is not None, "positions is required for a decode step")
+    R = cos.shape[-1]
+    _chk(cos.numel() == T * R and sin.shape == cos.shape, "cos and sin must hold one row of rot_dim values per token")
+    _same_device(q, k, "q", "k"); _same_device(q, cos, "q", "cos")
+    has_cache = k_cache is not None
+    _chk((k_cache is None) == (v_cache is None), "k_cache and v_cache must be given together")
+    if has_cache:
+        for t, n in ((k_cache, "k_cache"), (v_cache, "v_cache"), (block_table, "block_table")):
+            _check_input(t, n)
+            _same_device(q, t, "q", n)
+        _chk(k_cache.dtype == torch.float16 and v_cache.dtype == torch.float16, "k_cache and v_cache must be float16")
+        _chk(k_cache.dim() == 4 and k_cache.shape == v_cache.shape and k_cache.size(1) == H_KV and
+             k_cache.size(2) == PAGE_BLOCK_SIZE and k_cache.size(3) == D, "cache must be [pages, H_KV, 16, D]")
+        _chk(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.size(0) >= batch,
+             "block_table must be int32 [batch, *]")
+    if positions is not None:
+        _check_input(positions, "positions")
+        _chk(positions.dtype == torch.int32 and positions.numel() == batch, "positions must be int32 [batch]")
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        q_out = torch.empty_like(q)
+        k_out = torch.empty_like(k) if return_k else None
+        s = _stream_ptr(q.device)
+        _lib.check(lib.fa_rope_append_paged_f16(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(cos), _ptr(sin), _ptr(q_out), _ptr(k_out) if return_k else None,
+            _ptr(k_cache) if has_cache else None, _ptr(v_cache) if has_cache else None,
+            _ptr(block_table) if has_cache else None, _ptr(positions) if positions is not None else None,
+            _ptr(cu_seqlens) if packed else None, T, batch, H_Q, H_KV, D, R,
+            k_cache.size(0) if has_cache else 0, int(max_num_blocks) if has_cache else 0, ctypes.c_void_p(s)))
+    return (q_out, k_out) if return_k else q_out
+
+
+# --------------------------------------------------------------------------
 # exports of the reference module that are outside the attention hot path
 # --------------------------------------------------------------------------
 _NOT_BUILT = [

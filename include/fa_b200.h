@@ -196,6 +196,29 @@ int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out
                           const int32_t* cu_seqlens, int batch, int64_t total,
                           int H_Q, int H_KV, int D, int max_seqlen, int causal, void* stream);
 
+/*
+ * Fused rotary embedding + KV append into pages: the write side of the paged cache for one
+ * layer and one step.  Replaces the reference's rotary embedding
+ * (flash_attn_llm/models/rope.py:302-348, half rotation, optional partial rotary) followed by
+ * its per-token cache copies (flash_attn_llm/kv_cache/manager.py:350-357,
+ * tensor_parallel.py:285-327, models/attention.py:322-323).
+ *   q [T,H_Q,D], k/v [T,H_KV,D] fp16 (T tokens); cos/sin [T,rot_dim] fp32 exactly as the
+ *   reference computes them (cat(freqs,freqs).cos()); q_out [T,H_Q,D]; k_out optional [T,H_KV,D].
+ *   Results are bit-identical to the reference's fp16 PyTorch expression
+ *   (x*cos) + (rotate_half(x)*sin) with cos/sin cast to fp16.
+ *   Token placement: without cu_seqlens, token i is the new token of sequence i at slot
+ *   positions[i] (T == batch, a decode step); with cu_seqlens [batch+1] the tokens are packed
+ *   prompts and token j of sequence s goes to slot positions[s] + j (positions may be NULL = 0).
+ *   k (rotated) and v are stored at cache[block_table[s][slot/16], h_kv, slot%16, :];
+ *   k_cache/v_cache may both be NULL (rotation only).  A token without a valid page sets bit 1
+ *   of the status word read by fa_prefill_status and is not stored.
+ */
+int fa_rope_append_paged_f16(const void* q, const void* k, const void* v, const float* cos,
+                             const float* sin, void* q_out, void* k_out, void* k_cache, void* v_cache,
+                             const int32_t* block_table, const int32_t* positions,
+                             const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV, int D,
+                             int rot_dim, int64_t num_pages, int block_table_stride, void* stream);
+
 /* Kernel choice for the prefill entry points: 0 = automatic (tcgen05 kernel for
  * D = 64/128, mma.sync kernel otherwise), 1 = always the mma.sync kernel, 2 = require
  * the tcgen05 kernel, 3 = tcgen05 kernel with every other pair of exp2 evaluated as a

@@ -280,3 +280,50 @@ def make_paged_workload(B, H_Q, H_KV, D, min_len, max_len, seed=0, dtype=torch.f
         k_cache = v_cache = None
     return dict(q=q, k_cache=k_cache, v_cache=v_cache, block_table=block_table,
                 seq_lens=seq_lens, max_num_blocks=max_blocks, n_pages=n_pages)
+
+
+# --------------------------------------------------------------------------
+# rotary embedding + append into pages (the write side of the paged cache)
+# --------------------------------------------------------------------------
+def rope_cos_sin(positions, rot_dim, theta=10000.0):
+    """fp32 cos/sin tables [T, rot_dim] for integer positions [T], as
+    flash_attn_llm/models/rope.py:17-37 and :228-266 compute them:
+    inv_freq = 1 / theta^(2i/rot_dim), emb = cat(freqs, freqs)."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim))
+    freqs = torch.outer(positions.float().flatten(), inv_freq)
+    emb = torch.cat([freqs, freqs], dim=-1)
+    return emb.cos(), emb.sin()
+
+
+def rotate_half(x):
+    """rope.py:269-283."""
+    x1 = x[..., : x.shape[-1] // 2]
+    x2 = x[..., x.shape[-1] // 2:]
+    return torch.cat((-x2, x1), dim=-1)
+
+
+def apply_rotary_emb(q, k, cos, sin):
+    """rope.py:302-348 (half-rotation layout; partial rotary when cos is narrower than D).
+    q [..., H_Q, D] / k [..., H_KV, D] in fp16, cos/sin broadcastable [..., 1, rot_dim] fp32.
+    Evaluated with PyTorch fp16 tensor ops exactly as the reference does."""
+    rot = cos.shape[-1]
+    cos = cos.to(q.dtype)
+    sin = sin.to(q.dtype)
+
+    def emb(x):
+        xr, xp = x[..., :rot], x[..., rot:]
+        out = (xr * cos) + (rotate_half(xr) * sin)
+        return torch.cat([out, xp], dim=-1) if xp.shape[-1] else out
+
+    return emb(q), emb(k)
+
+
+def append_to_pages(k_cache, v_cache, block_table, seq, first_slot, k_rows, v_rows):
+    """Store tokens (k_rows/v_rows [n, H_KV, D]) of sequence `seq` at slots first_slot..;
+    token at slot s lives at cache[block_table[seq][s // 16], :, s % 16]
+    (flash_attn_llm/kv_cache/manager.py:350-357, kernel layout flash_attn_kernel.cu:3446)."""
+    for i in range(k_rows.shape[0]):
+        s = first_slot + i
+        page = int(block_table[seq, s // PAGE_BLOCK_SIZE])
+        k_cache[page, :, s % PAGE_BLOCK_SIZE] = k_rows[i]
+        v_cache[page, :, s % PAGE_BLOCK_SIZE] = v_rows[i]
