@@ -291,6 +291,54 @@ class VarlenPrefill:
 WORKLOADS = {w.name: w for w in (PagedDecode, ContigDecode, Int8Decode, VarlenPrefill)}
 
 
+def run_engine(args):
+    """BASELINE configs[4]: Qwen3-8B-shaped decoder, random-init bf16 weights, 256 requests x 1024-token
+    prompts, greedy generation of 256 tokens, paged KV, tensor parallel over all ranks (by KV-head group).
+    One step = the whole generation (prefill + 255 decode steps)."""
+    rank, world, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    from flash_attn_v100_b200.engine import GenerationRunner, TPDecoder, make_rank_weights, qwen3_8b_shaped, tiny_config
+    import flash_attn_v100_b200
+    peaks, peak_src = load_peaks()
+    cfg = tiny_config() if args.engine_tiny else qwen3_8b_shaped()
+    B, P, N = (8, 64, 16) if args.engine_tiny else (args.engine_requests, 1024, 256)
+    w = make_rank_weights(cfg, rank, world, 0, device)
+    model = TPDecoder(cfg, w, rank, world, None, device)
+    runner = GenerationRunner(model, max_batch=B, max_seq_len=P + N, use_cuda_graph=True)
+    prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=torch.Generator().manual_seed(0))
+    times = []
+    for it in range(max(args.warmup, 1) + args.steps):
+        torch.cuda.synchronize(); barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        toks = runner.generate(prompts, N, prefill_chunk=args.engine_prefill_chunk)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1), world, device)
+        if it >= max(args.warmup, 1):
+            times.append(ms)
+    flash_attn_v100_b200.check_async_errors(); flash_attn_v100_b200.check_prefill_errors()
+    if rank != 0:
+        return
+    ms = sum(times) / len(times)
+    wbytes = sum(t.numel() * t.element_size() for lw in w["layers"] for t in lw.values()) + w["lm_head"].numel() * 2
+    kv_bytes_mid = B * (P + N // 2) * cfg.num_layers * model.kl * 2 * cfg.head_dim * 2
+    line = {
+        "metric": "qwen3_8b_shaped_generation_tokens_per_s", "value": B * N / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 weights and activations, fp16 attention operators", "data": "synthetic (seeded random weights, uniform random token ids)",
+        "config": {"workload": "Qwen3-8B-shaped decoder end to end (BASELINE configs[4])" if not args.engine_tiny else "tiny decoder (smoke)",
+                   "layers": cfg.num_layers, "hidden": cfg.hidden_size, "heads": f"{cfg.num_heads}/{cfg.num_kv_heads}",
+                   "requests": B, "prompt_len": P, "new_tokens": N, "parallelism": f"tp{world}", "page": 16,
+                   "decode": "CUDA graph replay", "prefill_chunk": args.engine_prefill_chunk},
+        "per_rank_weight_bytes": wbytes, "per_rank_kv_bytes_mid_generation": kv_bytes_mid,
+        "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": None, "impl": "b200",
+    }
+    print(json.dumps(line), flush=True)
+
+
 # ----------------------------------------------------------------------------
 # timing
 # ----------------------------------------------------------------------------
@@ -507,11 +555,16 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="paged_decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="paged_decode", choices=sorted(WORKLOADS) + ["engine"])
+    ap.add_argument("--engine-tiny", action="store_true", help="engine workload on the tiny test shape")
+    ap.add_argument("--engine-requests", type=int, default=256)
+    ap.add_argument("--engine-prefill-chunk", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "engine":
+        run_engine(args)
     else:
         run_b200(args)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1 and torch.distributed.is_initialized():

@@ -28,6 +28,10 @@ SIGNATURES = {
     "fa_decode_varlen_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "fa_decode_int8_gqa": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "fa_rope_append_paged_f16": (_i, [_vp] * 12 + [_i, _i, _i, _i, _i, _i, _i64, _i, _vp]),
+    "fa_add_rmsnorm_bf16": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _c.c_float, _vp]),
+    "fa_qk_norm_split_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _c.c_float, _vp]),
+    "fa_silu_mul_bf16": (_i, [_vp, _vp, _i64, _i, _vp]),
+    "fa_half_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "fa_prefill_set_impl": (_i, [_i]),
     "fa_prefill_status": (_i, [_vp, _c.POINTER(_i), _i]),
     "fa_prefill_dense_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),

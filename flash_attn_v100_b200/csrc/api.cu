@@ -15,6 +15,7 @@
 #include "decode_splitkv.cuh"
 #include "prefill.cuh"
 #include "rope_append.cuh"
+#include "engine_ops.cuh"
 
 namespace {
 
@@ -514,6 +515,44 @@ int fa_rope_append_paged_f16(const void* q, const void* k, const void* v, const 
   FA_CUDA(fa::prefill_status_ptr(&p.status));
   cudaError_t e = fa::launch_rope_append(p, di.sm_count, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, "rope/append launch failed: %s", cudaGetErrorString(e));
+  return FA_OK;
+}
+
+int fa_add_rmsnorm_bf16(void* x, const void* delta, const void* weight, void* out, int64_t rows, int cols, float eps,
+                        void* stream) {
+  FA_REQUIRE(x && weight && out, "null tensor pointer");
+  FA_REQUIRE(rows >= 0 && cols > 0 && cols % 8 == 0 && cols <= 8 * 8 * 256, "cols must be a multiple of 8, at most 16384");
+  FA_CUDA(fa::launch_add_rmsnorm(x, delta, weight, out, rows, cols, eps, static_cast<cudaStream_t>(stream)));
+  return FA_OK;
+}
+
+int fa_qk_norm_split_f16(const void* qkv, const void* q_weight, const void* k_weight, void* q, void* k, void* v,
+                         int64_t T, int H_Q, int H_KV, int D, float eps, void* stream) {
+  FA_REQUIRE(qkv && q && k && v, "null tensor pointer");
+  FA_REQUIRE(T >= 0 && H_Q > 0 && H_KV > 0, "T must be >= 0, head counts positive");
+  if (!supported_d(D)) return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (supported: 64, 128, 256)", D);
+  FA_CUDA(fa::launch_qk_norm_split(qkv, q_weight, k_weight, q, k, v, T, H_Q, H_KV, D, eps,
+                                   static_cast<cudaStream_t>(stream)));
+  return FA_OK;
+}
+
+int fa_silu_mul_bf16(const void* gate_up, void* out, int64_t T, int I, void* stream) {
+  FA_REQUIRE(gate_up && out, "null tensor pointer");
+  FA_REQUIRE(T >= 0 && I > 0 && I % 8 == 0, "I must be a positive multiple of 8");
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != FA_OK) return rc;
+  FA_CUDA(fa::launch_silu_mul(gate_up, out, T, I, di.sm_count, static_cast<cudaStream_t>(stream)));
+  return FA_OK;
+}
+
+int fa_half_to_bf16(const void* in, void* out, int64_t n, void* stream) {
+  FA_REQUIRE(in && out, "null tensor pointer");
+  FA_REQUIRE(n >= 0 && n % 8 == 0, "n must be a multiple of 8");
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != FA_OK) return rc;
+  FA_CUDA(fa::launch_half_to_bf16(in, out, n, di.sm_count, static_cast<cudaStream_t>(stream)));
   return FA_OK;
 }
 

@@ -617,6 +617,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           seen = prev;
         }
         s_last_flag = (arrivals == n_parts) ? 1 : 0;
+        // everyone has arrived: leave the counter at zero arrivals, so that a CUDA-graph replay of
+        // this launch (same epoch) starts clean
+        if (arrivals == n_parts) *reinterpret_cast<volatile unsigned long long*>(cnt) = (unsigned long long)p.epoch << 32;
       }
       __syncthreads();
       if (s_last_flag) {

@@ -219,6 +219,30 @@ int fa_rope_append_paged_f16(const void* q, const void* k, const void* v, const 
                              const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV, int D,
                              int rot_dim, int64_t num_pages, int block_table_stride, void* stream);
 
+/*
+ * Fused row-wise operators of the decoder block around the attention operators (bf16 activations).
+ * They replace chains of PyTorch element-wise kernels in the reference's model code.
+ *
+ * fa_add_rmsnorm_bf16: x [rows, cols] bf16; if delta != NULL, x += delta (written back: the residual
+ *   stream, flash_attn_llm/models/decoder_layer.py:69-85); out = RMSNorm(x) * weight with fp32
+ *   statistics, the normalised value cast to bf16 before the multiplication by the weight
+ *   (flash_attn_llm/models/norm.py:25-33).
+ * fa_qk_norm_split_f16: qkv [T, (H_Q + 2*H_KV) * D] bf16 (q heads, k heads, v heads) -> q [T,H_Q,D],
+ *   k [T,H_KV,D], v [T,H_KV,D] fp16 (the dtype of the attention operators), with the per-head RMSNorm
+ *   of Qwen3-style attention on q and k (flash_attn_llm/models/attention.py:96-102, 230-233); NULL
+ *   weights skip the norm.
+ * fa_silu_mul_bf16: gate_up [T, 2*I] bf16 (gate, then up) -> out [T, I] = silu(gate) * up
+ *   (flash_attn_llm/models/mlp.py:27).
+ * fa_half_to_bf16: fp16 -> bf16 copy of n elements (attention output back to the bf16 stream).
+ */
+int fa_add_rmsnorm_bf16(void* x, const void* delta, const void* weight, void* out, int64_t rows,
+                        int cols, float eps, void* stream);
+int fa_qk_norm_split_f16(const void* qkv, const void* q_weight, const void* k_weight, void* q,
+                         void* k, void* v, int64_t T, int H_Q, int H_KV, int D, float eps,
+                         void* stream);
+int fa_silu_mul_bf16(const void* gate_up, void* out, int64_t T, int I, void* stream);
+int fa_half_to_bf16(const void* in, void* out, int64_t n, void* stream);
+
 /* Kernel choice for the prefill entry points: 0 = automatic (tcgen05 kernel for
  * D = 64/128, mma.sync kernel otherwise), 1 = always the mma.sync kernel, 2 = require
  * the tcgen05 kernel, 3 = tcgen05 kernel with every other pair of exp2 evaluated as a
