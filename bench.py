@@ -318,6 +318,7 @@ def run_engine(args):
         ms = max_over_ranks(e0.elapsed_time(e1), world, device)
         if it >= max(args.warmup, 1):
             times.append(ms)
+            phases = runner.last_timing_ms()
     flash_attn_v100_b200.check_async_errors(); flash_attn_v100_b200.check_prefill_errors()
     if rank != 0:
         return
@@ -332,7 +333,9 @@ def run_engine(args):
         "config": {"workload": "Qwen3-8B-shaped decoder end to end (BASELINE configs[4])" if not args.engine_tiny else "tiny decoder (smoke)",
                    "layers": cfg.num_layers, "hidden": cfg.hidden_size, "heads": f"{cfg.num_heads}/{cfg.num_kv_heads}",
                    "requests": B, "prompt_len": P, "new_tokens": N, "parallelism": f"tp{world}", "page": 16,
-                   "decode": "CUDA graph replay", "prefill_chunk": args.engine_prefill_chunk},
+                   "decode": "one CUDA graph per step" if world == 1 else "chain of CUDA graphs per step, NCCL collectives eager in between", "prefill_chunk": args.engine_prefill_chunk},
+        "prefill_ms": phases[0], "decode_ms": phases[1], "decode_ms_per_token_step": phases[1] / max(N - 1, 1),
+        "prefill_tokens_per_s": B * P / (phases[0] * 1e-3), "decode_tokens_per_s": B * (N - 1) / (phases[1] * 1e-3),
         "per_rank_weight_bytes": wbytes, "per_rank_kv_bytes_mid_generation": kv_bytes_mid,
         "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": None, "impl": "b200",
     }

@@ -83,51 +83,126 @@ class TPDecoder:
 
     # ---- one decoder stack pass -------------------------------------------------------
     def forward(self, token_ids, positions, kv, block_table, slots, max_blocks, *, cu_seqlens=None, max_seqlen=0,
-                seq_lens_after=None):
+                seq_lens_after=None, seg=None):
         """token_ids [T] int64; positions [T] int32 (rotary position of every token).
         Prefill (cu_seqlens given): packed prompts, `slots` [batch] = first cache slot per sequence; returns the
         hidden state of the last token of every sequence.  Decode: one token per sequence, `slots` [B] = slot of
-        the new token, `seq_lens_after` [B] = lengths including it; returns [B, hidden]."""
+        the new token, `seq_lens_after` [B] = lengths including it (default: slots + 1); returns [B, hidden].
+        `seg` (see `Segments`) receives the compute between two collectives as one unit, so that a decode
+        step can be replayed as a chain of CUDA graphs with the NCCL calls in between."""
         cfg = self.cfg
-        x = self.w["embed"][token_ids]                                   # [T, hidden] bf16
-        cos, sin = self.rope_tables(positions)
-        delta = None
+        seg = seg or Segments(capture=False)
         prefill = cu_seqlens is not None
+        st = {"delta": None}
+
+        def first():
+            st["x"] = self.w["embed"][token_ids]                          # [T, hidden] bf16
+            st["cos"], st["sin"] = self.rope_tables(positions)
+            # decode: lengths including the new token (derived here so that a replayed step recomputes them)
+            st["lens"] = seq_lens_after if (prefill or seq_lens_after is not None) else slots + 1
+
+        seg.run(first)
         for l, lw in enumerate(self.w["layers"]):
-            h = self._add_rmsnorm(x, delta, lw["ln1"])                    # x += delta (previous MLP); h = ln1(x)
-            qkv = h @ lw["wqkv"].t()
-            q, k, v = self._qk_norm_split(qkv, lw)
+            def attention_half(l=l, lw=lw):
+                x = st["x"]
+                h = self._add_rmsnorm(x, st["delta"], lw["ln1"])         # x += delta (previous MLP); h = ln1(x)
+                qkv = h @ lw["wqkv"].t()
+                q, k, v = self._qk_norm_split(qkv, lw)
+                if prefill:
+                    q_rot, k_rot = ops.rope_append_paged_fp16(q, k, v, st["cos"], st["sin"], kv.k_pools[l], kv.v_pools[l],
+                                                              block_table, slots, max_blocks, cu_seqlens=cu_seqlens,
+                                                              return_k=True)
+                    attn = ops.forward_varlen_prefill_fp16(q_rot, k_rot, v, cu_seqlens, max_seqlen, True)
+                else:
+                    q_rot = ops.rope_append_paged_fp16(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2), st["cos"], st["sin"],
+                                                       kv.k_pools[l], kv.v_pools[l], block_table, slots, max_blocks)
+                    attn = ops.forward_paged_decode_gqa_fp16(q_rot, kv.k_pools[l], kv.v_pools[l], block_table,
+                                                             st["lens"], max_blocks)
+                a = self._to_bf16(attn.reshape(x.size(0), self.ql * cfg.head_dim))
+                st["o"] = a @ lw["wo"].t()
+
+            seg.run(attention_half)
+            seg.collective(self._all_reduce, st["o"])
+
+            def mlp_half(lw=lw):
+                h = self._add_rmsnorm(st["x"], st["o"], lw["ln2"])       # x += attention; h = ln2(x)
+                gu = h @ lw["wgu"].t()
+                st["delta"] = self._silu_mul(gu) @ lw["wd"].t()
+
+            seg.run(mlp_half)
+            seg.collective(self._all_reduce, st["delta"])
+
+        def last():
             if prefill:
-                q_rot, k_rot = ops.rope_append_paged_fp16(q, k, v, cos, sin, kv.k_pools[l], kv.v_pools[l], block_table,
-                                                          slots, max_blocks, cu_seqlens=cu_seqlens, return_k=True)
-                attn = ops.forward_varlen_prefill_fp16(q_rot, k_rot, v, cu_seqlens, max_seqlen, True)
+                idx = (cu_seqlens[1:] - 1).long()
+                x_last, d_last = st["x"][idx].contiguous(), st["delta"][idx].contiguous()
             else:
-                q_rot = ops.rope_append_paged_fp16(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2), cos, sin,
-                                                   kv.k_pools[l], kv.v_pools[l], block_table, slots, max_blocks)
-                attn = ops.forward_paged_decode_gqa_fp16(q_rot, kv.k_pools[l], kv.v_pools[l], block_table,
-                                                         seq_lens_after, max_blocks)
-            a = self._to_bf16(attn.reshape(x.size(0), self.ql * cfg.head_dim))
-            o = self._all_reduce(a @ lw["wo"].t())
-            h = self._add_rmsnorm(x, o, lw["ln2"])                        # x += attention; h = ln2(x)
-            gu = h @ lw["wgu"].t()
-            delta = self._all_reduce(self._silu_mul(gu) @ lw["wd"].t())
-        if prefill:
-            last = (cu_seqlens[1:] - 1).long()
-            x_last, d_last = x[last].contiguous(), delta[last].contiguous()
+                x_last, d_last = st["x"], st["delta"]
+            st["hidden"] = self._add_rmsnorm(x_last, d_last, self.w["final_ln"])   # final norm of (x + last MLP)
+
+        seg.run(last)
+        return st["hidden"]
+
+    def greedy_local(self, hidden):
+        """This rank's best (value, index) per sequence over its vocabulary shard, and the shard's logits."""
+        logits = (hidden @ self.w["lm_head"].t()).float()                 # [B, vocab/world]
+        val, idx = logits.max(dim=-1)
+        pair = torch.stack([val, (idx + self.rank * self.vl).float()], dim=-1).contiguous()   # indices < 2^24: exact
+        return pair, logits
+
+    def greedy_gather(self, pair, out=None):
+        """All-gather of the per-rank (value, index) pairs into `out` [world, B, 2] (allocated if None)."""
+        if out is None:
+            out = torch.empty((self.world,) + pair.shape, dtype=pair.dtype, device=pair.device)
+        if self.world == 1:
+            out[0].copy_(pair)
         else:
-            x_last, d_last = x, delta
-        return self._add_rmsnorm(x_last, d_last, self.w["final_ln"])      # final norm of (x + last MLP)
+            torch.distributed.all_gather_into_tensor(out, pair, group=self.group)
+        return out
+
+    @staticmethod
+    def greedy_select(gathered):
+        best = gathered[..., 0].argmax(dim=0)                              # first maximum = lowest rank on ties
+        return gathered[..., 1].gather(0, best.unsqueeze(0)).squeeze(0).long()
 
     def greedy_token(self, hidden):
         """argmax over the vocabulary sharded across ranks: local max / argmax, then an all-gather of the
         (value, index) pairs (the reference's `allgather`, parallel/tensor_parallel.py:172-190)."""
-        logits = (hidden @ self.w["lm_head"].t()).float()                 # [B, vocab/world]
-        val, idx = logits.max(dim=-1)
-        idx = idx + self.rank * self.vl
-        if self.world > 1:
-            pair = torch.stack([val, idx.float()], dim=-1).contiguous()   # indices < 2^24 are exact in fp32
-            gathered = torch.empty((self.world,) + pair.shape, dtype=pair.dtype, device=pair.device)
-            torch.distributed.all_gather_into_tensor(gathered, pair, group=self.group)
-            best = gathered[..., 0].argmax(dim=0)                          # first maximum = lowest rank on ties
-            idx = gathered[..., 1].gather(0, best.unsqueeze(0)).squeeze(0).long()
-        return idx, logits
+        pair, logits = self.greedy_local(hidden)
+        return self.greedy_select(self.greedy_gather(pair)), logits
+
+
+class Segments:
+    """Runs a step as alternating compute segments and collectives.  With capture=True every compute
+    segment is captured into its own CUDA graph (sharing one memory pool) and replayed at once, the
+    collectives run eagerly in between; `replay()` then repeats the whole chain.  NCCL calls are never
+    captured."""
+
+    def __init__(self, capture: bool, stream=None):
+        self.capture, self.stream, self.items, self.pool = capture, stream, [], None
+
+    def run(self, fn):
+        if not self.capture:
+            fn()
+            return
+        g = torch.cuda.CUDAGraph()
+        # thread-local capture mode: the NCCL watchdog thread may poll events of the collectives issued
+        # between two segments while the next segment is being captured
+        with torch.cuda.graph(g, pool=self.pool, stream=self.stream, capture_error_mode="thread_local"):
+            fn()
+        self.pool = g.pool()
+        self.items.append(g)
+        g.replay()                      # capture records only: run it, the following collective needs the data
+
+    def collective(self, fn, tensor):
+        out = fn(tensor)
+        if self.capture:
+            self.items.append((fn, tensor))
+        return out
+
+    def replay(self):
+        for it in self.items:
+            if isinstance(it, tuple):
+                it[0](it[1])
+            else:
+                it.replay()

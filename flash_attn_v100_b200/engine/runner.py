@@ -9,7 +9,7 @@ from typing import List, Optional
 import torch
 
 from ..kv_cache import PagedKVCache
-from .model import TPDecoder
+from .model import Segments, TPDecoder
 
 
 class GenerationRunner:
@@ -21,11 +21,11 @@ class GenerationRunner:
         self.kv = PagedKVCache(num_blocks=max_batch * self.max_blocks, num_layers=cfg.num_layers,
                                num_kv_heads=model.kl, head_dim=cfg.head_dim, max_batch=max_batch,
                                max_blocks_per_seq=self.max_blocks, device=model.device)
-        # The decode step is replayed from one CUDA graph on a single rank.  With tensor parallelism the
-        # step contains NCCL collectives; capturing them is left out (steps run eagerly) until the step is
-        # split into graph segments between the collectives.
-        self.use_cuda_graph = use_cuda_graph and model.world == 1
-        self._graph = None
+        # The decode step is replayed from one CUDA graph on a single rank, and from a chain of graphs with
+        # the NCCL collectives issued eagerly in between under tensor parallelism (NCCL calls are not captured).
+        self.use_cuda_graph = use_cuda_graph
+        self._side_stream = torch.cuda.Stream(device=model.device)   # decode runs here (one scratch workspace)
+        self._decode_cache = {}     # batch size -> (step graph(s), cur, slot, gathered): captured once, replayed by later calls
 
     @torch.no_grad()
     def generate(self, prompts: torch.Tensor, max_new_tokens: int, prefill_chunk: int = 32, logits_out: Optional[list] = None):
@@ -39,6 +39,8 @@ class GenerationRunner:
             kv.allocate(r, P + max_new_tokens)          # blocks for the whole generation: the table is static
         table = kv.block_table[:B]
         out = torch.empty((B, max_new_tokens), dtype=torch.int64, device=dev)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record()
         # ---- prefill, `prefill_chunk` sequences per pass ----
         first = torch.empty(B, dtype=torch.int64, device=dev)
         for b0 in range(0, B, prefill_chunk):
@@ -56,41 +58,76 @@ class GenerationRunner:
         for r in ids:
             kv.commit(r, P)
         out[:, 0] = first
+        ev[1].record()
         # ---- decode ----
-        cur = first.clone()
-        slot = torch.full((B,), P, dtype=torch.int32, device=dev)        # slot of the token being fed
+        cached = self._decode_cache.get(B) if (self.use_cuda_graph and logits_out is None) else None
+        if cached is not None:
+            graph, cur, slot, gathered = cached
+        else:
+            graph = None
+            cur = torch.empty(B, dtype=torch.int64, device=dev)                    # token being fed
+            slot = torch.empty(B, dtype=torch.int32, device=dev)                   # its cache slot
+            gathered = torch.empty((m.world, B, 2), dtype=torch.float32, device=dev)
+        cur.copy_(first)
+        slot.fill_(P)
 
-        def step():
-            hidden = m.forward(cur, slot, kv, table, slot, self.max_blocks, seq_lens_after=slot + 1)
-            nxt, lg = m.greedy_token(hidden)
+        def step(seg=None):
+            hidden = m.forward(cur, slot, kv, table, slot, self.max_blocks, seg=seg)
+            st = {}
+
+            def head():
+                st["pair"], st["logits"] = m.greedy_local(hidden)
+
+            def tail():
+                cur.copy_(m.greedy_select(gathered))
+                slot.add_(1)
+
+            gather = lambda pair: m.greedy_gather(pair, gathered)
+            if seg is None:
+                head(); gather(st["pair"]); tail()
+            else:
+                seg.run(head)
+                seg.collective(gather, st["pair"])
+                seg.run(tail)
             if logits_out is not None:
-                logits_out.append(("decode", 0, lg))
-            cur.copy_(nxt)
-            slot.add_(1)
+                logits_out.append(("decode", 0, st["logits"]))
 
         n_steps = max_new_tokens - 1
-        if self.use_cuda_graph and n_steps > 2 and logits_out is None:
-            # warm up on a side stream (allocator, cuBLAS workspaces, NCCL), restore state, capture, replay
-            saved_cur, saved_slot = cur.clone(), slot.clone()
-            s = torch.cuda.Stream(device=dev)
-            s.wait_stream(torch.cuda.current_stream(dev))
-            with torch.cuda.stream(s):
-                step()
-            torch.cuda.current_stream(dev).wait_stream(s)
-            cur.copy_(saved_cur); slot.copy_(saved_slot)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=s):     # same stream as the warm-up: same scratch buffers
-                step()
-            cur.copy_(saved_cur); slot.copy_(saved_slot)
-            for i in range(n_steps):
-                graph.replay()
-                out[:, i + 1] = cur
-            self._graph = graph
-        else:
-            for i in range(n_steps):
-                step()
-                out[:, i + 1] = cur
-        for r in ids:
+        graphs_ok = self.use_cuda_graph and logits_out is None and (graph is not None or n_steps > 3)
+        side = self._side_stream
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            done = 0
+            if graphs_ok and graph is None:
+                # first call for this batch size: a warm-up step, then the capture.  One graph for the whole
+                # step on a single rank; under tensor parallelism a chain of graphs with the NCCL collectives
+                # in between (every captured segment is run right after its capture, so that step is real).
+                step(); out[:, 1] = cur; done = 1
+                if m.world == 1:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=side):
+                        step()
+                else:
+                    graph = Segments(capture=True, stream=side)
+                    step(graph); out[:, 2] = cur; done = 2
+                self._decode_cache[B] = (graph, cur, slot, gathered)
+            if graphs_ok:
+                for i in range(done, n_steps):
+                    graph.replay()
+                    out[:, i + 1] = cur
+            else:
+                for i in range(n_steps):
+                    step()
+                    out[:, i + 1] = cur
+        torch.cuda.current_stream(dev).wait_stream(side)
+        ev[2].record()
+        self._events = ev
+        for r in reversed(ids):         # rows and blocks return in the order the next call takes them
             kv.commit(r, max_new_tokens - 1)
             kv.release(r)
         return out
+
+    def last_timing_ms(self):
+        """(prefill ms, decode ms) of the last generate() call; synchronises."""
+        torch.cuda.synchronize(self.model.device)
+        return self._events[0].elapsed_time(self._events[1]), self._events[1].elapsed_time(self._events[2])

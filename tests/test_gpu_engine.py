@@ -50,9 +50,11 @@ def test_cuda_graph_replay_reproduces_eager_tokens():
     g = torch.Generator().manual_seed(4)
     prompts = torch.randint(0, cfg.vocab_size, (4, 33), generator=g)
     eager = Runner(model, max_batch=4, max_seq_len=80, use_cuda_graph=False).generate(prompts, 24)
-    graphed = Runner(model, max_batch=4, max_seq_len=80, use_cuda_graph=True).generate(prompts, 24)
+    r = Runner(model, max_batch=4, max_seq_len=80, use_cuda_graph=True)
+    graphed = r.generate(prompts, 24)
+    again = r.generate(prompts, 24)                 # second call replays the cached graph only
     torch.cuda.synchronize()
-    assert torch.equal(eager, graphed)
+    assert torch.equal(eager, graphed) and torch.equal(eager, again)
     import flash_attn_v100_b200 as pkg
     pkg.check_async_errors(); pkg.check_prefill_errors()
 
