@@ -10,6 +10,7 @@
 #include <string.h>
 
 #include <atomic>
+#include <climits>
 #include <mutex>
 
 #include "decode_splitkv.cuh"
@@ -153,6 +154,9 @@ struct DecodeCall {
   int B, H_Q, H_KV, D, mode, fixed_len, N, bt_stride;
   long long num_pages, rows_total, max_units;
   bool int8;
+  // sliding window + sink (contiguous fixed mode): see DecodeParams.  has_window = false: identity page map
+  bool has_window;
+  int sink, win_start, sink_pages, win_first_page, window_pages_total;
   void* ws;
   size_t ws_bytes;
   cudaStream_t stream;
@@ -193,6 +197,11 @@ int run_decode(const DecodeCall& c) {
   p.n_gblk = (G + 15) / 16;
   p.HV = c.H_KV * p.n_gblk;
   p.mode = c.mode; p.fixed_len = c.fixed_len; p.N = c.N;
+  p.sink = 0; p.win_start = 0; p.sink_pages = INT_MAX; p.win_first_page = 0; p.window_pages_total = 0;
+  if (c.has_window) {
+    p.sink = c.sink; p.win_start = c.win_start; p.sink_pages = c.sink_pages;
+    p.win_first_page = c.win_first_page; p.window_pages_total = c.window_pages_total;
+  }
   p.bt_stride = c.bt_stride;
   p.num_pages = c.num_pages;
   p.stages = cfg.stages;
@@ -305,6 +314,43 @@ int fa_decode_gqa_f16(const void* q, const void* k, const void* v, void* out, in
   c.bt_stride = 0; c.num_pages = 0;
   c.rows_total = (long long)B * H_KV * N;
   c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * ((c.fixed_len + 15) / 16);
+  c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
+  return run_decode(c);
+}
+
+int fa_decode_sliding_window_gqa_f16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV,
+                                     int N, int D, int cache_len, int window_size, int sink_size, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+  int rc = check_decode_common(q, k, v, out, B, H_Q, H_KV, D);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(N > 0, "N must be positive");
+  // Attended keys: k < sink_size, or window_start <= k <= cache_len, always with k < N.
+  long long end = (long long)cache_len + 1;
+  if (end > N) end = N;
+  long long wstart = end - (long long)window_size;   // window_size <= 0 leaves the window empty
+  if (wstart < 0) wstart = 0;
+  if (end < 0) end = 0;
+  if (wstart > end) wstart = end;
+  long long sink = sink_size < 0 ? 0 : sink_size;
+  if (sink > N) sink = N;
+  const long long vis_end = sink > end ? sink : end;
+  const int ns = (int)((sink + 15) / 16);
+  const int end_pages = (int)((end + 15) / 16);
+  int first_w = (int)(wstart / 16);
+  if (first_w < ns) first_w = ns;                     // pages shared with the sink are visited once
+  int win_pages = wstart < end ? end_pages - first_w : 0;
+  if (win_pages < 0) win_pages = 0;
+  DecodeCall c{};
+  c.q = q; c.k = k; c.v = v; c.out = out;
+  c.B = B; c.H_Q = H_Q; c.H_KV = H_KV; c.D = D;
+  c.mode = fa::kModeContigFixed; c.N = N;
+  c.fixed_len = (int)vis_end;
+  c.has_window = (ns + win_pages) > 0;
+  c.sink = (int)sink; c.win_start = (int)wstart; c.sink_pages = ns; c.win_first_page = first_w;
+  c.window_pages_total = ns + win_pages;
+  c.bt_stride = 0; c.num_pages = 0;
+  c.rows_total = (long long)B * H_KV * N;
+  c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * (ns + win_pages);
   c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
   return run_decode(c);
 }

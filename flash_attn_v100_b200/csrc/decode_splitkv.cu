@@ -60,6 +60,11 @@ __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
   return n < 0 ? 0 : (int)n;
 }
 
+__device__ __forceinline__ int pages_of(const DecodeParams& p, int b) {
+  if (p.window_pages_total > 0) return p.window_pages_total;   // sink pages + window pages, same for all b
+  return (seq_len_of(p, b) + 15) >> 4;
+}
+
 // ---------------------------------------------------------------------------
 // plan: prefix[b] = number of pages of sequences 0..b-1  (one CTA)
 // ---------------------------------------------------------------------------
@@ -75,7 +80,7 @@ __global__ void __launch_bounds__(1024) decode_plan_kernel(const DecodeParams p)
   for (int base = 0; base < p.B; base += 1024) {
     const int b = base + tid;
     int pages = 0;
-    if (b < p.B) pages = (seq_len_of(p, b) + 15) >> 4;
+    if (b < p.B) pages = pages_of(p, b);
     int incl = pages;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -142,7 +147,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
     const int i0 = threadIdx.x * chunk, i1 = (i0 + chunk < p.B) ? (i0 + chunk) : p.B;
     int local = 0;
     for (int i = i0; i < i1; ++i) {
-      local += (seq_len_of(p, i) + 15) >> 4;
+      local += pages_of(p, i);
       s_prefix[i + 1] = local;
     }
     int incl = local;
@@ -284,7 +289,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       // every lane takes part in the shuffle; lane 0 issues the copies
       int pid = __shfl_sync(0xffffffffu, tbl_cur, n & 31);
       if (lane == 0) {
-        const int page = p0 + warp + n * W;
+        const int upage = p0 + warp + n * W;
+        const int page = upage < p.sink_pages ? upage : p.win_first_page + (upage - p.sink_pages);
         long long row;
         if (p.mode == kModePaged) {
           if (pid < 0 || (long long)pid >= p.num_pages) {
@@ -334,17 +340,23 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       }
       const uint32_t kbase = stage0 + st * (2 * PAGE_BYTES);
       const uint32_t vbase = kbase + PAGE_BYTES;
-      const int page = p0 + warp + n * W;
-      const int nvalid = (len - page * 16) < 16 ? (len - page * 16) : 16;
+      const int upage = p0 + warp + n * W;
+      const int page = upage < p.sink_pages ? upage : p.win_first_page + (upage - p.sink_pages);
+      // bit t of vmask: token page*16 + t is attended (inside the length, and in the sink or the window)
+      uint32_t vmask;
+      {
+        auto low_bits = [](int n) -> uint32_t { return n <= 0 ? 0u : (n >= 16 ? 0xffffu : ((1u << n) - 1u)); };
+        const int tok0 = page * 16;
+        vmask = low_bits(len - tok0) & (low_bits(p.sink - tok0) | (0xffffu & ~low_bits(p.win_start - tok0)));
+      }
 
-      if (nvalid < 16) {
-        // zero the V rows of tokens past the end so that 0 * garbage cannot make NaN
+      if (vmask != 0xffffu) {
+        // zero the V rows of tokens that are not attended so that 0 * garbage cannot make NaN
         uint8_t* vptr = my_stages + (size_t)st * (2 * PAGE_BYTES) + PAGE_BYTES;
-        const int per_slab = (16 - nvalid) * 8;
-        for (int i = lane; i < per_slab * NSLAB; i += 32) {
-          const int sl = i / per_slab, r = i - sl * per_slab;
-          *reinterpret_cast<uint4*>(vptr + sl * SLAB_BYTES + (nvalid + (r >> 3)) * 128 + (r & 7) * 16) =
-              make_uint4(0, 0, 0, 0);
+        for (int i = lane; i < 16 * 8 * NSLAB; i += 32) {
+          const int sl = i / 128, r = i - sl * 128;      // r: row * 8 + chunk
+          if (!((vmask >> (r >> 3)) & 1u))
+            *reinterpret_cast<uint4*>(vptr + sl * SLAB_BYTES + (r >> 3) * 128 + (r & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         __syncwarp();
       }
@@ -464,19 +476,19 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
             for (int e = 0; e < 4; ++e) {
               const int row = g + (e >> 1) * 8;
               const int tin = 8 * j + cq + (e & 1);
-              if (row < Gb && tin < nvalid)
+              if (row < Gb && ((vmask >> tin) & 1u))
                 p.scores_out[((size_t)b * p.H_Q + head0 + row) * p.N + page * 16 + tin] = si[j][e];
             }
           }
         }
       }
 
-      if (nvalid < 16) {
+      if (vmask != 0xffffu) {
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            if (8 * j + cq + (e & 1) >= nvalid) s[j][e] = -INFINITY;
+            if (!((vmask >> (8 * j + cq + (e & 1))) & 1u)) s[j][e] = -INFINITY;
       }
 
       // ---- online softmax (base 2) ----------------------------------------------
@@ -530,7 +542,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         }
       }
 
-      if (nvalid < 16) fence_proxy_async();  // generic writes to this stage precede its next TMA fill
+      if (vmask != 0xffffu) fence_proxy_async();  // generic writes to this stage precede its next TMA fill
       __syncwarp();
       if (issued < n_my) {
         if ((issued & 31) == 0) {

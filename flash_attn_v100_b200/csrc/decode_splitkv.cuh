@@ -30,6 +30,11 @@ struct DecodeParams {
   int n_gblk;                  // ceil(G / 16): query-head blocks per KV head
   int HV;                      // H_KV * n_gblk
   int mode, fixed_len, N;      // N: tokens per (b, h_kv) row in contiguous modes
+  // Sliding window + attention sink (contiguous fixed mode only): visible tokens are [0, sink) and
+  // [win_start, fixed_len).  The pages of a sequence are the sink pages followed by the window pages:
+  // unit page i maps to page i for i < sink_pages, else to win_first_page + (i - sink_pages).
+  // Without a window: sink = 0, win_start = 0, sink_pages = INT_MAX (identity map).
+  int sink, win_start, sink_pages, win_first_page, window_pages_total;
   int bt_stride;
   long long num_pages;
   int n_cta, stages, slot_rows;

@@ -207,6 +207,36 @@ def forward_decode_fp16(q, k, v, causal, cache_len):
     return _decode_gqa(None, q, k, v, causal, cache_len)
 
 
+def forward_decode_sliding_window_gqa(q, k, v, causal, cache_len, window_size, sink_size):
+    """flash_attn_forward_decode_sliding_window_gqa (flash_attn_kernel.cu:4484-4535).
+    q [B,H_Q,1,D], k/v [B,H_KV,N,D] fp16 -> new [B,H_Q,1,D].  Key j is attended when
+    j < sink_size or window_start <= j <= cache_len, window_start = max(0, min(cache_len+1, N) - window_size)
+    (:4386-4387, :4410-4412).  `causal` has no effect, as in the reference; like the reference, no
+    bound is checked on cache_len, window_size or sink_size."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_input(t, n)
+    _chk(q.dtype == torch.float16, "q must be float16")
+    _chk(k.dtype == torch.float16 and v.dtype == torch.float16, "k and v must be float16")
+    _chk(q.dim() == 4 and k.dim() == 4 and v.dim() == 4, "q, k, v must be 4D tensors")
+    _chk(q.size(2) == 1, "q sequence length must be 1 for decode mode")
+    _same_device(q, k, "q", "k"); _same_device(q, v, "q", "v")
+    _chk(k.shape == v.shape, "k and v must have the same shape")
+    _chk(k.size(0) == q.size(0) and k.size(3) == q.size(3), "k must match q in batch size and head dimension")
+    B, H_Q, _, D = q.shape
+    H_KV, N = k.size(1), k.size(2)
+    _check_gqa_heads(H_Q, H_KV)
+    _chk(D <= MAX_D_LARGE, "D must be <= MAX_D_LARGE(256)")
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        out = torch.empty((B, H_Q, 1, D), dtype=q.dtype, device=q.device)
+        s = _stream_ptr(q.device)
+        ws = _workspace(q.device, s, B, H_Q, H_KV, D)
+        _lib.check(lib.fa_decode_sliding_window_gqa_f16(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H_Q, H_KV, N, D, int(cache_len), int(window_size),
+            int(sink_size), _ptr(ws), ws.numel(), ctypes.c_void_p(s)))
+    return out
+
+
 def forward_continuous_batching_fp16(q, k, v, cache_lens, causal):
     """flash_attn_forward_continuous_batching_fp16 (continuous_batching_kernel.cu:338-406).
     q [B,H_Q,1,D], k/v [B,H_KV,max_N,D] fp16, cache_lens [B] int32; sequence b attends
@@ -499,7 +529,7 @@ def rope_append_paged_fp16(q, k, v, cos, sin, k_cache, v_cache, block_table, pos
 _NOT_BUILT = [
     "forward", "forward_with_lse", "forward_fp16_with_lse", "backward", "async_h2d_transfer", "alloc_pinned_tensor",
     "pipeline_decode_step", "pipeline_decode_step_out", "speculative_verify", "forward_decode_int8_kv_cache_gqa",
-    "token_eviction", "forward_decode_sliding_window_gqa", "cross_gpu_allreduce_fp16", "scatter_heads", "gather_heads",
+    "token_eviction", "cross_gpu_allreduce_fp16", "scatter_heads", "gather_heads",
 ]
 
 

@@ -139,6 +139,24 @@ int fa_decode_gqa_f16(const void* q, const void* k, const void* v, void* out,
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Sliding-window decode with attention sinks over a contiguous cache.  Replaces
+ * flash_attn_forward_decode_sliding_window_gqa (flash_attn_kernel.cu:4484-4535;
+ * kernel :4346-4482; flash_attn.cpp:197, :251).  Layouts as fa_decode_gqa_f16.
+ *   Key j (0 <= j < N) is attended when j < sink_size, or when
+ *   window_start <= j <= cache_len with
+ *   window_start = max(0, min(cache_len + 1, N) - window_size) (:4386-4387, :4410-4412).
+ *   Only the pages that hold attended keys are read.  No bound is placed on
+ *   cache_len, window_size or sink_size, as in the reference.  When no key is
+ *   attended the output is zeros (the reference divides 0 by 0 there).
+ *   The reference's `causal` flag has no effect on its result (:4484-4535) and
+ *   is not part of this signature.
+ */
+int fa_decode_sliding_window_gqa_f16(const void* q, const void* k, const void* v, void* out,
+                                     int B, int H_Q, int H_KV, int N, int D, int cache_len,
+                                     int window_size, int sink_size,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Continuous-batching decode: contiguous cache padded to max_N, one length per
  * sequence.  Replaces flash_attn_forward_continuous_batching_fp16
  * (continuous_batching_kernel.cu:338-406; flash_attn.cpp:243).

@@ -74,6 +74,60 @@ def decode_gqa(q, k, v, causal, cache_len, final_cast=True):
     return continuous_batching_decode(q, k[:, :, :n_vis], v[:, :, :n_vis], lens, False, final_cast)
 
 
+def sliding_window_mask(N, cache_len, window_size, sink_size):
+    """Keys attended by `forward_decode_sliding_window_gqa` (flash_attn_kernel.cu:4386-4387,
+    :4410-4412): j < sink_size, or window_start <= j <= cache_len, with
+    window_start = max(0, min(cache_len + 1, N) - window_size).  The sink is NOT
+    bounded by cache_len.  The reference's test builds the same mask from
+    `mask[:sink] = True; mask[window_start:effective_end] = True` (test_kv_compress.py:265-270)."""
+    effective_end = min(cache_len + 1, N)
+    window_start = max(0, effective_end - window_size)
+    j = torch.arange(N)
+    return (j < sink_size) | ((j >= window_start) & (j <= cache_len))
+
+
+def sliding_window_decode(q, k, v, causal, cache_len, window_size, sink_size, final_cast=True):
+    """Semantics of `forward_decode_sliding_window_gqa` (flash_attn_kernel.cu:4346-4535):
+    fp32 softmax(q.k / sqrt(D)) over the attended keys only, times v; `causal` is ignored
+    by the reference.  A row with no attended key is returned as zeros here (the
+    reference computes 0/0 there, :4476-4480)."""
+    B, H_Q, _, D = q.shape
+    H_KV, N = k.size(1), k.size(2)
+    G = H_Q // H_KV
+    mask = sliding_window_mask(N, int(cache_len), int(window_size), int(sink_size))
+    out = torch.zeros(B, H_Q, 1, D, dtype=torch.float32)
+    if bool(mask.any()):
+        kf = k.float().repeat_interleave(G, dim=1)[:, :, mask]
+        vf = v.float().repeat_interleave(G, dim=1)[:, :, mask]
+        s = torch.einsum("bhqd,bhnd->bhqn", q.float(), kf) * (1.0 / math.sqrt(D))
+        out = torch.einsum("bhqn,bhnd->bhqd", torch.softmax(s, dim=-1), vf)
+    return out.half() if final_cast else out
+
+
+def quantize_kv_int8(kv):
+    """Per-token symmetric int8 quantisation of a KV tensor [B,H,N,D], the helper the
+    reference tests feed `forward_decode_int8_kv_cache_gqa` with (test_kv_compress.py:7-19):
+    scale = max(|x|, over D) / 127 clamped at 1e-8, stored as fp16; q = clamp(round(x / scale))."""
+    x = kv.float()
+    scale = (x.abs().amax(dim=-1, keepdim=True) / 127.0).clamp(min=1e-8)
+    q8 = (x / scale).round().clamp(-128, 127).to(torch.int8)
+    return q8.contiguous(), scale.squeeze(-1).half().contiguous()
+
+
+def dequantize_kv_int8(kv_int8, scale_f16):
+    """Dequantisation inside the reference kernel (flash_attn_kernel.cu:4083-4086):
+    fp16(float(int8) * float(scale_fp16)) per element."""
+    return (kv_int8.float() * scale_f16.float().unsqueeze(-1)).half()
+
+
+def decode_int8_kv_cache_gqa(q, k_int8, v_int8, k_scale, v_scale, cache_len, final_cast=True):
+    """Semantics of `forward_decode_int8_kv_cache_gqa` (flash_attn_kernel.cu:4020-4221): K and V
+    are dequantised to fp16 (see `dequantize_kv_int8`), then keys j <= cache_len (j < N) are
+    attended exactly as in the fp16 GQA decode (:4094-4098)."""
+    return decode_gqa(q, dequantize_kv_int8(k_int8, k_scale), dequantize_kv_int8(v_int8, v_scale), True,
+                      int(cache_len), final_cast)
+
+
 # --------------------------------------------------------------------------
 # SDPA-based oracles
 # --------------------------------------------------------------------------

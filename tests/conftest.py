@@ -23,3 +23,10 @@ def golden():
     import numpy as np
     path = os.path.join(ROOT, "tests", "golden", "reference_oracle_outputs.npz")
     return np.load(path, allow_pickle=False)
+
+
+@pytest.fixture(scope="session")
+def golden_kv_compress():
+    import numpy as np
+    path = os.path.join(ROOT, "tests", "golden", "reference_kv_compress_outputs.npz")
+    return np.load(path, allow_pickle=False)
