@@ -107,12 +107,30 @@ int make_rows_map(CUtensorMap* map, const void* base, long long rows, int D, int
   return FA_OK;
 }
 
+// 2-D map over a [rows, D] int8 tensor: box = min(D, 128) columns x 16 rows; 128-byte swizzle when the
+// box is 128 bytes wide, none for 64-byte rows.
+int make_rows_map_u8(CUtensorMap* map, const void* base, long long rows, int D) {
+  EncodeTiledFn enc;
+  int rc = get_encode(&enc);
+  if (rc != FA_OK) return rc;
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D};
+  cuuint32_t box[2] = {(cuuint32_t)(D < 128 ? D : 128), 16};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, D < 128 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return FA_OK;
+}
+
 // ---- decode tuning ----------------------------------------------------------
 fa::DecodeLaunchConfig g_cfg_override = {0, 0, 0};
 
-fa::DecodeLaunchConfig pick_decode_config(int D, int slot_rows, int B, const DeviceInfo& di) {
+fa::DecodeLaunchConfig pick_decode_config(int D, int slot_rows, int B, int kv_elem_bytes, const DeviceInfo& di) {
   fa::DecodeLaunchConfig c;
-  if (D == 256) c = {4, 2, 1};
+  if (kv_elem_bytes == 1) c = {4, 4, 2};   // int8 cache: pages are half the bytes, so a deeper ring
+  else if (D == 256) c = {4, 2, 1};
   else if (D == 128) c = {4, 2, 2};
   else c = {4, 4, 2};
   if (g_cfg_override.warps > 0) c.warps = g_cfg_override.warps;
@@ -123,7 +141,7 @@ fa::DecodeLaunchConfig pick_decode_config(int D, int slot_rows, int B, const Dev
   // shrink until ctas_per_sm CTAs fit in shared memory
   const size_t sm_total = (size_t)di.max_smem_optin + 1024;  // per-SM capacity = opt-in max + 1 KB reserve
   while (true) {
-    const size_t need = fa::decode_smem_bytes(D, c.warps, c.stages, slot_rows, B);
+    const size_t need = fa::decode_smem_bytes(D, c.warps, c.stages, slot_rows, B, kv_elem_bytes);
     if (need <= (size_t)di.max_smem_optin && (need + 1024) * c.ctas_per_sm <= sm_total) break;
     if (c.ctas_per_sm > 1) --c.ctas_per_sm;
     else if (c.stages > 2) --c.stages;
@@ -154,6 +172,8 @@ struct DecodeCall {
   int B, H_Q, H_KV, D, mode, fixed_len, N, bt_stride;
   long long num_pages, rows_total, max_units;
   bool int8;
+  bool kv8;                          // int8 cache with fp16 per-token scales
+  const void *k_scale_h, *v_scale_h;
   // sliding window + sink (contiguous fixed mode): see DecodeParams.  has_window = false: identity page map
   bool has_window;
   int sink, win_start, sink_pages, win_first_page, window_pages_total;
@@ -175,7 +195,8 @@ int run_decode(const DecodeCall& c) {
     return fail(FA_ERR_WORKSPACE, "decode workspace must be 256-byte aligned");
   if (c.rows_total >= (1ll << 31)) return fail(FA_ERR_UNSUPPORTED, "KV cache has too many rows for one tensor map");
 
-  fa::DecodeLaunchConfig cfg = pick_decode_config(c.D, slot_rows, c.B, di);
+  const int kv_elem_bytes = c.kv8 ? 1 : 2;
+  fa::DecodeLaunchConfig cfg = pick_decode_config(c.D, slot_rows, c.B, kv_elem_bytes, di);
   fa::DecodeParams p;
   memset(&p, 0, sizeof(p));
   p.q = static_cast<const __half*>(c.q);
@@ -185,6 +206,8 @@ int run_decode(const DecodeCall& c) {
   p.q_scale = c.q_scale;
   p.k_scale = c.k_scale;
   p.scores_out = c.scores_out;
+  p.k_scale_h = static_cast<const __half*>(c.k_scale_h);
+  p.v_scale_h = static_cast<const __half*>(c.v_scale_h);
   uint8_t* ws = static_cast<uint8_t*>(c.ws);
   p.status = reinterpret_cast<int32_t*>(ws + fa::kWsStatusOffset);
   p.prefix = reinterpret_cast<int32_t*>(ws + fa::kWsPrefixOffset);
@@ -215,12 +238,13 @@ int run_decode(const DecodeCall& c) {
   p.n_cta = (int)n_cta;
 
   CUtensorMap kmap, vmap;
-  rc = make_rows_map(&kmap, c.k, c.rows_total, c.D, 16);
+  rc = c.kv8 ? make_rows_map_u8(&kmap, c.k, c.rows_total, c.D) : make_rows_map(&kmap, c.k, c.rows_total, c.D, 16);
   if (rc != FA_OK) return rc;
-  rc = make_rows_map(&vmap, c.v, c.rows_total, c.D, 16);
+  rc = c.kv8 ? make_rows_map_u8(&vmap, c.v, c.rows_total, c.D) : make_rows_map(&vmap, c.v, c.rows_total, c.D, 16);
   if (rc != FA_OK) return rc;
-  const size_t smem = fa::decode_smem_bytes(c.D, cfg.warps, cfg.stages, slot_rows, c.B);
-  cudaError_t e = fa::launch_decode(kmap, vmap, p, c.D, c.int8, cfg.warps, smem, c.stream);
+  const size_t smem = fa::decode_smem_bytes(c.D, cfg.warps, cfg.stages, slot_rows, c.B, kv_elem_bytes);
+  const int kind = c.kv8 ? fa::kKindInt8KV : (c.int8 ? fa::kKindInt8QK : fa::kKindF16);
+  cudaError_t e = fa::launch_decode(kmap, vmap, p, c.D, kind, cfg.warps, smem, c.stream);
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, "decode launch failed: %s", cudaGetErrorString(e));
   return FA_OK;
 }
@@ -390,6 +414,28 @@ int fa_decode_int8_gqa(const void* q, const void* k, const void* v, void* out, c
   c.rows_total = (long long)B * H_KV * N;
   c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * ((c.fixed_len + 15) / 16);
   c.int8 = true;
+  c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
+  return run_decode(c);
+}
+
+int fa_decode_int8_kv_cache_gqa(const void* q, const void* k_int8, const void* v_int8, const void* k_scale,
+                                const void* v_scale, void* out, int B, int H_Q, int H_KV, int N, int D, int cache_len,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_decode_common(q, k_int8, v_int8, out, B, H_Q, H_KV, D);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(k_scale && v_scale, "null k_scale / v_scale");
+  FA_REQUIRE(N > 0, "N must be positive");
+  long long len = (long long)cache_len + 1;   // keys j <= cache_len, j < N
+  if (len > N) len = N;
+  if (len < 0) len = 0;
+  DecodeCall c{};
+  c.q = q; c.k = k_int8; c.v = v_int8; c.out = out;
+  c.k_scale_h = k_scale; c.v_scale_h = v_scale;
+  c.B = B; c.H_Q = H_Q; c.H_KV = H_KV; c.D = D;
+  c.mode = fa::kModeContigFixed; c.N = N; c.fixed_len = (int)len;
+  c.rows_total = (long long)B * H_KV * N;
+  c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * ((c.fixed_len + 15) / 16);
+  c.kv8 = true;
   c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
   return run_decode(c);
 }

@@ -60,6 +60,66 @@ __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
   return n < 0 ? 0 : (int)n;
 }
 
+// ---- int8 KV cache helpers ---------------------------------------------------
+// Byte offset of (token row, byte column) inside an int8 K or V page in shared memory: 128-byte-wide
+// slabs of 16 rows with the 128-byte swizzle (16-byte chunk index XOR row), or plain 64-byte rows.
+template <int D>
+__device__ __forceinline__ int kv8_offset(int tok, int byte) {
+  if constexpr (D == 64) {
+    return tok * 64 + byte;
+  } else {
+    const int slab = byte >> 7, chunk = (byte >> 4) & 7;
+    return slab * 2048 + tok * 128 + ((chunk ^ (tok & 7)) << 4) + (byte & 15);
+  }
+}
+
+__device__ __forceinline__ uint32_t hsub_hmul(uint32_t x, uint32_t bias, uint32_t scale) {
+  const __half2 d = __hsub2(*reinterpret_cast<const __half2*>(&x), *reinterpret_cast<const __half2*>(&bias));
+  const __half2 r = __hmul2(d, *reinterpret_cast<const __half2*>(&scale));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// Four consecutive int8 of one token -> two fp16 pairs, each fp16(float(int8) * float(scale)): the
+// byte b is placed in the mantissa of 1024.0 as b ^ 0x80 = b + 128, so 0x6400 | (b ^ 0x80) is the
+// fp16 1152 + b; subtracting 1152 is exact, and the fp16 product with the scale rounds the exact
+// product once, as the conversion from fp32 does.
+__device__ __forceinline__ void dequant_k4(uint32_t w, uint32_t scale2, uint32_t& b0, uint32_t& b1) {
+  const uint32_t u = w ^ 0x80808080u;
+  const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140);
+  const uint32_t hi = __byte_perm(u, 0x64646464u, 0x4342);
+  b0 = hsub_hmul(lo, 0x64806480u, scale2);
+  b1 = hsub_hmul(hi, 0x64806480u, scale2);
+}
+
+// NT bytes [NT*g, NT*g + NT) of V token row `tok` (NT = D / 8) into NT/4 words.
+template <int D>
+__device__ __forceinline__ void load_v_row(const uint8_t* vptr, int tok, int g, uint32_t (&w)[D / 32]) {
+  constexpr int NT = D / 8;
+  if constexpr (NT == 8) {
+    const uint2 t = *reinterpret_cast<const uint2*>(vptr + kv8_offset<D>(tok, NT * g));
+    w[0] = t.x; w[1] = t.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < NT / 16; ++i) {
+      const uint4 t = *reinterpret_cast<const uint4*>(vptr + kv8_offset<D>(tok, NT * g + 16 * i));
+      w[4 * i] = t.x; w[4 * i + 1] = t.y; w[4 * i + 2] = t.z; w[4 * i + 3] = t.w;
+    }
+  }
+}
+
+// Byte J of the words of four token rows (2c, 2c+1 | 2c+8, 2c+9) -> the B fragment of one output
+// tile, dequantised as in dequant_k4, then acc += P * V.
+template <int J>
+__device__ __forceinline__ void dequant_v_pair(uint32_t wa, uint32_t wb, uint32_t wc, uint32_t wd, uint32_t sc_lo,
+                                               uint32_t sc_hi, const uint32_t (&pa)[4], float (&acc)[4]) {
+  constexpr uint32_t sel = ((4u + J) << 12) | ((4u + J) << 8) | (J << 4) | J;  // [a.bJ, a.bJ, b.bJ, b.bJ]
+  uint32_t lo = __byte_perm(wa, wb, sel), hi = __byte_perm(wc, wd, sel);
+  // low byte of each half: x ^ 0x80; high byte: 0x64   (f = a ? (t ^ b) : b, lut 0x6a)
+  asm("lop3.b32 %0, %0, 0x00ff00ff, 0x64806480, 0x6a;" : "+r"(lo));
+  asm("lop3.b32 %0, %0, 0x00ff00ff, 0x64806480, 0x6a;" : "+r"(hi));
+  mma_f16_16816(acc, pa, hsub_hmul(lo, 0x64806480u, sc_lo), hsub_hmul(hi, 0x64806480u, sc_hi));
+}
+
 __device__ __forceinline__ int pages_of(const DecodeParams& p, int b) {
   if (p.window_pages_total > 0) return p.window_pages_total;   // sink pages + window pages, same for all b
   return (seq_len_of(p, b) + 15) >> 4;
@@ -111,13 +171,18 @@ __global__ void __launch_bounds__(1024) decode_plan_kernel(const DecodeParams p)
 // ---------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------
-template <int D, bool INT8>
+template <int D, int KIND>
 __global__ void __launch_bounds__(256)
 decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
                       const __grid_constant__ CUtensorMap vmap, const DecodeParams p) {
-  constexpr int PAGE_BYTES = 16 * D * 2;
-  constexpr int SLAB_BYTES = 16 * 128;  // 16 rows x 64 columns of fp16
-  constexpr int NSLAB = D / 64;
+  constexpr bool INT8 = KIND == kKindInt8QK;   // fp16 cache, K and Q quantised on the fly for the scores
+  constexpr bool KV8 = KIND == kKindInt8KV;    // int8 cache with per-token fp16 scales
+  constexpr int PAGE_BYTES = 16 * D * (KV8 ? 1 : 2);
+  // One TMA box: 16 rows x 128 bytes (64 fp16 or 128 int8 columns), 128-byte swizzle;
+  // D = 64 int8 rows are 64 bytes wide and are copied unswizzled.
+  constexpr int SLAB_BYTES = (KV8 && D == 64) ? 16 * 64 : 16 * 128;
+  constexpr int SLAB_COLS = KV8 ? (D == 64 ? 64 : 128) : 64;
+  constexpr int NSLAB = D / SLAB_COLS;
   constexpr int NT = D / 8;  // 8-column output tiles
   constexpr int ROWLEN = D + 2;
 
@@ -226,13 +291,25 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
 
     // Q fragments (A operand).  Rows >= Gb are zero.
     constexpr int QREGS = INT8 ? (D / 32) : (D / 16);
+    // KV8: the contraction index of k-step t, fragment slot pair (2c,2c+1 | 2c+8,2c+9) of lane c = lane & 3
+    // stands for head dimensions d0 .. d0+3 with d0 = 128 * (t / KPS) + 4 * KPS * c + 4 * (t % KPS):
+    // a lane then reads 16 consecutive int8 of a token row for four k-steps.  Q uses the same map.
+    constexpr int KPS = (D >= 128) ? 8 : 4;
     uint32_t qa[QREGS][4];
     float q_s0 = 1.f, q_s1 = 1.f;
     {
       const bool v0 = g < Gb, v1 = (g + 8) < Gb;
       const __half* q0 = p.q + ((size_t)b * p.H_Q + head0 + g) * D;
       const __half* q1 = q0 + (size_t)8 * D;
-      if constexpr (!INT8) {
+      if constexpr (KV8) {
+#pragma unroll
+        for (int t = 0; t < D / 16; ++t) {
+          const int d0 = 128 * (t / KPS) + 4 * KPS * (lane & 3) + 4 * (t % KPS);
+          const uint2 a = v0 ? __ldg(reinterpret_cast<const uint2*>(q0 + d0)) : make_uint2(0u, 0u);
+          const uint2 c = v1 ? __ldg(reinterpret_cast<const uint2*>(q1 + d0)) : make_uint2(0u, 0u);
+          qa[t][0] = a.x; qa[t][1] = c.x; qa[t][2] = a.y; qa[t][3] = c.y;
+        }
+      } else if constexpr (!INT8) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           qa[kk][0] = v0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + kk * 16 + cq)) : 0u;
@@ -307,8 +384,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         mbar_expect_tx(bar, 2 * PAGE_BYTES);
 #pragma unroll
         for (int sl = 0; sl < NSLAB; ++sl) {
-          tma_load_2d(dst + sl * SLAB_BYTES, &kmap, sl * 64, (int)row, bar, policy);
-          tma_load_2d(dst + PAGE_BYTES + sl * SLAB_BYTES, &vmap, sl * 64, (int)row, bar, policy);
+          tma_load_2d(dst + sl * SLAB_BYTES, &kmap, sl * SLAB_COLS, (int)row, bar, policy);
+          tma_load_2d(dst + PAGE_BYTES + sl * SLAB_BYTES, &vmap, sl * SLAB_COLS, (int)row, bar, policy);
         }
       }
       ++it_issue;
@@ -316,6 +393,31 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
 
     int issued = 0;
     for (; issued < S && issued < n_my; ++issued) issue(issued);
+
+    // bit t of the result: token page*16 + t is attended (inside the length, and in the sink or the window)
+    auto page_of = [&](int n) -> int {
+      const int upage = p0 + warp + n * W;
+      return upage < p.sink_pages ? upage : p.win_first_page + (upage - p.sink_pages);
+    };
+    auto vmask_of = [&](int page) -> uint32_t {
+      auto low_bits = [](int n) -> uint32_t { return n <= 0 ? 0u : (n >= 16 ? 0xffffu : ((1u << n) - 1u)); };
+      const int tok0 = page * 16;
+      return low_bits(len - tok0) & (low_bits(p.sink - tok0) | (0xffffu & ~low_bits(p.win_start - tok0)));
+    };
+
+    // KV8: fp16 scales of the next page, fetched one page ahead: lanes 0-15 hold the K scale of token
+    // `lane`, lanes 16-31 the V scale of token `lane - 16`; tokens that are not attended get scale 0,
+    // so that whatever the cache holds there dequantises to zero.
+    uint32_t sc_cur = 0, sc_next = 0;
+    auto load_sc = [&](int n) -> uint32_t {
+      if (n >= n_my) return 0u;
+      const int page = page_of(n);
+      const int t = lane & 15;
+      if (!((vmask_of(page) >> t) & 1u)) return 0u;
+      const __half* base = (lane < 16) ? p.k_scale_h : p.v_scale_h;
+      return __ldg(reinterpret_cast<const unsigned short*>(base) + ((size_t)b * p.H_KV + h_kv) * p.N + page * 16 + t);
+    };
+    if constexpr (KV8) sc_next = load_sc(0);
 
     // INT8: per-token K scales of the next page, fetched one page ahead.
     float ks_cur = 1.f, ks_next = 1.f;
@@ -332,6 +434,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         ks_cur = ks_next;
         ks_next = load_ks(n + 1);
       }
+      if constexpr (KV8) {
+        sc_cur = sc_next;
+        sc_next = load_sc(n + 1);
+      }
       const uint32_t st = it_cons % (uint32_t)S;
       const uint32_t parity = (it_cons / (uint32_t)S) & 1u;
       ++it_cons;
@@ -340,17 +446,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       }
       const uint32_t kbase = stage0 + st * (2 * PAGE_BYTES);
       const uint32_t vbase = kbase + PAGE_BYTES;
-      const int upage = p0 + warp + n * W;
-      const int page = upage < p.sink_pages ? upage : p.win_first_page + (upage - p.sink_pages);
-      // bit t of vmask: token page*16 + t is attended (inside the length, and in the sink or the window)
-      uint32_t vmask;
-      {
-        auto low_bits = [](int n) -> uint32_t { return n <= 0 ? 0u : (n >= 16 ? 0xffffu : ((1u << n) - 1u)); };
-        const int tok0 = page * 16;
-        vmask = low_bits(len - tok0) & (low_bits(p.sink - tok0) | (0xffffu & ~low_bits(p.win_start - tok0)));
-      }
+      const int page = page_of(n);
+      const uint32_t vmask = vmask_of(page);
 
-      if (vmask != 0xffffu) {
+      if (!KV8 && vmask != 0xffffu) {
         // zero the V rows of tokens that are not attended so that 0 * garbage cannot make NaN
         uint8_t* vptr = my_stages + (size_t)st * (2 * PAGE_BYTES) + PAGE_BYTES;
         for (int i = lane; i < 16 * 8 * NSLAB; i += 32) {
@@ -363,7 +462,33 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
 
       // ---- S = Q K^T : [16 heads x 16 tokens] ------------------------------------
       float s[2][4];
-      if constexpr (!INT8) {
+      if constexpr (KV8) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        const uint8_t* kptr = my_stages + (size_t)st * (2 * PAGE_BYTES);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int tok = 8 * j + g;  // token of this lane's B-fragment column
+          const uint32_t sc16 = __shfl_sync(0xffffffffu, sc_cur, tok);
+          const uint32_t sc2 = sc16 | (sc16 << 16);
+#pragma unroll
+          for (int q4 = 0; q4 < D / 64; ++q4) {  // 16 bytes = four k-steps per load
+            const int byte0 = 128 * ((q4 * 4) / KPS) + 4 * KPS * (lane & 3) + 4 * ((q4 * 4) % KPS);
+            const uint4 w4 = *reinterpret_cast<const uint4*>(kptr + kv8_offset<D>(tok, byte0));
+            const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t b0, b1;
+              dequant_k4(w[i], sc2, b0, b1);
+              mma_f16_16816(s[j], qa[q4 * 4 + i], b0, b1);
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[j][e] *= p.scale_log2;
+      } else if constexpr (!INT8) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
         const int mi = lane >> 3;
@@ -528,7 +653,30 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       }
 
       // ---- O += P V --------------------------------------------------------------
-      {
+      if constexpr (KV8) {
+        // Lane (g, c) reads the NT bytes [NT*g, NT*g + NT) of token rows 2c, 2c+1, 2c+8, 2c+9: byte nt is
+        // column g of output tile nt, so accumulator column n of tile nt is head dimension NT*n + nt.
+        const uint8_t* vptr = my_stages + (size_t)st * (2 * PAGE_BYTES) + PAGE_BYTES;
+        const int c2 = (lane & 3) * 2;
+        const uint32_t s_a = __shfl_sync(0xffffffffu, sc_cur, 16 + c2);
+        const uint32_t s_b = __shfl_sync(0xffffffffu, sc_cur, 16 + c2 + 1);
+        const uint32_t s_c = __shfl_sync(0xffffffffu, sc_cur, 16 + c2 + 8);
+        const uint32_t s_d = __shfl_sync(0xffffffffu, sc_cur, 16 + c2 + 9);
+        const uint32_t sc_lo = s_a | (s_b << 16), sc_hi = s_c | (s_d << 16);
+        constexpr int NW = NT / 4;  // 32-bit words per lane and token row
+        uint32_t va[NW], vb[NW], vc[NW], vd[NW];
+        load_v_row<D>(vptr, c2, g, va);
+        load_v_row<D>(vptr, c2 + 1, g, vb);
+        load_v_row<D>(vptr, c2 + 8, g, vc);
+        load_v_row<D>(vptr, c2 + 9, g, vd);
+#pragma unroll
+        for (int wd = 0; wd < NW; ++wd) {
+          dequant_v_pair<0>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 0]);
+          dequant_v_pair<1>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 1]);
+          dequant_v_pair<2>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 2]);
+          dequant_v_pair<3>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 3]);
+        }
+      } else {
         const int mi = lane >> 3;
         const int r = (lane & 7) + (mi & 1) * 8;
 #pragma unroll
@@ -542,7 +690,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         }
       }
 
-      if (vmask != 0xffffu) fence_proxy_async();  // generic writes to this stage precede its next TMA fill
+      if (!KV8 && vmask != 0xffffu) fence_proxy_async();  // generic writes to this stage precede its next TMA fill
       __syncwarp();
       if (issued < n_my) {
         if ((issued & 31) == 0) {
@@ -564,8 +712,14 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       if (g < Gb) {
         float* rowp = mb + g * ROWLEN;
 #pragma unroll
-        for (int i = 0; i < NT; ++i)
-          *reinterpret_cast<float2*>(rowp + i * 8 + cq) = make_float2(acc[i][0], acc[i][1]);
+        for (int i = 0; i < NT; ++i) {
+          if constexpr (KV8) {
+            rowp[NT * cq + i] = acc[i][0];
+            rowp[NT * (cq + 1) + i] = acc[i][1];
+          } else {
+            *reinterpret_cast<float2*>(rowp + i * 8 + cq) = make_float2(acc[i][0], acc[i][1]);
+          }
+        }
         if ((lane & 3) == 0) {
           rowp[D] = m0;
           rowp[D + 1] = l0;
@@ -574,8 +728,14 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       if (g + 8 < Gb) {
         float* rowp = mb + (g + 8) * ROWLEN;
 #pragma unroll
-        for (int i = 0; i < NT; ++i)
-          *reinterpret_cast<float2*>(rowp + i * 8 + cq) = make_float2(acc[i][2], acc[i][3]);
+        for (int i = 0; i < NT; ++i) {
+          if constexpr (KV8) {
+            rowp[NT * cq + i] = acc[i][2];
+            rowp[NT * (cq + 1) + i] = acc[i][3];
+          } else {
+            *reinterpret_cast<float2*>(rowp + i * 8 + cq) = make_float2(acc[i][2], acc[i][3]);
+          }
+        }
         if ((lane & 3) == 0) {
           rowp[D] = m1;
           rowp[D + 1] = l1;
@@ -664,10 +824,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
   }
 }
 
-template <int D, bool INT8>
+template <int D, int KIND>
 cudaError_t launch_t(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p,
                      int warps, size_t smem_bytes, cudaStream_t stream) {
-  auto kern = decode_splitkv_kernel<D, INT8>;
+  auto kern = decode_splitkv_kernel<D, KIND>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
   if (e != cudaSuccess) return e;
   if (p.B + 1 > kMaxSmemPrefix) decode_plan_kernel<<<1, 1024, 0, stream>>>(p);  // else scanned in-kernel
@@ -677,9 +837,9 @@ cudaError_t launch_t(const CUtensorMap& kmap, const CUtensorMap& vmap, const Dec
 
 }  // namespace
 
-size_t decode_smem_bytes(int D, int warps, int stages, int slot_rows, int B) {
+size_t decode_smem_bytes(int D, int warps, int stages, int slot_rows, int B, int kv_elem_bytes) {
   size_t bytes = 1024;  // slack to align the first stage to 1024 B (128-byte swizzle atom)
-  bytes += (size_t)warps * stages * (2 * 16 * D * 2);
+  bytes += (size_t)warps * stages * (2 * 16 * D * kv_elem_bytes);
   bytes += (size_t)warps * stages * 8;
   bytes += (size_t)warps * slot_rows * (D + 2) * 4;
   if (B + 1 <= kMaxSmemPrefix) bytes += (size_t)(B + 1) * 4;
@@ -698,20 +858,20 @@ size_t decode_workspace_bytes(int B, int H_Q, int H_KV, int D, int max_ctas) {
 }
 
 cudaError_t launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p,
-                          int D, bool int8, int warps, size_t smem_bytes, cudaStream_t stream) {
+                          int D, int kind, int warps, size_t smem_bytes, cudaStream_t stream) {
+#define FA_DECODE_CASE(DD)                                                                          \
+  case DD:                                                                                          \
+    if (kind == kKindInt8QK) return launch_t<DD, kKindInt8QK>(kmap, vmap, p, warps, smem_bytes, stream); \
+    if (kind == kKindInt8KV) return launch_t<DD, kKindInt8KV>(kmap, vmap, p, warps, smem_bytes, stream); \
+    return launch_t<DD, kKindF16>(kmap, vmap, p, warps, smem_bytes, stream);
   switch (D) {
-    case 64:
-      return int8 ? launch_t<64, true>(kmap, vmap, p, warps, smem_bytes, stream)
-                  : launch_t<64, false>(kmap, vmap, p, warps, smem_bytes, stream);
-    case 128:
-      return int8 ? launch_t<128, true>(kmap, vmap, p, warps, smem_bytes, stream)
-                  : launch_t<128, false>(kmap, vmap, p, warps, smem_bytes, stream);
-    case 256:
-      return int8 ? launch_t<256, true>(kmap, vmap, p, warps, smem_bytes, stream)
-                  : launch_t<256, false>(kmap, vmap, p, warps, smem_bytes, stream);
+    FA_DECODE_CASE(64)
+    FA_DECODE_CASE(128)
+    FA_DECODE_CASE(256)
     default:
       return cudaErrorInvalidValue;
   }
+#undef FA_DECODE_CASE
 }
 
 }  // namespace fa

@@ -13,6 +13,12 @@ enum DecodeMode : int {
   kModeContigFixed = 2,   // len = fixed_len for every sequence; rows contiguous
 };
 
+enum DecodeKind : int {
+  kKindF16 = 0,     // fp16 cache, fp16 arithmetic
+  kKindInt8QK = 1,  // fp16 cache; Q and K quantised in the kernel, integer score dot products
+  kKindInt8KV = 2,  // int8 cache with one fp16 scale per token, dequantised in the kernel
+};
+
 struct DecodeParams {
   const __half* q;             // [B, H_Q, 1, D]
   __half* out;                 // [B, H_Q, 1, D]
@@ -21,6 +27,8 @@ struct DecodeParams {
   const float* q_scale;        // int8 only: [B, H_Q]
   const float* k_scale;        // int8 only: [B, H_KV, N]
   int32_t* scores_out;         // int8 only, optional: [B, H_Q, N]
+  const __half* k_scale_h;     // int8 cache only: [B, H_KV, N] fp16
+  const __half* v_scale_h;     // int8 cache only: [B, H_KV, N] fp16
   int32_t* prefix;             // workspace: [B + 1] running page counts
   float* partials;             // workspace: [n_cta][2][slot_rows][D + 2]
   unsigned long long* counters;  // workspace: [B * HV] (epoch << 32 | arrivals) per segment
@@ -55,10 +63,11 @@ constexpr size_t kWsPrefixOffset = 256;   // int32 prefix[B + 1]
 
 // Launch the decode on `stream` (one kernel; a prefix-sum pre-pass only when B is too large for
 // the in-kernel scan).  kmap/vmap are 2-D tensor maps over
-// K and V seen as [rows, D] fp16 with a 64-column x 16-row box and 128-byte swizzle.
+// K and V seen as [rows, D] fp16 with a 64-column x 16-row box and 128-byte swizzle; for the int8
+// cache, [rows, D] bytes with a min(D, 128)-column x 16-row box (128-byte swizzle, none for D = 64).
 cudaError_t launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p,
-                          int D, bool int8, int warps, size_t smem_bytes, cudaStream_t stream);
+                          int D, int kind, int warps, size_t smem_bytes, cudaStream_t stream);
 
-size_t decode_smem_bytes(int D, int warps, int stages, int slot_rows, int B);
+size_t decode_smem_bytes(int D, int warps, int stages, int slot_rows, int B, int kv_elem_bytes);
 
 }  // namespace fa

@@ -237,6 +237,45 @@ def forward_decode_sliding_window_gqa(q, k, v, causal, cache_len, window_size, s
     return out
 
 
+def forward_decode_int8_kv_cache_gqa(q, k_int8, v_int8, k_scale, v_scale, cache_len):
+    """flash_attn_forward_decode_int8_kv_cache_gqa (flash_attn_kernel.cu:4164-4221).
+    q [B,H_Q,1,D] fp16; k_int8/v_int8 [B,H_KV,N,D] int8; k_scale/v_scale [B,H_KV,N] fp16 (one scale per
+    cached token) -> new [B,H_Q,1,D] fp16.  Elements are dequantised as fp16(float(int8) * float(scale))
+    (:4083-4086) and keys j <= cache_len are attended (:4094-4098)."""
+    for t, n in ((q, "q"), (k_int8, "k_int8"), (v_int8, "v_int8"), (k_scale, "k_scale"), (v_scale, "v_scale")):
+        _check_input(t, n)
+    _chk(q.dtype == torch.float16, "q must be float16")
+    _chk(k_int8.dtype == torch.int8, "k_int8 must be int8")
+    _chk(v_int8.dtype == torch.int8, "v_int8 must be int8")
+    _chk(k_scale.dtype == torch.float16, "k_scale must be float16")
+    _chk(v_scale.dtype == torch.float16, "v_scale must be float16")
+    _chk(q.dim() == 4 and k_int8.dim() == 4 and v_int8.dim() == 4, "q, k_int8, v_int8 must be 4D tensors")
+    _chk(k_scale.dim() == 3 and v_scale.dim() == 3, "k_scale and v_scale must be 3D tensors")
+    _chk(q.size(2) == 1, "q sequence length must be 1 for decode mode")
+    for t, n in ((k_int8, "k_int8"), (v_int8, "v_int8"), (k_scale, "k_scale"), (v_scale, "v_scale")):
+        _same_device(q, t, "q", n)
+    B, H_Q, _, D = q.shape
+    H_KV, N = k_int8.size(1), k_int8.size(2)
+    _check_gqa_heads(H_Q, H_KV)
+    _chk(D <= MAX_D_LARGE, "D must be <= MAX_D_LARGE(256)")
+    _chk(k_int8.size(3) == D, "k_int8 last dim must match D")
+    _chk(v_int8.size(3) == D, "v_int8 last dim must match D")
+    _chk(k_int8.size(0) == B and v_int8.shape == k_int8.shape, "k_int8 and v_int8 must be [B, H_KV, N, D]")
+    _chk(k_scale.size(2) == N, "k_scale size mismatch")
+    _chk(v_scale.size(2) == N, "v_scale size mismatch")
+    _chk(tuple(k_scale.shape) == (B, H_KV, N) and tuple(v_scale.shape) == (B, H_KV, N),
+         "k_scale and v_scale must be [B, H_KV, N]")
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        out = torch.empty((B, H_Q, 1, D), dtype=q.dtype, device=q.device)
+        s = _stream_ptr(q.device)
+        ws = _workspace(q.device, s, B, H_Q, H_KV, D)
+        _lib.check(lib.fa_decode_int8_kv_cache_gqa(
+            _ptr(q), _ptr(k_int8), _ptr(v_int8), _ptr(k_scale), _ptr(v_scale), _ptr(out), B, H_Q, H_KV, N, D,
+            int(cache_len), _ptr(ws), ws.numel(), ctypes.c_void_p(s)))
+    return out
+
+
 def forward_continuous_batching_fp16(q, k, v, cache_lens, causal):
     """flash_attn_forward_continuous_batching_fp16 (continuous_batching_kernel.cu:338-406).
     q [B,H_Q,1,D], k/v [B,H_KV,max_N,D] fp16, cache_lens [B] int32; sequence b attends
@@ -528,7 +567,7 @@ def rope_append_paged_fp16(q, k, v, cos, sin, k_cache, v_cache, block_table, pos
 # --------------------------------------------------------------------------
 _NOT_BUILT = [
     "forward", "forward_with_lse", "forward_fp16_with_lse", "backward", "async_h2d_transfer", "alloc_pinned_tensor",
-    "pipeline_decode_step", "pipeline_decode_step_out", "speculative_verify", "forward_decode_int8_kv_cache_gqa",
+    "pipeline_decode_step", "pipeline_decode_step_out", "speculative_verify",
     "token_eviction", "cross_gpu_allreduce_fp16", "scatter_heads", "gather_heads",
 ]
 

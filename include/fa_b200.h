@@ -157,6 +157,23 @@ int fa_decode_sliding_window_gqa_f16(const void* q, const void* k, const void* v
                                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Decode over an INT8 KV cache with one fp16 scale per cached token.  Replaces
+ * flash_attn_forward_decode_int8_kv_cache_gqa (flash_attn_kernel.cu:4164-4221;
+ * kernel :4020-4162; flash_attn.cpp:183, :249).
+ *   q [B,H_Q,1,D] fp16; k_int8 / v_int8 [B,H_KV,N,D] int8; k_scale / v_scale
+ *   [B,H_KV,N] fp16; out [B,H_Q,1,D] fp16.
+ *   Every cache element is dequantised as fp16(float(int8) * float(scale)) before
+ *   use (:4083-4086), bit for bit; keys j <= cache_len (j < N) are attended
+ *   (:4094-4098); fp32 softmax and accumulation.  cache_len is not bounded, as
+ *   in the reference; cache_len < 0 gives zeros.  Scales of tokens that are not
+ *   attended are never read.
+ */
+int fa_decode_int8_kv_cache_gqa(const void* q, const void* k_int8, const void* v_int8,
+                                const void* k_scale, const void* v_scale, void* out,
+                                int B, int H_Q, int H_KV, int N, int D, int cache_len,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Continuous-batching decode: contiguous cache padded to max_N, one length per
  * sequence.  Replaces flash_attn_forward_continuous_batching_fp16
  * (continuous_batching_kernel.cu:338-406; flash_attn.cpp:243).
