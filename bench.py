@@ -2,7 +2,7 @@
 """Benchmark of the attention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--workload paged_decode|varlen_prefill|int8_decode|contig_decode]
+                    [--workload paged_decode|varlen_prefill|int8_decode|contig_decode|int8_kv_decode|sliding_window_decode]
 
 Default workload (the headline): paged GQA decode, B=64, 32 query / 8 KV heads,
 D=128, fp16, 16-token pages, seq_lens uniform in [512, 8192], block table a
@@ -250,6 +250,73 @@ class Int8Decode:
     step_e2e = None
 
 
+class Int8KVDecode:
+    """Decode over an INT8 KV cache with per-token fp16 scales (same shape as the int8 score workload)."""
+    name = "int8_kv_decode"
+    metric = "int8_kv_cache_gqa_decode_tokens_per_s"
+    unit = "tokens/s"
+    bound = "hbm"
+    dtype = "int8 cache dequantised to fp16 in registers, fp32 accumulate"
+    B, H_Q, H_KV, D, N = 32, 32, 8, 128, 8192
+
+    def __init__(self, device, seed):
+        self.device = device
+        gd = torch.Generator(device=device).manual_seed(seed)
+        self.q = torch.randn(self.B, self.H_Q, 1, self.D, generator=gd, device=device, dtype=torch.float16)
+        shape = (self.B, self.H_KV, self.N, self.D)
+        self.k8 = torch.randint(-127, 128, shape, generator=gd, device=device, dtype=torch.int8)
+        self.v8 = torch.randint(-127, 128, shape, generator=gd, device=device, dtype=torch.int8)
+        # absmax/127 scales of N(0,1) rows of 128 values: about 3/127
+        self.ks = (torch.rand(shape[:3], generator=gd, device=device) * 0.01 + 0.02).half()
+        self.vs = (torch.rand(shape[:3], generator=gd, device=device) * 0.01 + 0.02).half()
+        self.units_per_step = self.B
+        self.alg_bytes = (2 * self.B * self.H_KV * self.N * self.D + 2 * self.ks.numel() * 2 +
+                          2 * self.B * self.H_Q * self.D * 2)
+        self.alg_flops = 4 * self.H_Q * self.D * self.N * self.B
+        self.launches_per_step = 1
+
+    def config(self):
+        return {"workload": "int8_kv_cache_gqa_decode B=32 H_Q=32 H_KV=8 D=128 N=8192 cache_len=8191",
+                "l2": "inputs larger than L2 (K/V 537 MB), no flush"}
+
+    def step(self, fa):
+        return fa.forward_decode_int8_kv_cache_gqa(self.q, self.k8, self.v8, self.ks, self.vs, self.N - 1)
+
+    step_e2e = None
+
+
+class SlidingWindowDecode:
+    """Sliding-window + sink decode: the window and the sink are read, the rest of the cache is not."""
+    name = "sliding_window_decode"
+    metric = "sliding_window_gqa_decode_tokens_per_s"
+    unit = "tokens/s"
+    bound = "hbm"
+    dtype = "fp16"
+    B, H_Q, H_KV, D, N, WINDOW, SINK = 128, 32, 8, 128, 8192, 4096, 4
+
+    def __init__(self, device, seed):
+        self.device = device
+        gd = torch.Generator(device=device).manual_seed(seed)
+        self.q = torch.randn(self.B, self.H_Q, 1, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.k = torch.randn(self.B, self.H_KV, self.N, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.v = torch.randn(self.B, self.H_KV, self.N, self.D, generator=gd, device=device, dtype=torch.float16)
+        self.units_per_step = self.B
+        pages = (self.SINK + 15) // 16 + self.WINDOW // 16      # window ends at N, page aligned
+        self.alg_bytes = self.B * self.H_KV * pages * 16 * self.D * 2 * 2 + 2 * self.B * self.H_Q * self.D * 2
+        self.alg_flops = 4 * self.H_Q * self.D * (self.WINDOW + self.SINK) * self.B
+        self.launches_per_step = 1
+
+    def config(self):
+        return {"workload": "sliding_window_gqa_decode B=128 H_Q=32 H_KV=8 D=128 N=8192 cache_len=8191 window=4096 sink=4",
+                "l2": "pages read per step (2.15 GB) larger than L2, no flush",
+                "bytes": "whole 16-token pages that hold an attended key"}
+
+    def step(self, fa):
+        return fa.forward_decode_sliding_window_gqa(self.q, self.k, self.v, True, self.N - 1, self.WINDOW, self.SINK)
+
+    step_e2e = None
+
+
 class VarlenPrefill:
     name = "varlen_prefill"
     metric = "varlen_causal_gqa_prefill_tflops"
@@ -288,7 +355,7 @@ class VarlenPrefill:
     step_e2e = None
 
 
-WORKLOADS = {w.name: w for w in (PagedDecode, ContigDecode, Int8Decode, VarlenPrefill)}
+WORKLOADS = {w.name: w for w in (PagedDecode, ContigDecode, Int8Decode, Int8KVDecode, SlidingWindowDecode, VarlenPrefill)}
 
 
 def run_engine(args):

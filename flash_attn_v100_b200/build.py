@@ -53,7 +53,8 @@ def find_nvcc() -> str:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB_PATH
-    cmd = [find_nvcc(), *NVCC_FLAGS, "-I", INCLUDE, "-o", LIB_PATH, *sources()]
+    extra = os.environ.get("FA_B200_NVCC_FLAGS", "").split()   # e.g. -DFA_KV8_MINB=4 for tuning experiments
+    cmd = [find_nvcc(), *NVCC_FLAGS, *extra, "-I", INCLUDE, "-o", LIB_PATH, *sources()]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

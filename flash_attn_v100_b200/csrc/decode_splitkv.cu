@@ -60,6 +60,35 @@ __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
   return n < 0 ? 0 : (int)n;
 }
 
+// MMA on the query-head block.  HM ("half M"): the block has at most 8 heads, so fragment rows 8-15 are
+// all-zero padding: their A registers are passed as zero and their accumulators are not kept.
+template <bool HM>
+__device__ __forceinline__ void mma_rows(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (HM) {
+    float d2, d3;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, "
+        "{%0,%1,%9,%9};"
+        : "+f"(c[0]), "+f"(c[1]), "=f"(d2), "=f"(d3)
+        : "r"(a[0]), "r"(0u), "r"(a[2]), "r"(b0), "r"(b1), "f"(0.f));
+  } else {
+    mma_f16_16816(c, a, b0, b1);
+  }
+}
+template <bool HM>
+__device__ __forceinline__ void mma_s8_rows(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (HM) {
+    int d2, d3;
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, "
+        "{%0,%1,%5,%5};"
+        : "+r"(c[0]), "+r"(c[1]), "=r"(d2), "=r"(d3)
+        : "r"(a[0]), "r"(0u), "r"(a[2]), "r"(b0), "r"(b1));
+  } else {
+    mma_s8_16832(c, a, b0, b1);
+  }
+}
+
 // ---- int8 KV cache helpers ---------------------------------------------------
 // Byte offset of (token row, byte column) inside an int8 K or V page in shared memory: 128-byte-wide
 // slabs of 16 rows with the 128-byte swizzle (16-byte chunk index XOR row), or plain 64-byte rows.
@@ -79,16 +108,16 @@ __device__ __forceinline__ uint32_t hsub_hmul(uint32_t x, uint32_t bias, uint32_
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-// Four consecutive int8 of one token -> two fp16 pairs, each fp16(float(int8) * float(scale)): the
-// byte b is placed in the mantissa of 1024.0 as b ^ 0x80 = b + 128, so 0x6400 | (b ^ 0x80) is the
-// fp16 1152 + b; subtracting 1152 is exact, and the fp16 product with the scale rounds the exact
-// product once, as the conversion from fp32 does.
-__device__ __forceinline__ void dequant_k4(uint32_t w, uint32_t scale2, uint32_t& b0, uint32_t& b1) {
+// int8 -> fp16 without a conversion instruction: the byte b is placed in the mantissa of 1024.0 as
+// b ^ 0x80 = b + 128, so 0x6400 | (b ^ 0x80) is the fp16 number 1152 + b, exactly.  For V, 1152 is
+// subtracted (exact) and the fp16 product with the token's scale rounds the exact product once, as
+// the reference's fp16(float(int8) * float(scale)) does (hsub_hmul).
+// Four consecutive int8 -> two fp16 pairs holding 1152 + b each (exact); the caller removes the
+// constant from the finished dot product.
+__device__ __forceinline__ void dequant_k4_biased(uint32_t w, uint32_t& b0, uint32_t& b1) {
   const uint32_t u = w ^ 0x80808080u;
-  const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140);
-  const uint32_t hi = __byte_perm(u, 0x64646464u, 0x4342);
-  b0 = hsub_hmul(lo, 0x64806480u, scale2);
-  b1 = hsub_hmul(hi, 0x64806480u, scale2);
+  b0 = __byte_perm(u, 0x64646464u, 0x4140);
+  b1 = __byte_perm(u, 0x64646464u, 0x4342);
 }
 
 // NT bytes [NT*g, NT*g + NT) of V token row `tok` (NT = D / 8) into NT/4 words.
@@ -109,7 +138,7 @@ __device__ __forceinline__ void load_v_row(const uint8_t* vptr, int tok, int g, 
 
 // Byte J of the words of four token rows (2c, 2c+1 | 2c+8, 2c+9) -> the B fragment of one output
 // tile, dequantised as in dequant_k4, then acc += P * V.
-template <int J>
+template <int J, bool HM>
 __device__ __forceinline__ void dequant_v_pair(uint32_t wa, uint32_t wb, uint32_t wc, uint32_t wd, uint32_t sc_lo,
                                                uint32_t sc_hi, const uint32_t (&pa)[4], float (&acc)[4]) {
   constexpr uint32_t sel = ((4u + J) << 12) | ((4u + J) << 8) | (J << 4) | J;  // [a.bJ, a.bJ, b.bJ, b.bJ]
@@ -117,7 +146,7 @@ __device__ __forceinline__ void dequant_v_pair(uint32_t wa, uint32_t wb, uint32_
   // low byte of each half: x ^ 0x80; high byte: 0x64   (f = a ? (t ^ b) : b, lut 0x6a)
   asm("lop3.b32 %0, %0, 0x00ff00ff, 0x64806480, 0x6a;" : "+r"(lo));
   asm("lop3.b32 %0, %0, 0x00ff00ff, 0x64806480, 0x6a;" : "+r"(hi));
-  mma_f16_16816(acc, pa, hsub_hmul(lo, 0x64806480u, sc_lo), hsub_hmul(hi, 0x64806480u, sc_hi));
+  mma_rows<HM>(acc, pa, hsub_hmul(lo, 0x64806480u, sc_lo), hsub_hmul(hi, 0x64806480u, sc_hi));
 }
 
 __device__ __forceinline__ int pages_of(const DecodeParams& p, int b) {
@@ -171,12 +200,29 @@ __global__ void __launch_bounds__(1024) decode_plan_kernel(const DecodeParams p)
 // ---------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------
-template <int D, int KIND>
-__global__ void __launch_bounds__(256)
+#ifndef FA_F16_MINB
+#define FA_F16_MINB 2
+#endif
+#ifndef FA_KV8_MINB
+#define FA_KV8_MINB 3
+#endif
+// Threads per CTA and CTAs per SM the kernel is compiled for.  The half-M variants keep half the
+// accumulators, which leaves room for more resident CTAs (more pages in flight, more warps to hide
+// the dequantisation latency); they run with at most 4 warps.
+template <int D, int KIND, bool HM>
+struct DecodeOccupancy {
+  static constexpr int kThreads = HM ? 128 : 256;
+  static constexpr int kMinBlocks =
+      !HM ? 1 : (D == 64 ? 4 : (D == 256 ? 2 : (KIND == kKindF16 ? FA_F16_MINB : (KIND == kKindInt8KV ? FA_KV8_MINB : 2))));
+};
+
+template <int D, int KIND, bool HM>
+__global__ void __launch_bounds__(DecodeOccupancy<D, KIND, HM>::kThreads, DecodeOccupancy<D, KIND, HM>::kMinBlocks)
 decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
                       const __grid_constant__ CUtensorMap vmap, const DecodeParams p) {
   constexpr bool INT8 = KIND == kKindInt8QK;   // fp16 cache, K and Q quantised on the fly for the scores
   constexpr bool KV8 = KIND == kKindInt8KV;    // int8 cache with per-token fp16 scales
+  constexpr int NR = HM ? 2 : 4;               // live accumulator registers per fragment (rows g | g, g + 8)
   constexpr int PAGE_BYTES = 16 * D * (KV8 ? 1 : 2);
   // One TMA box: 16 rows x 128 bytes (64 fp16 or 128 int8 columns), 128-byte swizzle;
   // D = 64 int8 rows are 64 bytes wide and are copied unswizzled.
@@ -257,7 +303,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
   const uint64_t policy = l2_policy_evict_first();
   const uint32_t bar0 = smem_u32(bars + warp * S);
   const uint32_t stage0 = smem_u32(my_stages);
-  uint32_t it_issue = 0, it_cons = 0;  // running item counters of this warp (ring position / phase)
+  // ring position of the next page to issue / to consume, and the phase parity of the consumer side
+  uint32_t st_issue = 0, st_cons = 0, par_cons = 0;
 
   // locate the sequence that holds unit u: largest b with HV * pre[b] <= u
   int b;
@@ -297,8 +344,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
     constexpr int KPS = (D >= 128) ? 8 : 4;
     uint32_t qa[QREGS][4];
     float q_s0 = 1.f, q_s1 = 1.f;
+    float kbias0 = 0.f, kbias1 = 0.f;  // KV8 only
     {
-      const bool v0 = g < Gb, v1 = (g + 8) < Gb;
+      const bool v0 = g < Gb, v1 = !HM && (g + 8) < Gb;
       const __half* q0 = p.q + ((size_t)b * p.H_Q + head0 + g) * D;
       const __half* q1 = q0 + (size_t)8 * D;
       if constexpr (KV8) {
@@ -308,7 +356,21 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           const uint2 a = v0 ? __ldg(reinterpret_cast<const uint2*>(q0 + d0)) : make_uint2(0u, 0u);
           const uint2 c = v1 ? __ldg(reinterpret_cast<const uint2*>(q1 + d0)) : make_uint2(0u, 0u);
           qa[t][0] = a.x; qa[t][1] = c.x; qa[t][2] = a.y; qa[t][3] = c.y;
+          const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x));
+          const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+          const float2 c0 = __half22float2(*reinterpret_cast<const __half2*>(&c.x));
+          const float2 c1 = __half22float2(*reinterpret_cast<const __half2*>(&c.y));
+          kbias0 += (a0.x + a0.y) + (a1.x + a1.y);
+          kbias1 += (c0.x + c0.y) + (c1.x + c1.y);
         }
+        // K enters the score product as the fp16 number 1152 + k (see dequant_k4_biased), so every raw
+        // score carries 1152 * sum_d q[d]; that constant of the query row is taken off again in fp32.
+        kbias0 += __shfl_xor_sync(0xffffffffu, kbias0, 1);
+        kbias0 += __shfl_xor_sync(0xffffffffu, kbias0, 2);
+        kbias1 += __shfl_xor_sync(0xffffffffu, kbias1, 1);
+        kbias1 += __shfl_xor_sync(0xffffffffu, kbias1, 2);
+        kbias0 *= 1152.f;
+        kbias1 *= 1152.f;
       } else if constexpr (!INT8) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -378,7 +440,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         } else {
           row = contig_row0 + (long long)page * 16;
         }
-        const uint32_t st = it_issue % (uint32_t)S;
+        const uint32_t st = st_issue;
         const uint32_t bar = bar0 + st * 8;
         const uint32_t dst = stage0 + st * (2 * PAGE_BYTES);
         mbar_expect_tx(bar, 2 * PAGE_BYTES);
@@ -388,7 +450,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           tma_load_2d(dst + PAGE_BYTES + sl * SLAB_BYTES, &vmap, sl * SLAB_COLS, (int)row, bar, policy);
         }
       }
-      ++it_issue;
+      st_issue = (st_issue + 1 == (uint32_t)S) ? 0u : st_issue + 1;
     };
 
     int issued = 0;
@@ -409,11 +471,12 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
     // `lane`, lanes 16-31 the V scale of token `lane - 16`; tokens that are not attended get scale 0,
     // so that whatever the cache holds there dequantises to zero.
     uint32_t sc_cur = 0, sc_next = 0;
+    uint32_t vmask_next = n_my > 0 ? vmask_of(page_of(0)) : 0u;
     auto load_sc = [&](int n) -> uint32_t {
       if (n >= n_my) return 0u;
       const int page = page_of(n);
       const int t = lane & 15;
-      if (!((vmask_of(page) >> t) & 1u)) return 0u;
+      if (!((vmask_next >> t) & 1u)) return 0u;
       const __half* base = (lane < 16) ? p.k_scale_h : p.v_scale_h;
       return __ldg(reinterpret_cast<const unsigned short*>(base) + ((size_t)b * p.H_KV + h_kv) * p.N + page * 16 + t);
     };
@@ -434,20 +497,24 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         ks_cur = ks_next;
         ks_next = load_ks(n + 1);
       }
+      const uint32_t vmask = vmask_next;
+      vmask_next = (n + 1 < n_my) ? vmask_of(page_of(n + 1)) : 0u;
       if constexpr (KV8) {
         sc_cur = sc_next;
         sc_next = load_sc(n + 1);
       }
-      const uint32_t st = it_cons % (uint32_t)S;
-      const uint32_t parity = (it_cons / (uint32_t)S) & 1u;
-      ++it_cons;
+      const uint32_t st = st_cons;
+      const uint32_t parity = par_cons;
+      if (++st_cons == (uint32_t)S) {
+        st_cons = 0;
+        par_cons ^= 1u;
+      }
       if (!mbar_wait(bar0 + st * 8, parity)) {
         if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
       }
       const uint32_t kbase = stage0 + st * (2 * PAGE_BYTES);
       const uint32_t vbase = kbase + PAGE_BYTES;
       const int page = page_of(n);
-      const uint32_t vmask = vmask_of(page);
 
       if (!KV8 && vmask != 0xffffu) {
         // zero the V rows of tokens that are not attended so that 0 * garbage cannot make NaN
@@ -467,27 +534,37 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
         const uint8_t* kptr = my_stages + (size_t)st * (2 * PAGE_BYTES);
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int tok = 8 * j + g;  // token of this lane's B-fragment column
-          const uint32_t sc16 = __shfl_sync(0xffffffffu, sc_cur, tok);
-          const uint32_t sc2 = sc16 | (sc16 << 16);
+        for (int q4 = 0; q4 < D / 64; ++q4) {  // 16 bytes = four k-steps per load; token g and token g + 8
+          const int byte0 = 128 * ((q4 * 4) / KPS) + 4 * KPS * (lane & 3) + 4 * ((q4 * 4) % KPS);
+          const uint4 wa = *reinterpret_cast<const uint4*>(kptr + kv8_offset<D>(g, byte0));
+          const uint4 wb = *reinterpret_cast<const uint4*>(kptr + kv8_offset<D>(g + 8, byte0));
+          const uint32_t w0[4] = {wa.x, wa.y, wa.z, wa.w};
+          const uint32_t w1[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-          for (int q4 = 0; q4 < D / 64; ++q4) {  // 16 bytes = four k-steps per load
-            const int byte0 = 128 * ((q4 * 4) / KPS) + 4 * KPS * (lane & 3) + 4 * ((q4 * 4) % KPS);
-            const uint4 w4 = *reinterpret_cast<const uint4*>(kptr + kv8_offset<D>(tok, byte0));
-            const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t b0, b1;
-              dequant_k4(w[i], sc2, b0, b1);
-              mma_f16_16816(s[j], qa[q4 * 4 + i], b0, b1);
-            }
+          for (int i = 0; i < 4; ++i) {
+            uint32_t b0, b1;
+            dequant_k4_biased(w0[i], b0, b1);
+            mma_rows<HM>(s[0], qa[q4 * 4 + i], b0, b1);
+            dequant_k4_biased(w1[i], b0, b1);
+            mma_rows<HM>(s[1], qa[q4 * 4 + i], b0, b1);
           }
         }
+        // score = (raw - 1152 * sum q) * k_scale[token] / sqrt(D), in fp32, to base 2.  The per-element
+        // product k * k_scale is not rounded to fp16 first: the score is the exact-dequantisation score
+        // up to fp32 rounding.
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) s[j][e] *= p.scale_log2;
+        for (int j = 0; j < 2; ++j) {
+          const uint32_t ka = __shfl_sync(0xffffffffu, sc_cur, 8 * j + cq);
+          const uint32_t kb = __shfl_sync(0xffffffffu, sc_cur, 8 * j + cq + 1);
+          const float ta = __half2float(__ushort_as_half((unsigned short)ka)) * p.scale_log2;
+          const float tb = __half2float(__ushort_as_half((unsigned short)kb)) * p.scale_log2;
+          s[j][0] = (s[j][0] - kbias0) * ta;
+          s[j][1] = (s[j][1] - kbias0) * tb;
+          if constexpr (!HM) {
+            s[j][2] = (s[j][2] - kbias1) * ta;
+            s[j][3] = (s[j][3] - kbias1) * tb;
+          }
+        }
       } else if constexpr (!INT8) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -499,13 +576,13 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           const uint32_t addr = kbase + (chunk >> 3) * SLAB_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
           uint32_t kb[4];
           ldmatrix_x4(kb, addr);
-          mma_f16_16816(s[0], qa[kk], kb[0], kb[1]);
-          mma_f16_16816(s[1], qa[kk], kb[2], kb[3]);
+          mma_rows<HM>(s[0], qa[kk], kb[0], kb[1]);
+          mma_rows<HM>(s[1], qa[kk], kb[2], kb[3]);
         }
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) s[j][e] *= p.scale_log2;
+          for (int e = 0; e < NR; ++e) s[j][e] *= p.scale_log2;
       } else {
         int si[2][4];
 #pragma unroll
@@ -586,7 +663,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-          for (int kk = 0; kk < D / 32; ++kk) mma_s8_16832(si[j], qa[kk], bq[j][kk][0], bq[j][kk][1]);
+          for (int kk = 0; kk < D / 32; ++kk) mma_s8_rows<HM>(si[j], qa[kk], bq[j][kk][0], bq[j][kk][1]);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const float ks_a = __shfl_sync(0xffffffffu, ks_cur, 8 * j + cq);
@@ -594,11 +671,13 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           // score = float(dot) * q_s * k_s * scale, then to base 2
           s[j][0] = ((static_cast<float>(si[j][0]) * q_s0) * ks_a) * p.scale * 1.4426950408889634f;
           s[j][1] = ((static_cast<float>(si[j][1]) * q_s0) * ks_b) * p.scale * 1.4426950408889634f;
-          s[j][2] = ((static_cast<float>(si[j][2]) * q_s1) * ks_a) * p.scale * 1.4426950408889634f;
-          s[j][3] = ((static_cast<float>(si[j][3]) * q_s1) * ks_b) * p.scale * 1.4426950408889634f;
+          if constexpr (!HM) {
+            s[j][2] = ((static_cast<float>(si[j][2]) * q_s1) * ks_a) * p.scale * 1.4426950408889634f;
+            s[j][3] = ((static_cast<float>(si[j][3]) * q_s1) * ks_b) * p.scale * 1.4426950408889634f;
+          }
           if (p.scores_out != nullptr) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < NR; ++e) {
               const int row = g + (e >> 1) * 8;
               const int tin = 8 * j + cq + (e & 1);
               if (row < Gb && ((vmask >> tin) & 1u))
@@ -612,43 +691,54 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
+          for (int e = 0; e < NR; ++e)
             if (!((vmask >> (8 * j + cq + (e & 1))) & 1u)) s[j][e] = -INFINITY;
       }
 
       // ---- online softmax (base 2) ----------------------------------------------
       float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-      float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-      const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
+      const float mn0 = fmaxf(m0, mx0);
+      const float a0 = fast_exp2(m0 - mn0);
       m0 = mn0;
-      m1 = mn1;
       float pr[2][4];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         pr[j][0] = fast_exp2(s[j][0] - mn0);
         pr[j][1] = fast_exp2(s[j][1] - mn0);
-        pr[j][2] = fast_exp2(s[j][2] - mn1);
-        pr[j][3] = fast_exp2(s[j][3] - mn1);
       }
       l0 = l0 * a0 + (pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1]);
-      l1 = l1 * a1 + (pr[0][2] + pr[0][3] + pr[1][2] + pr[1][3]);
+      float a1 = 1.f;
       uint32_t pa[4];
       pa[0] = pack_half2(pr[0][0], pr[0][1]);
-      pa[1] = pack_half2(pr[0][2], pr[0][3]);
       pa[2] = pack_half2(pr[1][0], pr[1][1]);
-      pa[3] = pack_half2(pr[1][2], pr[1][3]);
+      pa[1] = pa[3] = 0u;
+      if constexpr (!HM) {
+        float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn1 = fmaxf(m1, mx1);
+        a1 = fast_exp2(m1 - mn1);
+        m1 = mn1;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          pr[j][2] = fast_exp2(s[j][2] - mn1);
+          pr[j][3] = fast_exp2(s[j][3] - mn1);
+        }
+        l1 = l1 * a1 + (pr[0][2] + pr[0][3] + pr[1][2] + pr[1][3]);
+        pa[1] = pack_half2(pr[0][2], pr[0][3]);
+        pa[3] = pack_half2(pr[1][2], pr[1][3]);
+      }
       if (__any_sync(0xffffffffu, (a0 != 1.f) || (a1 != 1.f))) {
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
           acc[i][0] *= a0;
           acc[i][1] *= a0;
-          acc[i][2] *= a1;
-          acc[i][3] *= a1;
+          if constexpr (!HM) {
+            acc[i][2] *= a1;
+            acc[i][3] *= a1;
+          }
         }
       }
 
@@ -671,10 +761,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         load_v_row<D>(vptr, c2 + 9, g, vd);
 #pragma unroll
         for (int wd = 0; wd < NW; ++wd) {
-          dequant_v_pair<0>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 0]);
-          dequant_v_pair<1>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 1]);
-          dequant_v_pair<2>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 2]);
-          dequant_v_pair<3>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 3]);
+          dequant_v_pair<0, HM>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 0]);
+          dequant_v_pair<1, HM>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 1]);
+          dequant_v_pair<2, HM>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 2]);
+          dequant_v_pair<3, HM>(va[wd], vb[wd], vc[wd], vd[wd], sc_lo, sc_hi, pa, acc[wd * 4 + 3]);
         }
       } else {
         const int mi = lane >> 3;
@@ -685,8 +775,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           const uint32_t addr = vbase + (chunk >> 3) * SLAB_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
           uint32_t vb[4];
           ldmatrix_x4_trans(vb, addr);
-          mma_f16_16816(acc[2 * c2], pa, vb[0], vb[1]);
-          mma_f16_16816(acc[2 * c2 + 1], pa, vb[2], vb[3]);
+          mma_rows<HM>(acc[2 * c2], pa, vb[0], vb[1]);
+          mma_rows<HM>(acc[2 * c2 + 1], pa, vb[2], vb[3]);
         }
       }
 
@@ -705,8 +795,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
     // ---- merge the warps of this CTA ---------------------------------------------
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if constexpr (!HM) {
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    }
     {
       float* mb = mbuf + (size_t)warp * p.slot_rows * ROWLEN;
       if (g < Gb) {
@@ -725,7 +817,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           rowp[D + 1] = l0;
         }
       }
-      if (g + 8 < Gb) {
+      if (!HM && g + 8 < Gb) {
         float* rowp = mb + (g + 8) * ROWLEN;
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
@@ -824,10 +916,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
   }
 }
 
-template <int D, int KIND>
+template <int D, int KIND, bool HM>
 cudaError_t launch_t(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p,
                      int warps, size_t smem_bytes, cudaStream_t stream) {
-  auto kern = decode_splitkv_kernel<D, KIND>;
+  auto kern = decode_splitkv_kernel<D, KIND, HM>;
+  if (warps * 32 > DecodeOccupancy<D, KIND, HM>::kThreads) return cudaErrorInvalidConfiguration;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
   if (e != cudaSuccess) return e;
   if (p.B + 1 > kMaxSmemPrefix) decode_plan_kernel<<<1, 1024, 0, stream>>>(p);  // else scanned in-kernel
@@ -859,11 +952,14 @@ size_t decode_workspace_bytes(int B, int H_Q, int H_KV, int D, int max_ctas) {
 
 cudaError_t launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeParams& p,
                           int D, int kind, int warps, size_t smem_bytes, cudaStream_t stream) {
-#define FA_DECODE_CASE(DD)                                                                          \
-  case DD:                                                                                          \
-    if (kind == kKindInt8QK) return launch_t<DD, kKindInt8QK>(kmap, vmap, p, warps, smem_bytes, stream); \
-    if (kind == kKindInt8KV) return launch_t<DD, kKindInt8KV>(kmap, vmap, p, warps, smem_bytes, stream); \
-    return launch_t<DD, kKindF16>(kmap, vmap, p, warps, smem_bytes, stream);
+#define FA_DECODE_KIND(DD, KK)                                                              \
+  return p.G <= 8 ? launch_t<DD, KK, true>(kmap, vmap, p, warps, smem_bytes, stream)        \
+                  : launch_t<DD, KK, false>(kmap, vmap, p, warps, smem_bytes, stream);
+#define FA_DECODE_CASE(DD)                               \
+  case DD:                                               \
+    if (kind == kKindInt8QK) { FA_DECODE_KIND(DD, kKindInt8QK) } \
+    if (kind == kKindInt8KV) { FA_DECODE_KIND(DD, kKindInt8KV) } \
+    FA_DECODE_KIND(DD, kKindF16)
   switch (D) {
     FA_DECODE_CASE(64)
     FA_DECODE_CASE(128)
@@ -872,6 +968,7 @@ cudaError_t launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, cons
       return cudaErrorInvalidValue;
   }
 #undef FA_DECODE_CASE
+#undef FA_DECODE_KIND
 }
 
 }  // namespace fa

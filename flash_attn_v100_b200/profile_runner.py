@@ -16,7 +16,8 @@ import torch
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="paged_decode",
-                    choices=["paged_decode", "int8_decode", "varlen_prefill", "contig_decode"])
+                    choices=["paged_decode", "int8_decode", "varlen_prefill", "contig_decode", "int8_kv_decode",
+                             "sliding_window_decode"])
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--seed", type=int, default=0)
@@ -48,6 +49,23 @@ def main():
         else:
             run = lambda: fa.forward_decode_gqa_fp16(q, k, v, True, N - 1)
         print(f"case {args.case}: B={args.batch} N={N} kv_bytes={args.batch * H_KV * N * D * 4}")
+    elif args.case == "int8_kv_decode":
+        N = 8192
+        q = torch.randn(args.batch, H_Q, 1, D, generator=g, device=dev, dtype=torch.float16)
+        k8 = torch.randint(-127, 128, (args.batch, H_KV, N, D), generator=g, device=dev, dtype=torch.int8)
+        v8 = torch.randint(-127, 128, (args.batch, H_KV, N, D), generator=g, device=dev, dtype=torch.int8)
+        ks = (torch.rand(args.batch, H_KV, N, generator=g, device=dev) * 0.01 + 0.02).half()
+        vs = (torch.rand(args.batch, H_KV, N, generator=g, device=dev) * 0.01 + 0.02).half()
+        run = lambda: fa.forward_decode_int8_kv_cache_gqa(q, k8, v8, ks, vs, N - 1)
+        print(f"case int8_kv_decode: B={args.batch} N={N} kv_bytes={args.batch * H_KV * N * (D * 2 + 4)}")
+    elif args.case == "sliding_window_decode":
+        N, window, sink = 8192, 4096, 4
+        q = torch.randn(args.batch, H_Q, 1, D, generator=g, device=dev, dtype=torch.float16)
+        k = torch.randn(args.batch, H_KV, N, D, generator=g, device=dev, dtype=torch.float16)
+        v = torch.randn(args.batch, H_KV, N, D, generator=g, device=dev, dtype=torch.float16)
+        run = lambda: fa.forward_decode_sliding_window_gqa(q, k, v, True, N - 1, window, sink)
+        print(f"case sliding_window_decode: B={args.batch} N={N} window={window} sink={sink} "
+              f"kv_bytes={args.batch * H_KV * (window + 16) * D * 4}")
     else:
         gl = torch.Generator().manual_seed(args.seed)
         lens = torch.randint(128, 4097, (args.batch,), generator=gl).tolist()
