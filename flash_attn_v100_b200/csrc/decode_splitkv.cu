@@ -206,6 +206,9 @@ __global__ void __launch_bounds__(1024) decode_plan_kernel(const DecodeParams p)
 #ifndef FA_KV8_MINB
 #define FA_KV8_MINB 3
 #endif
+#ifndef FA_I8QK_MINB
+#define FA_I8QK_MINB 2
+#endif
 // Threads per CTA and CTAs per SM the kernel is compiled for.  The half-M variants keep half the
 // accumulators, which leaves room for more resident CTAs (more pages in flight, more warps to hide
 // the dequantisation latency); they run with at most 4 warps.
@@ -213,7 +216,7 @@ template <int D, int KIND, bool HM>
 struct DecodeOccupancy {
   static constexpr int kThreads = HM ? 128 : 256;
   static constexpr int kMinBlocks =
-      !HM ? 1 : (D == 64 ? 4 : (D == 256 ? 2 : (KIND == kKindF16 ? FA_F16_MINB : (KIND == kKindInt8KV ? FA_KV8_MINB : 2))));
+      !HM ? 1 : (D == 64 ? 4 : (D == 256 ? 2 : (KIND == kKindF16 ? FA_F16_MINB : (KIND == kKindInt8KV ? FA_KV8_MINB : FA_I8QK_MINB))));
 };
 
 template <int D, int KIND, bool HM>
