@@ -33,16 +33,67 @@ namespace fa {
 
 namespace {
 
-__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
-  uint64_t ra = *reinterpret_cast<uint64_t*>(&a), rb = *reinterpret_cast<uint64_t*>(&b), rd;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
-  return *reinterpret_cast<float2*>(&rd);
-}
 __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   uint64_t ra = *reinterpret_cast<uint64_t*>(&a), rb = *reinterpret_cast<uint64_t*>(&b), rd;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
   return *reinterpret_cast<float2*>(&rd);
 }
+
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  uint64_t ra = *reinterpret_cast<uint64_t*>(&a), rb = *reinterpret_cast<uint64_t*>(&b),
+           rc = *reinterpret_cast<uint64_t*>(&c), rd;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  return *reinterpret_cast<float2*>(&rd);
+}
+// max(a, |b|, |c|), NaN if any operand is NaN
+__device__ __forceinline__ float fmax3_abs_nan(float a, float b, float c) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(fabsf(b)), "f"(fabsf(c)));
+  return d;
+}
+
+// clamp(roundf(x / s), -127, 127) exactly as IEEE fp32 evaluates it (the reference's quantiser)
+__device__ __forceinline__ uint32_t quant_exact1(float x, float s) {
+  const float t = fmaxf(-127.f, fminf(127.f, roundf(__fdiv_rn(x, s))));
+  return static_cast<uint32_t>(static_cast<int>(t)) & 0xffu;
+}
+
+// Exact quantisation of K[tok][d] of an fp16 K page in shared memory (64-column slabs of 16 rows,
+// 128-byte swizzle).  Out of line: it runs for a few values per page.
+template <int SLAB_BYTES>
+__device__ __noinline__ uint32_t quant_exact_elem(const uint8_t* kptr, int tok, int d, float s) {
+  const int ch = d >> 3;
+  const __half v = *reinterpret_cast<const __half*>(kptr + (ch >> 3) * SLAB_BYTES + tok * 128 +
+                                                    (((ch & 7) ^ (tok & 7)) << 4) + (d & 7) * 2);
+  return quant_exact1(__half2float(v), s);
+}
+
+// Fast quantisation of four values (two half2 registers) of one token, rcp = 1 / scale:
+//   yn = -(x * rcp + 1.5 * 2^23)   one FMA: the low mantissa byte is rint(x * rcp) as int8
+//   rn = yn + 1.5 * 2^23           = -rint(x * rcp), exact
+//   u  = x * rcp + rn              = the distance to the nearest integer
+// Returns the four bytes; umax / rmax collect max |u| and max |rint| (NaN-propagating), from which
+// the caller decides whether any value needs the exact path (near a rounding tie, beyond the clamp
+// range, NaN or Inf).
+__device__ __forceinline__ uint32_t quant_fast4(uint32_t h01, uint32_t h23, float rcp, float& umax, float& rmax) {
+  const float kMagic = 12582912.f;
+  const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+  const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+  const float2 nr = make_float2(-rcp, -rcp), pr = make_float2(rcp, rcp);
+  const float2 nm = make_float2(-kMagic, -kMagic), pm = make_float2(kMagic, kMagic);
+  const float2 y01 = ffma2(f01, nr, nm), y23 = ffma2(f23, nr, nm);
+  const float2 r01 = fadd2(y01, pm), r23 = fadd2(y23, pm);
+  const float2 u01 = ffma2(f01, pr, r01), u23 = ffma2(f23, pr, r23);
+  umax = fmax3_abs_nan(umax, u01.x, u01.y);
+  umax = fmax3_abs_nan(umax, u23.x, u23.y);
+  rmax = fmax3_abs_nan(rmax, r01.x, r01.y);
+  rmax = fmax3_abs_nan(rmax, r23.x, r23.y);
+  return __byte_perm(__byte_perm(__float_as_uint(y01.x), __float_as_uint(y01.y), 0x0040),
+                     __byte_perm(__float_as_uint(y23.x), __float_as_uint(y23.y), 0x0040), 0x5410);
+}
+// |u| at or above this, or |rint| above 127.5: the fast result may differ from the IEEE quotient's
+// rounding (|x * rcp - x / s| < 2.3e-5 for |x / s| < 128), so the value is redone exactly.
+constexpr float kQuantTieGuard = 0.49997f;
 
 constexpr int kMaxSmemPrefix = 4096;  // B + 1 <= this: prefix sums are staged in shared memory
 
@@ -385,26 +436,21 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       } else {
         if (v0) q_s0 = __ldg(p.q_scale + (size_t)b * p.H_Q + head0 + g);
         if (v1) q_s1 = __ldg(p.q_scale + (size_t)b * p.H_Q + head0 + g + 8);
+        // Slot 4c+i of k-step kk of the int8 MMA stands for head dimension
+        // 32*kk + {2c, 2c+1, 8+2c, 9+2c}[i], slot 16+4c+i for the same plus 16: these are the values a
+        // lane holds after ldmatrix of the fp16 K tile, so K needs no shuffling before it is quantised.
         auto quant4 = [](const __half* src, float s) -> uint32_t {
-          const uint2 raw2 = __ldg(reinterpret_cast<const uint2*>(src));
-          const __half2 h01 = *reinterpret_cast<const __half2*>(&raw2.x);
-          const __half2 h23 = *reinterpret_cast<const __half2*>(&raw2.y);
-          const float f[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
-          uint32_t packed = 0;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float t = fmaxf(-127.f, fminf(127.f, roundf(__fdiv_rn(f[i], s))));
-            packed |= (static_cast<uint32_t>(static_cast<int>(t)) & 0xffu) << (8 * i);
-          }
-          return packed;
+          const __half2 h01 = __ldg(reinterpret_cast<const __half2*>(src));
+          const __half2 h23 = __ldg(reinterpret_cast<const __half2*>(src + 8));
+          return quant_exact1(__low2float(h01), s) | (quant_exact1(__high2float(h01), s) << 8) |
+                 (quant_exact1(__low2float(h23), s) << 16) | (quant_exact1(__high2float(h23), s) << 24);
         };
-        const int c4 = (lane & 3) * 4;
 #pragma unroll
         for (int kk = 0; kk < D / 32; ++kk) {
-          qa[kk][0] = v0 ? quant4(q0 + kk * 32 + c4, q_s0) : 0u;
-          qa[kk][1] = v1 ? quant4(q1 + kk * 32 + c4, q_s1) : 0u;
-          qa[kk][2] = v0 ? quant4(q0 + kk * 32 + 16 + c4, q_s0) : 0u;
-          qa[kk][3] = v1 ? quant4(q1 + kk * 32 + 16 + c4, q_s1) : 0u;
+          qa[kk][0] = v0 ? quant4(q0 + kk * 32 + cq, q_s0) : 0u;
+          qa[kk][1] = v1 ? quant4(q1 + kk * 32 + cq, q_s1) : 0u;
+          qa[kk][2] = v0 ? quant4(q0 + kk * 32 + 16 + cq, q_s0) : 0u;
+          qa[kk][3] = v1 ? quant4(q1 + kk * 32 + 16 + cq, q_s1) : 0u;
         }
       }
     }
@@ -590,83 +636,69 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         int si[2][4];
 #pragma unroll
         for (int j = 0; j < 2; ++j) si[j][0] = si[j][1] = si[j][2] = si[j][3] = 0;
-        const uint8_t* kptr = my_stages + (size_t)st * (2 * PAGE_BYTES);
-        // Quantise four consecutive K values of one token: clamp(roundf(k / k_s), -127, 127) in IEEE
-        // fp32, bit for bit.  Fast path: multiply by the reciprocal and round with the 1.5*2^23
-        // trick.  For |t| < 127.5 the product differs from the correctly rounded quotient by < 2.3e-5,
-        // which changes the result only next to a rounding boundary (x.5); those values, exact ties
-        // (round-half-away differs from the trick's round-half-even) and values beyond the clamp
-        // range are flagged and redone exactly.  The fast path is branch-free so that the sixteen
-        // independent quantisations of a page interleave.
-        auto load_k4 = [&](int row, int d, float (&f)[4]) {
-          const int chunk = d >> 3;  // 16-byte chunk within the row
-          const uint8_t* src = kptr + (chunk >> 3) * SLAB_BYTES + row * 128 +
-                               (((chunk & 7) ^ (row & 7)) << 4) + (d & 7) * 2;
-          const uint2 raw2 = *reinterpret_cast<const uint2*>(src);
-          const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&raw2.x));
-          const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&raw2.y));
-          f[0] = f01.x; f[1] = f01.y; f[2] = f23.x; f[3] = f23.y;
-        };
-        auto quant_fast = [&](int row, int d, float rcp, bool& flagged) -> uint32_t {
-          float f[4];
-          load_k4(row, d, f);
-          const float2 t01 = fmul2(make_float2(f[0], f[1]), make_float2(rcp, rcp));
-          const float2 t23 = fmul2(make_float2(f[2], f[3]), make_float2(rcp, rcp));
-          const float2 mg = make_float2(12582912.f, 12582912.f), ng = make_float2(-12582912.f, -12582912.f);
-          const float2 y01 = fadd2(t01, mg), y23 = fadd2(t23, mg);
-          const float2 r01 = fadd2(y01, ng), r23 = fadd2(y23, ng);          // rint(t)
-          const float2 u01 = fadd2(t01, make_float2(-r01.x, -r01.y));
-          const float2 u23 = fadd2(t23, make_float2(-r23.x, -r23.y));
-          const float umax = fmaxf(fmaxf(fabsf(u01.x), fabsf(u01.y)), fmaxf(fabsf(u23.x), fabsf(u23.y)));
-          const float tmax = fmaxf(fmaxf(fabsf(t01.x), fabsf(t01.y)), fmaxf(fabsf(t23.x), fabsf(t23.y)));
-          flagged = !(umax <= 0.49997f) || !(tmax <= 127.4f);   // also catches NaN / Inf
-          return __byte_perm(__byte_perm(__float_as_uint(y01.x), __float_as_uint(y01.y), 0x0040),
-                             __byte_perm(__float_as_uint(y23.x), __float_as_uint(y23.y), 0x0040), 0x5410);
-        };
-        auto quant_exact = [&](int row, int d, float ksr) -> uint32_t {
-          float f[4];
-          load_k4(row, d, f);
-          uint32_t packed = 0;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float t = fmaxf(-127.f, fminf(127.f, roundf(__fdiv_rn(f[i], ksr))));
-            packed |= (static_cast<uint32_t>(static_cast<int>(t)) & 0xffu) << (8 * i);
-          }
-          return packed;
-        };
-        const int c4 = (lane & 3) * 4;
+        // K scale of the token of this lane's B-fragment column in each n-tile (tokens g and g + 8)
+        const float ksr0 = __shfl_sync(0xffffffffu, ks_cur, g);
+        const float ksr1 = __shfl_sync(0xffffffffu, ks_cur, g + 8);
+        const float rcp0 = __frcp_rn(ksr0), rcp1 = __frcp_rn(ksr1);
+        float um[D / 16], rmax = 0.f;   // max |distance to the nearest integer| per 16-wide slice, max |rint|
         uint32_t bq[2][D / 32][2];
-        float ksr[2];
-        uint32_t tie_mask = 0;
+        const int mi = lane >> 3;
+        const int lrow = (lane & 7) + (mi >> 1) * 8;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int row = 8 * j + g;  // token within the page owned by this lane in the B fragment
-          ksr[j] = __shfl_sync(0xffffffffu, ks_cur, row);
-          const float rcp = __frcp_rn(ksr[j]);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const int chunk = 2 * kk + (mi & 1);
+          const uint32_t addr = kbase + (chunk >> 3) * SLAB_BYTES + lrow * 128 + (((chunk & 7) ^ (lrow & 7)) << 4);
+          uint32_t kb[4];
+          ldmatrix_x4(kb, addr);
+          um[kk] = 0.f;
+          bq[0][kk >> 1][kk & 1] = quant_fast4(kb[0], kb[1], rcp0, um[kk], rmax);
+          bq[1][kk >> 1][kk & 1] = quant_fast4(kb[2], kb[3], rcp1, um[kk], rmax);
+        }
+        float umax = um[0];
 #pragma unroll
-          for (int kk = 0; kk < D / 32; ++kk) {
+        for (int kk = 1; kk < D / 16; kk += 2) umax = fmax3_abs_nan(umax, um[kk], kk + 1 < D / 16 ? um[kk + 1] : 0.f);
+        const bool redo = !(umax < kQuantTieGuard) || !(rmax <= 127.5f);   // NaN-safe
+        if (__any_sync(0xffffffffu, redo)) {
+          // Some value of some lane sits next to a rounding boundary (exact ties are common with
+          // absmax / 127 scales) or beyond the clamp range.  The 16-wide slices concerned are redone with
+          // the IEEE division by the whole warp: for one (lane L, slice) at a time, lanes 0-7 each
+          // quantise one of L's eight values of that slice (two tokens x four values) and the bytes
+          // are gathered back into L's fragment registers.
+          uint32_t todo = 0;
+          if (redo) {
+            const bool all = !(rmax <= 127.5f);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              bool fl;
-              bq[j][kk][h] = quant_fast(row, kk * 32 + h * 16 + c4, rcp, fl);
-              tie_mask |= (fl ? 1u : 0u) << ((j * (D / 32) + kk) * 2 + h);
+            for (int kk = 0; kk < D / 16; ++kk) todo |= (all || !(um[kk] < kQuantTieGuard)) ? (1u << kk) : 0u;
+          }
+          const uint8_t* kptr = my_stages + (size_t)st * (2 * PAGE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t lanes = __ballot_sync(0xffffffffu, (todo >> kk) & 1u);
+            while (lanes != 0) {
+              const int L = __ffs(lanes) - 1;
+              lanes &= lanes - 1;
+              const float s0 = __shfl_sync(0xffffffffu, ksr0, L), s1 = __shfl_sync(0xffffffffu, ksr1, L);
+              uint32_t w = 0;
+              if (lane < 8) {
+                const int j = lane >> 2, i = lane & 3;
+                const int d = 16 * kk + (L & 3) * 2 + (i & 1) + 8 * (i >> 1);
+                w = quant_exact_elem<SLAB_BYTES>(kptr, 8 * j + (L >> 2), d, j ? s1 : s0) << (8 * i);
+              }
+              w |= __shfl_xor_sync(0xffffffffu, w, 1);
+              w |= __shfl_xor_sync(0xffffffffu, w, 2);
+              const uint32_t w0 = __shfl_sync(0xffffffffu, w, 0), w1 = __shfl_sync(0xffffffffu, w, 4);
+              if (lane == L) {
+                bq[0][kk >> 1][kk & 1] = w0;
+                bq[1][kk >> 1][kk & 1] = w1;
+              }
             }
           }
         }
-        if (tie_mask != 0) {
 #pragma unroll
-          for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int kk = 0; kk < D / 32; ++kk)
-#pragma unroll
-              for (int h = 0; h < 2; ++h)
-                if ((tie_mask >> ((j * (D / 32) + kk) * 2 + h)) & 1u)
-                  bq[j][kk][h] = quant_exact(8 * j + g, kk * 32 + h * 16 + c4, ksr[j]);
+        for (int kk = 0; kk < D / 32; ++kk) {
+          mma_s8_rows<HM>(si[0], qa[kk], bq[0][kk][0], bq[0][kk][1]);
+          mma_s8_rows<HM>(si[1], qa[kk], bq[1][kk][0], bq[1][kk][1]);
         }
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-          for (int kk = 0; kk < D / 32; ++kk) mma_s8_rows<HM>(si[j], qa[kk], bq[j][kk][0], bq[j][kk][1]);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const float ks_a = __shfl_sync(0xffffffffu, ks_cur, 8 * j + cq);
