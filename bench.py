@@ -37,8 +37,10 @@ if ROOT not in sys.path:
 # the benchmark launch (275,479 tokens); the INT8 figure is the B=16 capture (274.8 MB) scaled to
 # B=32; traffic grows in proportion to tokens.  None = no DRAM-traffic figure (tensor-bound kernel
 # or no capture).
-NCU_TRAFFIC_BYTES = {"paged_decode": 1_144_600_000, "int8_decode": 549_700_000, "contig_decode": None,
-                     "varlen_prefill": None}
+NCU_TRAFFIC_BYTES = {"paged_decode": 1_146_000_000, "int8_decode": 549_700_000, "contig_decode": None,
+                     "varlen_prefill": None,
+                     # B=16 capture (272.8 + 4.6 MB) scaled by 2 to the B=32 launch (traffic grows with the tokens)
+                     "int8_kv_decode": 554_800_000, "sliding_window_decode": None}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
