@@ -129,7 +129,9 @@ class PagedDecode:
     def __init__(self, device, seed):
         from flash_attn_v100_b200.synthetic import make_paged_tables
         self.device = device
-        t = make_paged_tables(self.B, 512, 8192, seed)
+        # lengths and page placement are the same on every rank (seed 0), so that the work per GPU is
+        # fixed exactly under weak scaling; the tensor values are seeded by the rank
+        t = make_paged_tables(self.B, 512, 8192, 0)
         self.seq_lens_h, self.block_table_h, self.n_pages = t["seq_lens"], t["block_table"], t["n_pages"]
         self.max_blocks = t["max_num_blocks"]
         g = torch.Generator(device=device).manual_seed(seed)
@@ -158,7 +160,8 @@ class PagedDecode:
         return {"workload": "paged_gqa_decode B=64 H_Q=32 H_KV=8 D=128 page=16 seq_lens~U[512,8192] (BASELINE configs[1])",
                 "batch_per_gpu": self.B, "tokens_attended_per_gpu": int(self.seq_lens_h.sum()),
                 "kv_bytes_per_gpu": int(self.k_cache.numel() * 4),
-                "l2": "inputs larger than L2 (KV pool >> 126 MB), no flush", "partition": "independent batch per rank"}
+                "l2": "inputs larger than L2 (KV pool >> 126 MB), no flush",
+                "partition": "independent batch per rank (same lengths on every rank, values seeded by rank)"}
 
     def step(self, fa):
         return fa.forward_paged_decode_gqa_fp16(self.q, self.k_cache, self.v_cache, self.bt, self.sl, self.max_blocks)
@@ -194,7 +197,7 @@ class ContigDecode(PagedDecode):
     metric = "continuous_batching_decode_tokens_per_s"
 
     def __init__(self, device, seed):
-        g = torch.Generator().manual_seed(seed)
+        g = torch.Generator().manual_seed(0)   # same lengths on every rank
         self.device = device
         self.B = 32
         self.max_N = 8192
@@ -329,7 +332,7 @@ class VarlenPrefill:
 
     def __init__(self, device, seed):
         self.device = device
-        g = torch.Generator().manual_seed(seed)
+        g = torch.Generator().manual_seed(0)   # same lengths on every rank
         self.lens = torch.randint(128, 4097, (16,), generator=g).tolist()
         cu = [0]
         for n in self.lens:
