@@ -34,6 +34,14 @@ SIGNATURES = {
     "fa_qk_norm_split_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _c.c_float, _vp]),
     "fa_silu_mul_bf16": (_i, [_vp, _vp, _i64, _i, _vp]),
     "fa_half_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
+    "fa_peer_alloc": (_i, [_sz, _c.POINTER(_vp), _c.POINTER(_vp), _c.POINTER(_vp), _vp, _vp]),
+    "fa_peer_open": (_i, [_vp, _c.POINTER(_vp)]),
+    "fa_peer_close": (_i, [_vp]),
+    "fa_peer_free": (_i, [_vp, _vp, _vp]),
+    "fa_peer_allreduce_sum_bf16": (_i, [_c.POINTER(_vp), _c.POINTER(_vp), _vp, _i, _i, _i64, _i64, _vp]),
+    "fa_peer_allgather": (_i, [_c.POINTER(_vp), _c.POINTER(_vp), _vp, _i, _i, _vp, _i64, _i64, _vp]),
+    "fa_peer_status": (_i, [_vp, _vp, _c.POINTER(_i)]),
+    "fa_peer_set_max_polls": (_i, [_c.c_uint]),
     "fa_prefill_set_impl": (_i, [_i]),
     "fa_prefill_status": (_i, [_vp, _c.POINTER(_i), _i]),
     "fa_prefill_dense_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),

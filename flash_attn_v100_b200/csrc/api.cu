@@ -17,6 +17,7 @@
 #include "prefill.cuh"
 #include "rope_append.cuh"
 #include "engine_ops.cuh"
+#include "peer_collectives.cuh"
 
 namespace {
 
@@ -647,6 +648,119 @@ int fa_half_to_bf16(const void* in, void* out, int64_t n, void* stream) {
   int rc = device_info(&di);
   if (rc != FA_OK) return rc;
   FA_CUDA(fa::launch_half_to_bf16(in, out, n, di.sm_count, static_cast<cudaStream_t>(stream)));
+  return FA_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Peer-memory collectives (one process per GPU; buffers shared through CUDA IPC)
+// ---------------------------------------------------------------------------
+int fa_peer_alloc(size_t data_bytes, void** data, void** flags, void** state, void* data_handle, void* flags_handle) {
+  FA_REQUIRE(data && flags && state && data_handle && flags_handle, "null pointer");
+  FA_REQUIRE(data_bytes > 0 && data_bytes % 256 == 0, "data_bytes must be a positive multiple of 256");
+  void *d = nullptr, *f = nullptr, *s = nullptr;
+  FA_CUDA(cudaMalloc(&d, data_bytes));
+  FA_CUDA(cudaMalloc(&f, fa::kPeerFlagBytes));
+  FA_CUDA(cudaMalloc(&s, 256));
+  FA_CUDA(cudaMemset(d, 0, data_bytes));
+  FA_CUDA(cudaMemset(f, 0, fa::kPeerFlagBytes));
+  FA_CUDA(cudaMemset(s, 0, 256));
+  FA_CUDA(cudaDeviceSynchronize());
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are exchanged as 64 bytes");
+  FA_CUDA(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(data_handle), d));
+  FA_CUDA(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(flags_handle), f));
+  *data = d; *flags = f; *state = s;
+  return FA_OK;
+}
+
+int fa_peer_open(const void* handle, void** ptr) {
+  FA_REQUIRE(handle && ptr, "null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  FA_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return FA_OK;
+}
+
+int fa_peer_close(void* ptr) {
+  FA_REQUIRE(ptr, "null pointer");
+  FA_CUDA(cudaIpcCloseMemHandle(ptr));
+  return FA_OK;
+}
+
+int fa_peer_free(void* data, void* flags, void* state) {
+  if (data) FA_CUDA(cudaFree(data));
+  if (flags) FA_CUDA(cudaFree(flags));
+  if (state) FA_CUDA(cudaFree(state));
+  return FA_OK;
+}
+
+namespace {
+// Bound of a flag wait in polls of >= 100 ns: tens of seconds by default, because ranks can be skewed
+// by a whole CUDA-graph capture; tests shorten it.
+unsigned int g_peer_max_polls = 1u << 26;
+
+int fill_peer_args(void* const* data_ptrs, void* const* flag_ptrs, void* state, int rank, int world,
+                   fa::PeerPointers* pp, fa::PeerState* st) {
+  FA_REQUIRE(data_ptrs && flag_ptrs && state, "null pointer");
+  FA_REQUIRE(world >= 1 && world <= fa::kPeerMaxWorld, "world must be between 1 and 8");
+  FA_REQUIRE(rank >= 0 && rank < world, "rank out of range");
+  memset(pp, 0, sizeof(*pp));
+  for (int i = 0; i < world; ++i) {
+    FA_REQUIRE(data_ptrs[i] && flag_ptrs[i], "null peer pointer");
+    pp->data[i] = static_cast<uint8_t*>(data_ptrs[i]);
+    pp->flags[i] = static_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  uint8_t* s = static_cast<uint8_t*>(state);
+  st->epoch = reinterpret_cast<uint32_t*>(s);
+  st->ticket = reinterpret_cast<unsigned int*>(s + 64);
+  st->status = reinterpret_cast<int32_t*>(s + 128);
+  st->max_polls = g_peer_max_polls;
+  return FA_OK;
+}
+}  // namespace
+
+int fa_peer_allreduce_sum_bf16(void* const* data_ptrs, void* const* flag_ptrs, void* state, int rank, int world,
+                               int64_t offset_bytes, int64_t n_elems, void* stream) {
+  fa::PeerPointers pp;
+  fa::PeerState st;
+  int rc = fill_peer_args(data_ptrs, flag_ptrs, state, rank, world, &pp, &st);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(offset_bytes >= 0 && offset_bytes % 16 == 0, "offset_bytes must be a non-negative multiple of 16");
+  FA_REQUIRE(n_elems > 0 && n_elems % (8 * world) == 0, "n_elems must be a positive multiple of 8 * world");
+  const long long vec_per_slice = n_elems / 8 / world;
+  const int ctas = (int)((vec_per_slice + 511) / 512);
+  FA_CUDA(fa::launch_peer_allreduce_bf16(pp, st, rank, world, offset_bytes, n_elems, ctas,
+                                         static_cast<cudaStream_t>(stream)));
+  return FA_OK;
+}
+
+int fa_peer_allgather(void* const* data_ptrs, void* const* flag_ptrs, void* state, int rank, int world, const void* src,
+                      int64_t offset_bytes, int64_t chunk_bytes, void* stream) {
+  fa::PeerPointers pp;
+  fa::PeerState st;
+  int rc = fill_peer_args(data_ptrs, flag_ptrs, state, rank, world, &pp, &st);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(src, "null source pointer");
+  FA_REQUIRE(offset_bytes >= 0 && offset_bytes % 4 == 0, "offset_bytes must be a non-negative multiple of 4");
+  FA_REQUIRE(chunk_bytes > 0 && chunk_bytes % 4 == 0, "chunk_bytes must be a positive multiple of 4");
+  FA_CUDA(fa::launch_peer_allgather(pp, st, rank, world, src, offset_bytes, chunk_bytes,
+                                    static_cast<cudaStream_t>(stream)));
+  return FA_OK;
+}
+
+int fa_peer_set_max_polls(unsigned int max_polls) {
+  FA_REQUIRE(max_polls > 0, "max_polls must be positive");
+  g_peer_max_polls = max_polls;
+  return FA_OK;
+}
+
+int fa_peer_status(const void* state, void* stream, int* host_status_out) {
+  FA_REQUIRE(state && host_status_out, "null pointer");
+  int32_t v = 0;
+  FA_CUDA(cudaMemcpyAsync(&v, static_cast<const uint8_t*>(state) + 128, 4, cudaMemcpyDeviceToHost,
+                          static_cast<cudaStream_t>(stream)));
+  FA_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  *host_status_out = v;
+  if (v != 0) return fail(FA_ERR_DEVICE_STATUS, "a peer collective gave up waiting for another rank (status 0x%x)", v);
   return FA_OK;
 }
 

@@ -1,0 +1,35 @@
+// Peer-memory collectives of the tensor-parallel decode step: parameter blocks and launchers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fa {
+
+constexpr int kPeerMaxWorld = 8;    // ranks of one NVLink domain served by these kernels
+constexpr int kPeerMaxCtas = 32;    // CTAs of one collective launch (each has its own flags)
+constexpr size_t kPeerFlagBytes = 2 * kPeerMaxCtas * kPeerMaxWorld * sizeof(uint32_t);
+constexpr int kPeerStatusTimeout = 1;
+
+struct PeerPointers {
+  uint8_t* data[kPeerMaxWorld];     // data buffer of every rank (own one included), same size on all ranks
+  uint32_t* flags[kPeerMaxWorld];   // flag array of every rank: [2 phases][kPeerMaxCtas][kPeerMaxWorld]
+};
+
+struct PeerState {                  // local device memory of this rank
+  uint32_t* epoch;                  // number of collective launches completed
+  unsigned int* ticket;             // CTAs of the current launch that have finished
+  int32_t* status;                  // sticky status word
+  unsigned int max_polls;           // bound of every flag wait (each poll sleeps >= 100 ns)
+};
+
+// In-place sum of n_elems bf16 values at byte offset `offset_bytes` of every rank's data buffer.
+// n_elems must be a multiple of 8 * world.
+cudaError_t launch_peer_allreduce_bf16(const PeerPointers& pp, const PeerState& st, int rank, int world,
+                                       long long offset_bytes, long long n_elems, int ctas, cudaStream_t stream);
+
+// Rank r's `chunk_bytes` at `src` (local memory) end up at offset_bytes + r * chunk_bytes of every
+// rank's data buffer.  chunk_bytes must be a multiple of 4.
+cudaError_t launch_peer_allgather(const PeerPointers& pp, const PeerState& st, int rank, int world, const void* src,
+                                  long long offset_bytes, long long chunk_bytes, cudaStream_t stream);
+
+}  // namespace fa

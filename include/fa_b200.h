@@ -289,6 +289,45 @@ int fa_prefill_set_impl(int impl);
  * launch are undefined, no fault is raised).  `clear` != 0 resets it afterwards. */
 int fa_prefill_status(void* stream, int* host_status_out, int clear);
 
+/* --------------------------------------------------------------------------
+ * Peer-memory collectives of the tensor-parallel decode step (one process per
+ * GPU of one NVLink domain, at most 8 ranks).  They stand where the reference
+ * calls dist.all_reduce / dist.all_gather (flash_attn_llm/parallel/
+ * tensor_parallel.py:152-190; its single-process peer all-reduce export is
+ * cross_gpu_allreduce_fp16, flash_attn.cpp:206, :252), as single kernels on
+ * plain peer loads and stores that can be recorded into a CUDA graph.
+ *
+ * fa_peer_alloc: allocate this rank's data buffer (data_bytes, zeroed), flag
+ *   array and local state, and return CUDA IPC handles (64 bytes each) of the
+ *   first two for the other ranks.  fa_peer_open maps another rank's handle.
+ *   All ranks must allocate the same data_bytes and make the same sequence of
+ *   collective calls.
+ * fa_peer_allreduce_sum_bf16: in-place sum of n_elems bf16 values at
+ *   offset_bytes of every rank's data buffer (n_elems a multiple of 8 * world);
+ *   each element is reduced in fp32, in rank order, by one rank and stored to
+ *   all: the result is bit-identical on every rank.
+ * fa_peer_allgather: rank r's chunk_bytes at `src` (local memory) are stored
+ *   at offset_bytes + r * chunk_bytes of every rank's data buffer.
+ * data_ptrs / flag_ptrs: host arrays of `world` device pointers in rank order
+ *   (own buffers at index `rank`).  Every wait for another rank is bounded;
+ *   fa_peer_status reports a wait that ran out (FA_ERR_DEVICE_STATUS).
+ * -------------------------------------------------------------------------- */
+int fa_peer_alloc(size_t data_bytes, void** data, void** flags, void** state,
+                  void* data_handle, void* flags_handle);
+int fa_peer_open(const void* handle, void** ptr);
+int fa_peer_close(void* ptr);
+int fa_peer_free(void* data, void* flags, void* state);
+int fa_peer_allreduce_sum_bf16(void* const* data_ptrs, void* const* flag_ptrs, void* state,
+                               int rank, int world, int64_t offset_bytes, int64_t n_elems,
+                               void* stream);
+int fa_peer_allgather(void* const* data_ptrs, void* const* flag_ptrs, void* state,
+                      int rank, int world, const void* src, int64_t offset_bytes,
+                      int64_t chunk_bytes, void* stream);
+int fa_peer_status(const void* state, void* stream, int* host_status_out);
+/* Bound of every wait for another rank, in polls of at least 100 ns (default 2^26;
+ * applies to launches made after the call). */
+int fa_peer_set_max_polls(unsigned int max_polls);
+
 #ifdef __cplusplus
 }
 #endif
