@@ -377,7 +377,8 @@ def run_engine(args):
     B, P, N = (8, 64, 16) if args.engine_tiny else (args.engine_requests, 1024, 256)
     w = make_rank_weights(cfg, rank, world, 0, device)
     model = TPDecoder(cfg, w, rank, world, None, device)
-    runner = GenerationRunner(model, max_batch=B, max_seq_len=P + N, use_cuda_graph=True)
+    runner = GenerationRunner(model, max_batch=B, max_seq_len=P + N, use_cuda_graph=True,
+                              peer_collectives=not args.engine_nccl_decode)
     prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=torch.Generator().manual_seed(0))
     times = []
     for it in range(max(args.warmup, 1) + args.steps):
@@ -392,6 +393,8 @@ def run_engine(args):
             times.append(ms)
             phases = runner.last_timing_ms()
     flash_attn_v100_b200.check_async_errors(); flash_attn_v100_b200.check_prefill_errors()
+    if model.comm is not None:
+        model.comm.check()
     if rank != 0:
         return
     ms = sum(times) / len(times)
@@ -632,6 +635,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="paged_decode", choices=sorted(WORKLOADS) + ["engine"])
     ap.add_argument("--engine-tiny", action="store_true", help="engine workload on the tiny test shape")
+    ap.add_argument("--engine-nccl-decode", action="store_true",
+                    help="engine workload: NCCL collectives in the decode step (chain of CUDA graphs) instead of "
+                         "the library's peer-memory collectives (one CUDA graph per step)")
     ap.add_argument("--engine-requests", type=int, default=256)
     ap.add_argument("--engine-prefill-chunk", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -79,6 +79,10 @@ class PeerCollectives:
             raise ValueError("view outside the peer buffer or not 16-byte aligned")
         return self._bytes[offset_bytes:offset_bytes + nbytes].view(dtype).view(*shape)
 
+    def owns(self, t: torch.Tensor) -> bool:
+        off = t.data_ptr() - self._own[0]
+        return 0 <= off and off + t.numel() * t.element_size() <= self.data_bytes
+
     def _offset_of(self, t: torch.Tensor) -> int:
         off = t.data_ptr() - self._own[0]
         if off < 0 or off + t.numel() * t.element_size() > self.data_bytes or not t.is_contiguous():

@@ -30,6 +30,10 @@ class TPDecoder:
     def __init__(self, cfg: ModelConfig, weights, rank: int = 0, world: int = 1, group=None, device="cuda"):
         cfg.validate(world)
         self.cfg, self.w, self.rank, self.world, self.group = cfg, weights, rank, world, group
+        # Optional `comm.PeerCollectives`: when set, the decode step sums its row-parallel outputs and gathers
+        # the greedy candidates with the library's peer-memory kernels (capturable into the step's CUDA graph)
+        # instead of NCCL calls.  Prefill keeps NCCL (large messages, not replayed from a graph).
+        self.comm = None
         self.device = torch.device(device)
         self.ql = cfg.num_heads // world
         self.kl = cfg.num_kv_heads // world
@@ -75,6 +79,18 @@ class TPDecoder:
             torch.distributed.all_reduce(t, group=self.group)
         return t
 
+    def _peer_rows(self, T):
+        """Two [T, hidden] bf16 views of the peer buffer (attention and MLP outputs), or None when the step
+        does not go through the peer collectives."""
+        c = self.comm
+        if c is None or self.world == 1:
+            return None
+        nbytes = (T * self.cfg.hidden_size * 2 + 255) // 256 * 256
+        if 2 * nbytes > c.data_bytes or (T * self.cfg.hidden_size) % (8 * self.world) != 0:
+            return None
+        return (c.view(0, (T, self.cfg.hidden_size), torch.bfloat16),
+                c.view(nbytes, (T, self.cfg.hidden_size), torch.bfloat16))
+
     def rope_tables(self, positions):
         """fp32 cos/sin [T, D] exactly as the reference computes them (rope.py:228-266)."""
         freqs = torch.outer(positions.float(), self.inv_freq)
@@ -94,6 +110,7 @@ class TPDecoder:
         seg = seg or Segments(capture=False)
         prefill = cu_seqlens is not None
         st = {"delta": None}
+        peer = None if prefill else self._peer_rows(token_ids.numel())
 
         def first():
             st["x"] = self.w["embed"][token_ids]                          # [T, hidden] bf16
@@ -119,18 +136,26 @@ class TPDecoder:
                     attn = ops.forward_paged_decode_gqa_fp16(q_rot, kv.k_pools[l], kv.v_pools[l], block_table,
                                                              st["lens"], max_blocks)
                 a = self._to_bf16(attn.reshape(x.size(0), self.ql * cfg.head_dim))
-                st["o"] = a @ lw["wo"].t()
+                if peer is None:
+                    st["o"] = a @ lw["wo"].t()
+                else:                      # GEMM straight into the peer buffer, summed in place over the ranks
+                    st["o"] = self.comm.all_reduce_(torch.mm(a, lw["wo"].t(), out=peer[0]))
 
             seg.run(attention_half)
-            seg.collective(self._all_reduce, st["o"])
+            if peer is None:
+                seg.collective(self._all_reduce, st["o"])
 
             def mlp_half(lw=lw):
                 h = self._add_rmsnorm(st["x"], st["o"], lw["ln2"])       # x += attention; h = ln2(x)
                 gu = h @ lw["wgu"].t()
-                st["delta"] = self._silu_mul(gu) @ lw["wd"].t()
+                if peer is None:
+                    st["delta"] = self._silu_mul(gu) @ lw["wd"].t()
+                else:
+                    st["delta"] = self.comm.all_reduce_(torch.mm(self._silu_mul(gu), lw["wd"].t(), out=peer[1]))
 
             seg.run(mlp_half)
-            seg.collective(self._all_reduce, st["delta"])
+            if peer is None:
+                seg.collective(self._all_reduce, st["delta"])
 
         def last():
             if prefill:
@@ -156,6 +181,8 @@ class TPDecoder:
             out = torch.empty((self.world,) + pair.shape, dtype=pair.dtype, device=pair.device)
         if self.world == 1:
             out[0].copy_(pair)
+        elif self.comm is not None and self.comm.owns(out):
+            self.comm.all_gather_into(out, pair)
         else:
             torch.distributed.all_gather_into_tensor(out, pair, group=self.group)
         return out

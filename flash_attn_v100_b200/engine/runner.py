@@ -13,7 +13,8 @@ from .model import Segments, TPDecoder
 
 
 class GenerationRunner:
-    def __init__(self, model: TPDecoder, max_batch: int, max_seq_len: int, use_cuda_graph: bool = True):
+    def __init__(self, model: TPDecoder, max_batch: int, max_seq_len: int, use_cuda_graph: bool = True,
+                 peer_collectives: bool = False):
         cfg = model.cfg
         self.model = model
         self.max_batch, self.max_seq_len = max_batch, max_seq_len
@@ -23,7 +24,17 @@ class GenerationRunner:
                                max_blocks_per_seq=self.max_blocks, device=model.device)
         # The decode step is replayed from one CUDA graph on a single rank, and from a chain of graphs with
         # the NCCL collectives issued eagerly in between under tensor parallelism (NCCL calls are not captured).
+        # With peer_collectives the decode step's collectives are the library's peer-memory kernels, and the
+        # whole step is one CUDA graph under tensor parallelism too.
         self.use_cuda_graph = use_cuda_graph
+        self._gather_off = 0
+        if peer_collectives and model.world > 1:
+            from ..comm import PeerCollectives
+            import torch.distributed as dist
+            rows = (max_batch * cfg.hidden_size * 2 + 255) // 256 * 256
+            self._gather_off = 2 * rows
+            model.comm = PeerCollectives(model.group if model.group is not None else dist.group.WORLD, model.device,
+                                         2 * rows + model.world * max_batch * 8)
         self._side_stream = torch.cuda.Stream(device=model.device)   # decode runs here (one scratch workspace)
         self._decode_cache = {}     # batch size -> (step graph(s), cur, slot, gathered): captured once, replayed by later calls
 
@@ -67,7 +78,10 @@ class GenerationRunner:
             graph = None
             cur = torch.empty(B, dtype=torch.int64, device=dev)                    # token being fed
             slot = torch.empty(B, dtype=torch.int32, device=dev)                   # its cache slot
-            gathered = torch.empty((m.world, B, 2), dtype=torch.float32, device=dev)
+            if m.comm is not None:
+                gathered = m.comm.view(self._gather_off, (m.world, B, 2), torch.float32)
+            else:
+                gathered = torch.empty((m.world, B, 2), dtype=torch.float32, device=dev)
         cur.copy_(first)
         slot.fill_(P)
 
@@ -103,9 +117,10 @@ class GenerationRunner:
                 # step on a single rank; under tensor parallelism a chain of graphs with the NCCL collectives
                 # in between (every captured segment is run right after its capture, so that step is real).
                 step(); out[:, 1] = cur; done = 1
-                if m.world == 1:
+                if m.world == 1 or m.comm is not None:
                     graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph, stream=side):
+                    # (thread-local capture mode: the NCCL watchdog thread of the process group may poll events)
+                    with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
                         step()
                 else:
                     graph = Segments(capture=True, stream=side)

@@ -29,6 +29,21 @@ def main():
     torch.cuda.synchronize()
     graphs_equal = torch.equal(toks_graph, toks_tp) and torch.equal(toks_again, toks_tp)
     print(f"[rank {rank}] segmented-graph replay equal to eager: {graphs_equal}", flush=True)
+    # the decode step on the library's peer-memory collectives: one CUDA graph per step; eager and replayed
+    # runs are the same arithmetic (identical tokens), and its logits agree with the NCCL run's
+    pr = GenerationRunner(TPDecoder(cfg, w_tp, rank, world, None, f"cuda:{local}"), 4, 64, peer_collectives=True)
+    logs_pr = []
+    toks_pr = pr.generate(prompts, 16, logits_out=logs_pr)
+    toks_pr_graph = pr.generate(prompts, 16)
+    toks_pr_again = pr.generate(prompts, 16)
+    torch.cuda.synchronize()
+    pr.model.comm.check()
+    peer_equal = torch.equal(toks_pr_graph, toks_pr) and torch.equal(toks_pr_again, toks_pr)
+    err_peer = (logs_pr[0][2] - logs_tp[0][2]).abs().max().item()
+    err_peer_dec = (logs_pr[1][2] - logs_tp[1][2]).abs().max().item() if torch.equal(toks_pr[:, 0], toks_tp[:, 0]) else 0.0
+    print(f"[rank {rank}] peer-collective decode: graph equal to eager {peer_equal}, logit err vs NCCL run "
+          f"{err_peer:.4f} / {err_peer_dec:.4f}", flush=True)
+    graphs_equal = graphs_equal and peer_equal and err_peer < 3e-2 and err_peer_dec < 3e-2
     w_1 = make_rank_weights(cfg, 0, 1, 5, f"cuda:{local}", gen_device="cpu")
     one = GenerationRunner(TPDecoder(cfg, w_1, 0, 1, None, f"cuda:{local}"), 4, 64, use_cuda_graph=False)
     logs_1 = []
