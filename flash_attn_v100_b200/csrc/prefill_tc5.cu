@@ -179,7 +179,7 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   x.y = fmaxf(x.y, -125.f);
   const float2 t = fadd2(x, make_float2(kMagic, kMagic));
   const float2 n = fadd2(t, make_float2(-kMagic, -kMagic));
-  const float2 f = fadd2(x, make_float2(-n.x, -n.y));
+  const float2 f = ffma2(n, make_float2(-1.f, -1.f), x);
   float2 r = ffma2(make_float2(0.05508868f, 0.05508868f), f, make_float2(0.24260405f, 0.24260405f));
   r = ffma2(r, f, make_float2(0.69327623f, 0.69327623f));
   r = ffma2(r, f, make_float2(0.99992895f, 0.99992895f));
@@ -620,14 +620,12 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float2 x = ffma2(make_float2(sv[c][2 * i], sv[c][2 * i + 1]), sc2, nm2);
-            if (POLY) {
-              // two exponentials per MUFU instruction: round the argument to fp16, exp2 on the
-              // half2; the row sum is taken from the very values the PV MMA will multiply
-              const uint32_t xh = pack_half2(x.x, x.y);
-              uint32_t eh;
-              asm("ex2.approx.f16x2 %0, %1;" : "=r"(eh) : "r"(xh));
-              pk[i] = eh;
-              rs2[c] = fadd2(rs2[c], __half22float2(*reinterpret_cast<const __half2*>(&eh)));
+            if (POLY && (i & 3) == 0) {
+              // every fourth pair on the FMA/ALU pipes (measured neutral: 803 vs 810 TFLOP/s; larger shares
+              // are slower, the row is bound by dependent latencies rather than by the MUFU alone)
+              const float2 e = exp2_poly2(x);
+              rs2[c] = fadd2(rs2[c], e);
+              pk[i] = pack_half2(e.x, e.y);
             } else {
               float2 e;
               e.x = fast_exp2(x.x);
@@ -732,7 +730,7 @@ cudaError_t next_item_counter(unsigned long long** out, cudaStream_t stream) {
   return e;
 }
 
-bool g_tc5_poly = false;  // true: exp2 evaluated on half2 (two results per MUFU instruction)
+bool g_tc5_poly = false;  // true: a quarter of the exponentials evaluated as a polynomial on the FMA pipes
 
 template <int D>
 cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t stream) {

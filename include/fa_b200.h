@@ -280,7 +280,7 @@ int fa_half_to_bf16(const void* in, void* out, int64_t n, void* stream);
 
 /* Kernel choice for the prefill entry points: 0 = automatic (tcgen05 kernel for
  * D = 64/128, mma.sync kernel otherwise), 1 = always the mma.sync kernel, 2 = require
- * the tcgen05 kernel, 3 = tcgen05 kernel with every other pair of exp2 evaluated as a
+ * the tcgen05 kernel, 3 = tcgen05 kernel with every fourth pair of exp2 evaluated as a
  * polynomial on the FMA pipes.  Process-wide; meant for tests and measurements. */
 int fa_prefill_set_impl(int impl);
 

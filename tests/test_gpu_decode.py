@@ -218,3 +218,37 @@ def test_paged_config2_shape_properties(fa):
     out_half = fa.forward_paged_decode_gqa_fp16(q, kc, vc * 0.5, bt.cuda(), lens.cuda(), w["max_num_blocks"])
     assert (out_half.float() * 2 - out.float()).abs().max().item() < 1e-3
     _finish(fa)
+
+
+def test_paged_large_batch_uses_the_prefix_pre_pass(fa):
+    """B + 1 > 4096: the page prefix sums come from the one-CTA pre-pass instead of the in-kernel scan."""
+    torch.manual_seed(21)
+    B, H_Q, H_KV, D = 4500, 8, 2, 64
+    lens = torch.randint(0, 40, (B,), dtype=torch.int32)
+    max_len = 48
+    k = torch.randn(B, H_KV, max_len, D).half()
+    v = torch.randn(B, H_KV, max_len, D).half()
+    q = torch.randn(B, H_Q, 1, D).half()
+    order = torch.randperm(B * 3, generator=torch.Generator().manual_seed(5)).tolist()
+    kc, vc, bt, mnb = orc.build_paged_cache(k, v, lens, order)
+    out = fa.forward_paged_decode_gqa_fp16(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), lens.cuda(), mnb)
+    sel = torch.arange(0, B, 37)
+    ref = orc.paged_decode(q[sel], kc, vc, bt[sel], lens[sel], final_cast=False)
+    assert _err(out[sel.cuda()], ref) < TOL
+    assert out[(lens == 0).cuda()].abs().max().item() == 0
+    _finish(fa)
+
+
+@pytest.mark.parametrize("heads", [(12, 1), (24, 2), (20, 1), (48, 3)])
+def test_group_sizes_beyond_eight_heads(fa, heads):
+    """More than 8 query heads per KV head: full 16-row fragments, and more than 16: several head blocks."""
+    H_Q, H_KV = heads
+    torch.manual_seed(H_Q)
+    B, N, D = 2, 203, 128
+    q = torch.randn(B, H_Q, 1, D).half()
+    k = torch.randn(B, H_KV, N, D).half()
+    v = torch.randn(B, H_KV, N, D).half()
+    for cache_len in (202, 17):
+        out = fa.forward_decode_gqa_fp16(q.cuda(), k.cuda(), v.cuda(), True, cache_len)
+        assert _err(out, orc.decode_gqa(q, k, v, True, cache_len, final_cast=False)) < TOL, (heads, cache_len)
+    _finish(fa)
