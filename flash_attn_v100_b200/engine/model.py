@@ -98,19 +98,17 @@ class TPDecoder:
         return emb.cos().contiguous(), emb.sin().contiguous()
 
     # ---- one decoder stack pass -------------------------------------------------------
-    def forward(self, token_ids, positions, kv, block_table, slots, max_blocks, *, cu_seqlens=None, max_seqlen=0,
-                seq_lens_after=None, seg=None):
-        """token_ids [T] int64; positions [T] int32 (rotary position of every token).
-        Prefill (cu_seqlens given): packed prompts, `slots` [batch] = first cache slot per sequence; returns the
-        hidden state of the last token of every sequence.  Decode: one token per sequence, `slots` [B] = slot of
-        the new token, `seq_lens_after` [B] = lengths including it (default: slots + 1); returns [B, hidden].
-        `seg` (see `Segments`) receives the compute between two collectives as one unit, so that a decode
-        step can be replayed as a chain of CUDA graphs with the NCCL calls in between."""
+    def _stages(self, token_ids, positions, kv, block_table, slots, max_blocks, cu_seqlens, max_seqlen,
+                seq_lens_after):
+        """The pass as closures over a shared state dict: `first`, per layer (`attention_half`, `mlp_half`),
+        `last`.  After `attention_half` the row-parallel output st["o"] and after `mlp_half` st["delta"]
+        still have to be summed over the ranks, unless st["peer"] is set: then the halves have already done
+        it with the peer-memory all-reduce."""
         cfg = self.cfg
-        seg = seg or Segments(capture=False)
         prefill = cu_seqlens is not None
         st = {"delta": None}
         peer = None if prefill else self._peer_rows(token_ids.numel())
+        st["peer"] = peer
 
         def first():
             st["x"] = self.w["embed"][token_ids]                          # [T, hidden] bf16
@@ -118,7 +116,7 @@ class TPDecoder:
             # decode: lengths including the new token (derived here so that a replayed step recomputes them)
             st["lens"] = seq_lens_after if (prefill or seq_lens_after is not None) else slots + 1
 
-        seg.run(first)
+        layers = []
         for l, lw in enumerate(self.w["layers"]):
             def attention_half(l=l, lw=lw):
                 x = st["x"]
@@ -141,10 +139,6 @@ class TPDecoder:
                 else:                      # GEMM straight into the peer buffer, summed in place over the ranks
                     st["o"] = self.comm.all_reduce_(torch.mm(a, lw["wo"].t(), out=peer[0]))
 
-            seg.run(attention_half)
-            if peer is None:
-                seg.collective(self._all_reduce, st["o"])
-
             def mlp_half(lw=lw):
                 h = self._add_rmsnorm(st["x"], st["o"], lw["ln2"])       # x += attention; h = ln2(x)
                 gu = h @ lw["wgu"].t()
@@ -153,9 +147,7 @@ class TPDecoder:
                 else:
                     st["delta"] = self.comm.all_reduce_(torch.mm(self._silu_mul(gu), lw["wd"].t(), out=peer[1]))
 
-            seg.run(mlp_half)
-            if peer is None:
-                seg.collective(self._all_reduce, st["delta"])
+            layers.append((attention_half, mlp_half))
 
         def last():
             if prefill:
@@ -165,8 +157,66 @@ class TPDecoder:
                 x_last, d_last = st["x"], st["delta"]
             st["hidden"] = self._add_rmsnorm(x_last, d_last, self.w["final_ln"])   # final norm of (x + last MLP)
 
+        return st, first, layers, last
+
+    def forward(self, token_ids, positions, kv, block_table, slots, max_blocks, *, cu_seqlens=None, max_seqlen=0,
+                seq_lens_after=None, seg=None):
+        """token_ids [T] int64; positions [T] int32 (rotary position of every token).
+        Prefill (cu_seqlens given): packed prompts, `slots` [batch] = first cache slot per sequence; returns the
+        hidden state of the last token of every sequence.  Decode: one token per sequence, `slots` [B] = slot of
+        the new token, `seq_lens_after` [B] = lengths including it (default: slots + 1); returns [B, hidden].
+        `seg` (see `Segments`) receives the compute between two collectives as one unit, so that a decode
+        step can be replayed as a chain of CUDA graphs with the NCCL calls in between."""
+        seg = seg or Segments(capture=False)
+        st, first, layers, last = self._stages(token_ids, positions, kv, block_table, slots, max_blocks, cu_seqlens,
+                                               max_seqlen, seq_lens_after)
+        seg.run(first)
+        for attention_half, mlp_half in layers:
+            seg.run(attention_half)
+            if st["peer"] is None:
+                seg.collective(self._all_reduce, st["o"])
+            seg.run(mlp_half)
+            if st["peer"] is None:
+                seg.collective(self._all_reduce, st["delta"])
         seg.run(last)
         return st["hidden"]
+
+    def forward_stages(self, token_ids, positions, kv, block_table, slots, max_blocks, *, cu_seqlens=None,
+                       max_seqlen=0, seq_lens_after=None):
+        """The same pass as a generator: it yields every tensor that has to be summed over the ranks (the
+        caller all-reduces it in place before resuming) and finally returns the hidden state through
+        StopIteration.  Several passes over independent token batches can thus be advanced in turn, each on
+        its own stream, so that one batch's all-reduce overlaps the other's compute (`forward_overlapped`)."""
+        st, first, layers, last = self._stages(token_ids, positions, kv, block_table, slots, max_blocks, cu_seqlens,
+                                               max_seqlen, seq_lens_after)
+        first()
+        for attention_half, mlp_half in layers:
+            attention_half()
+            if st["peer"] is None:
+                yield st["o"]
+            mlp_half()
+            if st["peer"] is None:
+                yield st["delta"]
+        last()
+        return st["hidden"]
+
+    def forward_overlapped(self, batches, streams):
+        """Run one pass per entry of `batches` (dicts of forward() arguments), entry i on streams[i], advancing
+        them in turn from one collective to the next; returns the hidden states in order.  The caller orders the
+        streams against whatever produced the inputs and consumes the outputs."""
+        gens = [self.forward_stages(**b) for b in batches]
+        out = [None] * len(gens)
+        live = list(range(len(gens)))
+        while live:
+            for i in list(live):
+                with torch.cuda.stream(streams[i]):
+                    try:
+                        t = next(gens[i])
+                        self._all_reduce(t)
+                    except StopIteration as done:
+                        out[i] = done.value
+                        live.remove(i)
+        return out
 
     def greedy_local(self, hidden):
         """This rank's best (value, index) per sequence over its vocabulary shard, and the shard's logits."""

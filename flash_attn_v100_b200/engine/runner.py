@@ -36,6 +36,10 @@ class GenerationRunner:
             model.comm = PeerCollectives(model.group if model.group is not None else dist.group.WORLD, model.device,
                                          2 * rows + model.world * max_batch * 8)
         self._side_stream = torch.cuda.Stream(device=model.device)   # decode runs here (one scratch workspace)
+        # Under tensor parallelism prompt chunks are prefilled two at a time, each on its own stream and
+        # advanced in turn from one all-reduce to the next, so that one chunk's NCCL all-reduce (134 MB per
+        # 16 x 1024 tokens) overlaps the other chunk's compute.
+        self._prefill_streams = [torch.cuda.Stream(device=model.device) for _ in range(2)] if model.world > 1 else []
         self._decode_cache = {}     # batch size -> (step graph(s), cur, slot, gathered): captured once, replayed by later calls
 
     @torch.no_grad()
@@ -54,18 +58,36 @@ class GenerationRunner:
         ev[0].record()
         # ---- prefill, `prefill_chunk` sequences per pass ----
         first = torch.empty(B, dtype=torch.int64, device=dev)
-        for b0 in range(0, B, prefill_chunk):
-            b1 = min(b0 + prefill_chunk, B)
+
+        def chunk_args(b0, b1):
             nb = b1 - b0
-            toks = prompts[b0:b1].reshape(-1).to(dev)
-            cu = (torch.arange(nb + 1, dtype=torch.int32, device=dev) * P)
-            pos = torch.arange(P, dtype=torch.int32, device=dev).repeat(nb)
-            slots = torch.zeros(nb, dtype=torch.int32, device=dev)
-            hidden = m.forward(toks, pos, kv, table[b0:b1], slots, self.max_blocks, cu_seqlens=cu, max_seqlen=P)
-            tok, lg = m.greedy_token(hidden)
-            first[b0:b1] = tok
-            if logits_out is not None:
-                logits_out.append(("prefill", b0, lg))
+            return dict(token_ids=prompts[b0:b1].reshape(-1).to(dev),
+                        positions=torch.arange(P, dtype=torch.int32, device=dev).repeat(nb), kv=kv,
+                        block_table=table[b0:b1], slots=torch.zeros(nb, dtype=torch.int32, device=dev),
+                        max_blocks=self.max_blocks,
+                        cu_seqlens=(torch.arange(nb + 1, dtype=torch.int32, device=dev) * P), max_seqlen=P)
+
+        chunks = [(b0, min(b0 + prefill_chunk, B)) for b0 in range(0, B, prefill_chunk)]
+        group = len(self._prefill_streams) if (self._prefill_streams and logits_out is None) else 1
+        main = torch.cuda.current_stream(dev)
+        for g0 in range(0, len(chunks), group):
+            part = chunks[g0:g0 + group]
+            batches = [chunk_args(b0, b1) for b0, b1 in part]
+            if len(part) == 1:
+                hiddens = [m.forward(**batches[0])]
+            else:
+                streams = self._prefill_streams[:len(part)]
+                for s_ in streams:
+                    s_.wait_stream(main)
+                hiddens = m.forward_overlapped(batches, streams)
+                for s_ in streams:
+                    main.wait_stream(s_)
+            for (b0, b1), hidden in zip(part, hiddens):
+                tok, lg = m.greedy_token(hidden)
+                first[b0:b1] = tok
+                if logits_out is not None:
+                    logits_out.append(("prefill", b0, lg))
+            del batches, hiddens
         for r in ids:
             kv.commit(r, P)
         out[:, 0] = first

@@ -44,6 +44,14 @@ def main():
     print(f"[rank {rank}] peer-collective decode: graph equal to eager {peer_equal}, logit err vs NCCL run "
           f"{err_peer:.4f} / {err_peer_dec:.4f}", flush=True)
     graphs_equal = graphs_equal and peer_equal and err_peer < 3e-2 and err_peer_dec < 3e-2
+    # prompt chunks prefilled two at a time on two streams (one chunk's all-reduce overlaps the other's compute):
+    # the same tokens as the same chunks prefilled one after the other
+    toks_seq = tp.generate(prompts, 16, prefill_chunk=2, logits_out=[])
+    toks_ovl = tp.generate(prompts, 16, prefill_chunk=2)
+    torch.cuda.synchronize()
+    overlap_equal = torch.equal(toks_seq, toks_ovl)
+    print(f"[rank {rank}] overlapped prefill equal to sequential: {overlap_equal}", flush=True)
+    graphs_equal = graphs_equal and overlap_equal
     w_1 = make_rank_weights(cfg, 0, 1, 5, f"cuda:{local}", gen_device="cpu")
     one = GenerationRunner(TPDecoder(cfg, w_1, 0, 1, None, f"cuda:{local}"), 4, 64, use_cuda_graph=False)
     logs_1 = []
