@@ -364,7 +364,7 @@ WORKLOADS = {w.name: w for w in (PagedDecode, ContigDecode, Int8Decode, Int8KVDe
 
 
 def run_engine(args):
-    """BASELINE configs[4]: Qwen3-8B-shaped decoder, random-init bf16 weights, 256 requests x 1024-token
+    """BASELINE.json configs[4]: Qwen3-8B-shaped decoder, random-init bf16 weights, 256 requests x 1024-token
     prompts, greedy generation of 256 tokens, paged KV, tensor parallel over all ranks (by KV-head group).
     One step = the whole generation (prefill + 255 decode steps)."""
     rank, world, local = dist_setup(args.gpus)

@@ -1,7 +1,7 @@
 """Static-batch generation: packed prompt prefill in chunks, then greedy decode steps replayed
 from a CUDA graph.  (The reference's scheduler, flash_attn_llm/engine/scheduler.py:15-247, does block
-accounting for continuous batching; this slice serves one fixed batch, the shape of BASELINE
-configuration 5.)"""
+accounting for continuous batching; this slice serves one fixed batch: 256 requests with 1024-token
+prompts and 256 new tokens each is the shape it is measured on.)"""
 from __future__ import annotations
 
 from typing import List, Optional
@@ -22,10 +22,10 @@ class GenerationRunner:
         self.kv = PagedKVCache(num_blocks=max_batch * self.max_blocks, num_layers=cfg.num_layers,
                                num_kv_heads=model.kl, head_dim=cfg.head_dim, max_batch=max_batch,
                                max_blocks_per_seq=self.max_blocks, device=model.device)
-        # The decode step is replayed from one CUDA graph on a single rank, and from a chain of graphs with
-        # the NCCL collectives issued eagerly in between under tensor parallelism (NCCL calls are not captured).
-        # With peer_collectives the decode step's collectives are the library's peer-memory kernels, and the
-        # whole step is one CUDA graph under tensor parallelism too.
+        # The decode step is replayed from one CUDA graph on a single rank.  Under tensor parallelism it is a
+        # chain of graphs with the NCCL collectives issued eagerly in between (NCCL calls are not captured),
+        # or - with peer_collectives - again one CUDA graph, the collectives being the library's peer-memory
+        # kernels inside it.
         self.use_cuda_graph = use_cuda_graph
         self._gather_off = 0
         if peer_collectives and model.world > 1:
