@@ -541,43 +541,51 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
     };
     if constexpr (INT8) ks_next = load_ks(0);
 
-    for (int n = 0; n < n_my; ++n) {
+    // Per-page state, produced by begin_page() in page order: ring stage, visibility mask, page index and
+    // the scales that go with the page.
+    struct PageState {
+      uint32_t st, vmask, sc;
+      int page;
+      float ks;
+    };
+    // Takes the next page of this warp: rotates the prefetched scales and masks, claims the ring stage and
+    // waits for the page's data.  Called once per page, in order.
+    auto begin_page = [&](int n) -> PageState {
+      PageState ps;
       if constexpr (INT8) {
         ks_cur = ks_next;
         ks_next = load_ks(n + 1);
       }
-      const uint32_t vmask = vmask_next;
+      ps.vmask = vmask_next;
       vmask_next = (n + 1 < n_my) ? vmask_of(page_of(n + 1)) : 0u;
       if constexpr (KV8) {
         sc_cur = sc_next;
         sc_next = load_sc(n + 1);
       }
-      const uint32_t st = st_cons;
+      ps.ks = ks_cur;
+      ps.sc = sc_cur;
+      ps.st = st_cons;
       const uint32_t parity = par_cons;
       if (++st_cons == (uint32_t)S) {
         st_cons = 0;
         par_cons ^= 1u;
       }
-      if (!mbar_wait(bar0 + st * 8, parity)) {
+      if (!mbar_wait(bar0 + ps.st * 8, parity)) {
         if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
       }
+      ps.page = page_of(n);
+      return ps;
+    };
+
+    // Scores of one page (all tokens, not yet masked), base 2.
+    auto compute_scores = [&](const PageState& ps, float (&s)[2][4]) {
+      const uint32_t st = ps.st, vmask = ps.vmask;
+      const int page = ps.page;
+      const float ks_cur = ps.ks;
+      const uint32_t sc_cur = ps.sc;
       const uint32_t kbase = stage0 + st * (2 * PAGE_BYTES);
-      const uint32_t vbase = kbase + PAGE_BYTES;
-      const int page = page_of(n);
-
-      if (!KV8 && vmask != 0xffffu) {
-        // zero the V rows of tokens that are not attended so that 0 * garbage cannot make NaN
-        uint8_t* vptr = my_stages + (size_t)st * (2 * PAGE_BYTES) + PAGE_BYTES;
-        for (int i = lane; i < 16 * 8 * NSLAB; i += 32) {
-          const int sl = i / 128, r = i - sl * 128;      // r: row * 8 + chunk
-          if (!((vmask >> (r >> 3)) & 1u))
-            *reinterpret_cast<uint4*>(vptr + sl * SLAB_BYTES + (r >> 3) * 128 + (r & 7) * 16) = make_uint4(0, 0, 0, 0);
-        }
-        __syncwarp();
-      }
-
+      (void)vmask; (void)page; (void)ks_cur; (void)sc_cur; (void)kbase;
       // ---- S = Q K^T : [16 heads x 16 tokens] ------------------------------------
-      float s[2][4];
       if constexpr (KV8) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -722,6 +730,19 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         }
       }
 
+    };
+
+    // (Computing the scores of page n+1 before the softmax of page n, with a third ring stage, was
+    // measured for the INT8 kinds: no gain for INT8-QK, 4 % slower for INT8-KV.)
+    for (int n = 0; n < n_my; ++n) {
+      const PageState ps_cur = begin_page(n);
+      float s[2][4];
+      compute_scores(ps_cur, s);
+      const uint32_t st = ps_cur.st, vmask = ps_cur.vmask;
+      const uint32_t sc_cur = ps_cur.sc;
+      const uint32_t vbase = stage0 + st * (2 * PAGE_BYTES) + PAGE_BYTES;
+      (void)sc_cur; (void)vbase;
+
       if (vmask != 0xffffu) {
 #pragma unroll
         for (int j = 0; j < 2; ++j)
@@ -775,6 +796,17 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
             acc[i][3] *= a1;
           }
         }
+      }
+
+      if (!KV8 && vmask != 0xffffu) {
+        // zero the V rows of tokens that are not attended so that 0 * garbage cannot make NaN
+        uint8_t* vptr = my_stages + (size_t)st * (2 * PAGE_BYTES) + PAGE_BYTES;
+        for (int i = lane; i < 16 * 8 * NSLAB; i += 32) {
+          const int sl = i / 128, r = i - sl * 128;      // r: row * 8 + chunk
+          if (!((vmask >> (r >> 3)) & 1u))
+            *reinterpret_cast<uint4*>(vptr + sl * SLAB_BYTES + (r >> 3) * 128 + (r & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
       }
 
       // ---- O += P V --------------------------------------------------------------
