@@ -142,9 +142,18 @@ class PagedDecode:
             e = min(s + chunk, self.n_pages)
             self.k_cache[s:e] = torch.randn(e - s, self.H_KV, 16, self.D, generator=g, device=device).half()
             self.v_cache[s:e] = torch.randn(e - s, self.H_KV, 16, self.D, generator=g, device=device).half()
-        self.q_h = torch.randn(self.B, self.H_Q, 1, self.D, generator=torch.Generator().manual_seed(seed)).half().pin_memory()
-        self.bt_h = self.block_table_h.pin_memory()
-        self.sl_h = self.seq_lens_h.pin_memory()
+        # the per-step inputs live in ONE pinned host allocation (q | block_table | seq_lens), so that the
+        # end-to-end step moves them with a single host-to-device copy
+        q_bytes, bt_bytes = self.B * self.H_Q * self.D * 2, self.block_table_h.numel() * 4
+        self._in_off = (0, q_bytes, q_bytes + bt_bytes, q_bytes + bt_bytes + self.B * 4)
+        self.in_h = torch.empty(self._in_off[3], dtype=torch.uint8).pin_memory()
+        self.q_h = self.in_h[:q_bytes].view(torch.float16).view(self.B, self.H_Q, 1, self.D)
+        self.bt_h = self.in_h[q_bytes:q_bytes + bt_bytes].view(torch.int32).view(self.block_table_h.shape)
+        self.sl_h = self.in_h[q_bytes + bt_bytes:].view(torch.int32)
+        self.q_h.copy_(torch.randn(self.B, self.H_Q, 1, self.D, generator=torch.Generator().manual_seed(seed)).half())
+        self.bt_h.copy_(self.block_table_h)
+        self.sl_h.copy_(self.seq_lens_h)
+        self.in_d = torch.empty(self._in_off[3], dtype=torch.uint8, device=device)
         self.q = self.q_h.to(device)
         self.bt = self.bt_h.to(device)
         self.sl = self.sl_h.to(device)
@@ -169,9 +178,11 @@ class PagedDecode:
     def step_e2e(self, fa):
         # per-step inputs of a decode iteration: the new queries, the block table and the lengths;
         # the KV pool is resident state (it lives on the device in the reference as well)
-        q = self.q_h.to(self.device, non_blocking=True)
-        bt = self.bt_h.to(self.device, non_blocking=True)
-        sl = self.sl_h.to(self.device, non_blocking=True)
+        o = self._in_off
+        self.in_d.copy_(self.in_h, non_blocking=True)
+        q = self.in_d[:o[1]].view(torch.float16).view(self.B, self.H_Q, 1, self.D)
+        bt = self.in_d[o[1]:o[2]].view(torch.int32).view(self.block_table_h.shape)
+        sl = self.in_d[o[2]:].view(torch.int32)
         out = fa.forward_paged_decode_gqa_fp16(q, self.k_cache, self.v_cache, bt, sl, self.max_blocks)
         self.out_h.copy_(out, non_blocking=True)
         return out

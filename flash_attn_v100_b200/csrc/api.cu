@@ -165,7 +165,7 @@ unsigned int next_epoch() {
   return v;
 }
 
-constexpr int kMaxDecodeCtas = 148 * 4 * 2;  // bound used to size workspaces on any sm_100 part
+using fa::kMaxDecodeCtas;
 
 struct DecodeCall {
   const void *q, *k, *v;
@@ -217,9 +217,8 @@ int run_decode(const DecodeCall& c) {
   p.status = reinterpret_cast<int32_t*>(ws + fa::kWsStatusOffset);
   p.prefix = reinterpret_cast<int32_t*>(ws + fa::kWsPrefixOffset);
   const size_t prefix_bytes = (((size_t)(c.B + 1) * 4 + 255) & ~(size_t)255);
-  const size_t counter_bytes = (((size_t)c.B * c.H_KV * ((G + 15) / 16) * 8 + 255) & ~(size_t)255);
-  p.counters = reinterpret_cast<unsigned long long*>(ws + fa::kWsPrefixOffset + prefix_bytes);
-  p.partials = reinterpret_cast<float*>(ws + fa::kWsPrefixOffset + prefix_bytes + counter_bytes);
+  p.counters = reinterpret_cast<unsigned long long*>(ws + fa::kWsCountersOffset);
+  p.partials = reinterpret_cast<float*>(ws + fa::kWsPrefixOffset + prefix_bytes);
   p.epoch = next_epoch();
   p.B = c.B; p.H_Q = c.H_Q; p.H_KV = c.H_KV; p.G = G;
   p.n_gblk = (G + 15) / 16;
@@ -283,8 +282,8 @@ size_t fa_decode_workspace_bytes(int B, int H_Q, int H_KV, int D) {
 }
 
 int fa_decode_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
-  FA_REQUIRE(workspace != nullptr && workspace_bytes >= 256, "workspace missing");
-  FA_CUDA(cudaMemsetAsync(workspace, 0, 256, static_cast<cudaStream_t>(stream)));
+  FA_REQUIRE(workspace != nullptr && workspace_bytes >= fa::kWsInitBytes, "workspace missing or too small");
+  FA_CUDA(cudaMemsetAsync(workspace, 0, fa::kWsInitBytes, static_cast<cudaStream_t>(stream)));
   return FA_OK;
 }
 

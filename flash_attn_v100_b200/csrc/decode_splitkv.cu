@@ -11,9 +11,10 @@
 // [c*per, (c+1)*per).  A CTA therefore reads an equal share of the KV bytes
 // whatever the length spread, and a segment is split across CTAs only at range
 // boundaries: at most two partial results per CTA.  The CTA that delivers the
-// last partial of a split segment (an arrival counter per segment, tagged with
-// a per-launch epoch so that it never needs clearing) merges them by
-// log-sum-exp.  The page prefix sums that define the unit numbering are
+// last partial of a split segment (an arrival counter per split segment, named
+// by the first CTA that works on it, tagged with a per-launch epoch and left at
+// "no arrivals" by the last arriver, so that it never needs clearing after the
+// workspace's one-time initialisation) merges them by log-sum-exp.  The page prefix sums that define the unit numbering are
 // recomputed by every CTA in shared memory: the whole decode is one launch.
 //
 // Data path.  Inside a CTA each warp streams its own pages (page i of a piece
@@ -936,7 +937,9 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       __threadfence();
       __syncthreads();
       if (threadIdx.x == 0) {
-        unsigned long long* cnt = p.counters + ((size_t)b * p.HV + hv);
+        // At most one split segment starts in a CTA's range (segments that start and end inside it are
+        // complete), so the first CTA of the segment names its counter.
+        unsigned long long* cnt = p.counters + first;
         unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(cnt);
         unsigned int arrivals;
         while (true) {
@@ -1010,9 +1013,9 @@ size_t decode_workspace_bytes(int B, int H_Q, int H_KV, int D, int max_ctas) {
   const int G = H_Q / H_KV;
   const int slot_rows = G < 16 ? G : 16;
   const int HV = H_KV * ((G + 15) / 16);
+  (void)HV;
   size_t bytes = kWsPrefixOffset;
   bytes += ((size_t)(B + 1) * 4 + 255) & ~(size_t)255;
-  bytes += ((size_t)B * HV * 8 + 255) & ~(size_t)255;
   bytes += (size_t)max_ctas * 2 * slot_rows * (D + 2) * 4;
   return (bytes + 255) & ~(size_t)255;
 }

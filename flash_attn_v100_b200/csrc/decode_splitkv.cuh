@@ -31,7 +31,8 @@ struct DecodeParams {
   const __half* v_scale_h;     // int8 cache only: [B, H_KV, N] fp16
   int32_t* prefix;             // workspace: [B + 1] running page counts
   float* partials;             // workspace: [n_cta][2][slot_rows][D + 2]
-  unsigned long long* counters;  // workspace: [B * HV] (epoch << 32 | arrivals) per segment
+  unsigned long long* counters;  // workspace: [kMaxDecodeCtas] (epoch << 32 | arrivals), one per split
+                                 // segment, indexed by the first CTA that works on the segment
   unsigned int epoch;          // unique per launch; counters of other epochs read as zero
   int32_t* status;             // workspace: sticky status word
   int B, H_Q, H_KV, G;         // G = H_Q / H_KV
@@ -58,8 +59,15 @@ struct DecodeLaunchConfig {
 
 // Workspace layout helpers (host).
 size_t decode_workspace_bytes(int B, int H_Q, int H_KV, int D, int max_ctas);
-constexpr size_t kWsStatusOffset = 0;     // int32 status word (+ padding to 256 B)
-constexpr size_t kWsPrefixOffset = 256;   // int32 prefix[B + 1]
+// Workspace layout: [status 256 B][arrival counters][prefix sums][partials].  The status word and the
+// counters are at fixed offsets and are zeroed when the workspace is initialised; the counters are only
+// ever written by the decode kernels (which leave them at "no arrivals"), so a launch never mistakes
+// stale bytes of another region for arrivals, whatever shapes the workspace served before.
+constexpr int kMaxDecodeCtas = 148 * 4 * 2;  // bound on the persistent grid, sizes the counters and partials
+constexpr size_t kWsStatusOffset = 0;        // int32 status word (+ padding to 256 B)
+constexpr size_t kWsCountersOffset = 256;    // u64 counters[kMaxDecodeCtas]
+constexpr size_t kWsPrefixOffset = kWsCountersOffset + (((size_t)kMaxDecodeCtas * 8 + 255) & ~(size_t)255);  // int32 prefix[B + 1]
+constexpr size_t kWsInitBytes = kWsPrefixOffset;   // what fa_decode_workspace_init zeroes
 
 // Launch the decode on `stream` (one kernel; a prefix-sum pre-pass only when B is too large for
 // the in-kernel scan).  kmap/vmap are 2-D tensor maps over

@@ -55,7 +55,9 @@ const char* fa_last_error(void);
  * Returns 0 on invalid arguments. */
 size_t fa_decode_workspace_bytes(int B, int H_Q, int H_KV, int D);
 
-/* Zero the status word of a workspace (do this once after allocating it). */
+/* Zero the status word and the arrival counters at the head of a workspace.  REQUIRED once
+ * after allocating it, before its first use (the counters must not start from arbitrary
+ * bytes); afterwards the kernels keep them consistent, whatever shapes the workspace serves. */
 int fa_decode_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Read back (synchronously: it waits for `stream`) the sticky device-side status

@@ -252,3 +252,29 @@ def test_group_sizes_beyond_eight_heads(fa, heads):
         out = fa.forward_decode_gqa_fp16(q.cuda(), k.cuda(), v.cuda(), True, cache_len)
         assert _err(out, orc.decode_gqa(q, k, v, True, cache_len, final_cast=False)) < TOL, (heads, cache_len)
     _finish(fa)
+
+
+def test_split_segments_after_a_large_batch_on_the_same_workspace(fa):
+    """The scratch of a stream is shared by calls of any shape.  A large batch leaves its page prefix sums
+    (all small integers) in it; the arrival counters of later calls must not be read from such leftovers.
+    Small batches whose segments are all split across CTAs, over many consecutive launches."""
+    torch.manual_seed(33)
+    Bl, H_Q, H_KV, D = 4500, 8, 2, 64
+    lens = torch.randint(1, 40, (Bl,), dtype=torch.int32)
+    k = torch.randn(Bl, H_KV, 48, D).half()
+    v = torch.randn(Bl, H_KV, 48, D).half()
+    q = torch.randn(Bl, H_Q, 1, D).half()
+    order = torch.randperm(Bl * 3, generator=torch.Generator().manual_seed(6)).tolist()
+    kc, vc, bt, mnb = orc.build_paged_cache(k, v, lens, order)
+    fa.forward_paged_decode_gqa_fp16(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), lens.cuda(), mnb)
+    # 2 sequences x 16 KV heads x 2 pages: one page per CTA, every segment is merged from two partials
+    B, H, N, Ds = 2, 16, 33, 128
+    qs = torch.randn(B, H, 1, Ds).half()
+    ks_ = torch.randn(B, H, N, Ds).half()
+    vs_ = torch.randn(B, H, N, Ds).half()
+    ref = orc.decode_gqa(qs, ks_, vs_, True, 20, final_cast=False)
+    qc, kc2, vc2 = qs.cuda(), ks_.cuda(), vs_.cuda()
+    for it in range(60):
+        out = fa.forward_decode_gqa_fp16(qc, kc2, vc2, True, 20)
+        assert _err(out, ref) < TOL, it
+    _finish(fa)
