@@ -72,3 +72,20 @@ def test_python_checks_raise_runtime_error_like_torch_check():
         fa.forward_fp16(k, k, k, True)
     with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
         fa.forward_paged_decode_gqa_fp16(q, k, k, q, q, 1)
+
+
+def test_decode_workspace_layout_is_shape_independent_at_its_head():
+    """The status word and the arrival counters sit at fixed offsets (zeroed by fa_decode_workspace_init);
+    only what follows them depends on the shape."""
+    from flash_attn_v100_b200 import _lib
+    lib = _lib.load()
+    head = 256 + 1184 * 8                                   # status + one counter per possible CTA
+    assert head % 256 == 0
+    for B, H_Q, H_KV, D in [(1, 8, 8, 64), (64, 32, 8, 128), (4500, 8, 2, 64), (3, 40, 2, 256)]:
+        G = H_Q // H_KV
+        rows = min(G, 16)
+        want = head + ((B + 1) * 4 + 255) // 256 * 256 + 1184 * 2 * rows * (D + 2) * 4
+        want = (want + 255) // 256 * 256
+        assert lib.fa_decode_workspace_bytes(B, H_Q, H_KV, D) == want
+    assert lib.fa_decode_workspace_bytes(2, 8, 3, 128) == 0      # H_Q not divisible by H_KV
+    assert lib.fa_decode_workspace_bytes(2, 8, 2, 96) == 0       # head dimension not built
