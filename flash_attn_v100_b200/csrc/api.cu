@@ -42,7 +42,13 @@ int fail(int code, const char* fmt, ...) {
     if (e__ != cudaSuccess) return fail(FA_ERR_CUDA, #call " failed: %s", cudaGetErrorString(e__)); \
   } while (0)
 
-bool supported_d(int D) { return D == 64 || D == 128 || D == 256; }
+bool supported_d(int D) { return D == 64 || D == 128 || D == 256; }   // head dimensions the prefill kernels serve
+// Decode kernels are built for 64, 128 and 256 columns; any head dimension from 64 to 256 that keeps rows
+// 16-byte aligned runs on the next larger build (the missing columns read as zeros through the tensor maps).
+int padded_decode_d(int D) {
+  if (D < 64 || D > 256 || D % 8 != 0) return 0;
+  return D <= 64 ? 64 : (D <= 128 ? 128 : 256);
+}
 
 // ---- per-device facts -------------------------------------------------------
 struct DeviceInfo {
@@ -116,10 +122,10 @@ int make_rows_map_u8(CUtensorMap* map, const void* base, long long rows, int D) 
   if (rc != FA_OK) return rc;
   cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)D};
-  cuuint32_t box[2] = {(cuuint32_t)(D < 128 ? D : 128), 16};
+  cuuint32_t box[2] = {(cuuint32_t)(D <= 64 ? 64 : 128), 16};   // columns past D read as zeros
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, D < 128 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, D <= 64 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(FA_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return FA_OK;
@@ -193,7 +199,10 @@ int run_decode(const DecodeCall& c) {
   if (rc != FA_OK) return rc;
   const int G = c.H_Q / c.H_KV;
   const int slot_rows = G < 16 ? G : 16;
-  const size_t need_ws = fa::decode_workspace_bytes(c.B, c.H_Q, c.H_KV, c.D, kMaxDecodeCtas);
+  const int Dp = padded_decode_d(c.D);      // head dimension of the kernel build that serves c.D
+  if (Dp == 0 || (c.kv8 && c.D % 16 != 0))
+    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built for this operator", c.D);
+  const size_t need_ws = fa::decode_workspace_bytes(c.B, c.H_Q, c.H_KV, Dp, kMaxDecodeCtas);
   if (c.ws == nullptr || c.ws_bytes < need_ws)
     return fail(FA_ERR_WORKSPACE, "decode workspace too small: need %zu bytes, got %zu", need_ws, c.ws_bytes);
   if ((reinterpret_cast<uintptr_t>(c.ws) & 255) != 0)
@@ -201,7 +210,7 @@ int run_decode(const DecodeCall& c) {
   if (c.rows_total >= (1ll << 31)) return fail(FA_ERR_UNSUPPORTED, "KV cache has too many rows for one tensor map");
 
   const int kv_elem_bytes = c.kv8 ? 1 : 2;
-  fa::DecodeLaunchConfig cfg = pick_decode_config(c.D, G, slot_rows, c.B, kv_elem_bytes, c.int8, di);
+  fa::DecodeLaunchConfig cfg = pick_decode_config(Dp, G, slot_rows, c.B, kv_elem_bytes, c.int8, di);
   fa::DecodeParams p;
   memset(&p, 0, sizeof(p));
   p.q = static_cast<const __half*>(c.q);
@@ -221,6 +230,7 @@ int run_decode(const DecodeCall& c) {
   p.partials = reinterpret_cast<float*>(ws + fa::kWsPrefixOffset + prefix_bytes);
   p.epoch = next_epoch();
   p.B = c.B; p.H_Q = c.H_Q; p.H_KV = c.H_KV; p.G = G;
+  p.D_real = c.D;
   p.n_gblk = (G + 15) / 16;
   p.HV = c.H_KV * p.n_gblk;
   p.mode = c.mode; p.fixed_len = c.fixed_len; p.N = c.N;
@@ -246,9 +256,9 @@ int run_decode(const DecodeCall& c) {
   if (rc != FA_OK) return rc;
   rc = c.kv8 ? make_rows_map_u8(&vmap, c.v, c.rows_total, c.D) : make_rows_map(&vmap, c.v, c.rows_total, c.D, 16);
   if (rc != FA_OK) return rc;
-  const size_t smem = fa::decode_smem_bytes(c.D, cfg.warps, cfg.stages, slot_rows, c.B, kv_elem_bytes);
+  const size_t smem = fa::decode_smem_bytes(Dp, cfg.warps, cfg.stages, slot_rows, c.B, kv_elem_bytes);
   const int kind = c.kv8 ? fa::kKindInt8KV : (c.int8 ? fa::kKindInt8QK : fa::kKindF16);
-  cudaError_t e = fa::launch_decode(kmap, vmap, p, c.D, kind, cfg.warps, smem, c.stream);
+  cudaError_t e = fa::launch_decode(kmap, vmap, p, Dp, kind, cfg.warps, smem, c.stream);
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, "decode launch failed: %s", cudaGetErrorString(e));
   return FA_OK;
 }
@@ -260,7 +270,8 @@ int check_decode_common(const void* q, const void* k, const void* v, const void*
   FA_REQUIRE(H_Q >= H_KV, "H_Q must be >= H_KV");
   FA_REQUIRE(H_Q % H_KV == 0, "H_Q must be divisible by H_KV");
   FA_REQUIRE(D <= 256, "D must be <= 256");
-  if (!supported_d(D)) return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (supported: 64, 128, 256)", D);
+  if (padded_decode_d(D) == 0)
+    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (decode serves multiples of 8 from 64 to 256)", D);
   FA_REQUIRE((reinterpret_cast<uintptr_t>(k) & 15) == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0,
              "k and v must be 16-byte aligned");
   FA_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
@@ -277,8 +288,8 @@ int fa_version(void) { return 100; }
 const char* fa_last_error(void) { return g_err; }
 
 size_t fa_decode_workspace_bytes(int B, int H_Q, int H_KV, int D) {
-  if (B <= 0 || H_Q <= 0 || H_KV <= 0 || H_Q % H_KV != 0 || !supported_d(D)) return 0;
-  return fa::decode_workspace_bytes(B, H_Q, H_KV, D, kMaxDecodeCtas);
+  if (B <= 0 || H_Q <= 0 || H_KV <= 0 || H_Q % H_KV != 0 || padded_decode_d(D) == 0) return 0;
+  return fa::decode_workspace_bytes(B, H_Q, H_KV, padded_decode_d(D), kMaxDecodeCtas);
 }
 
 int fa_decode_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
@@ -486,8 +497,9 @@ int fa_paged_decode_gqa_f16_static_scratch(const void* q, const void* k_cache, c
   // argument errors first, so that a bad call never touches the device
   if (B <= 0 || H_Q <= 0 || H_KV <= 0 || H_Q % H_KV != 0)
     return fail(FA_ERR_INVALID_ARGUMENT, "B, H_Q, H_KV must be positive and H_Q divisible by H_KV");
-  if (!supported_d(D)) return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (supported: 64, 128, 256)", D);
-  const size_t need = fa::decode_workspace_bytes(B, H_Q, H_KV, D, kMaxDecodeCtas);
+  if (padded_decode_d(D) == 0)
+    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (decode serves multiples of 8 from 64 to 256)", D);
+  const size_t need = fa::decode_workspace_bytes(B, H_Q, H_KV, padded_decode_d(D), kMaxDecodeCtas);
   if (need > kStaticScratchBytes)
     return fail(FA_ERR_WORKSPACE,
                 "this shape needs %zu bytes of decode scratch but the built-in scratch holds %zu: use "

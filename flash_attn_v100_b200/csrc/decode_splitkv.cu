@@ -344,8 +344,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
     // sequences with nothing to attend: zeros by definition (no unit ever touches their output)
     for (int bb = 0; bb < p.B; ++bb) {
       if (pre[bb + 1] != pre[bb]) continue;
-      __half* o = p.out + (size_t)bb * p.H_Q * D;
-      for (int e = threadIdx.x; e < p.H_Q * D; e += blockDim.x) o[e] = __float2half_rn(0.f);
+      __half* o = p.out + (size_t)bb * p.H_Q * p.D_real;
+      for (int e = threadIdx.x; e < p.H_Q * p.D_real; e += blockDim.x) o[e] = __float2half_rn(0.f);
     }
   }
   const long long T = (long long)p.HV * pre[p.B];
@@ -401,15 +401,18 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
     float q_s0 = 1.f, q_s1 = 1.f;
     float kbias0 = 0.f, kbias1 = 0.f;  // KV8 only
     {
+      // D is the padded head dimension the kernel is built for, Dr the real one: columns [Dr, D) of K and V
+      // read as zeros through the tensor maps, and the same columns of Q are taken as zero here.
+      const int Dr = p.D_real;
       const bool v0 = g < Gb, v1 = !HM && (g + 8) < Gb;
-      const __half* q0 = p.q + ((size_t)b * p.H_Q + head0 + g) * D;
-      const __half* q1 = q0 + (size_t)8 * D;
+      const __half* q0 = p.q + ((size_t)b * p.H_Q + head0 + g) * Dr;
+      const __half* q1 = q0 + (size_t)8 * Dr;
       if constexpr (KV8) {
 #pragma unroll
         for (int t = 0; t < D / 16; ++t) {
           const int d0 = 128 * (t / KPS) + 4 * KPS * (lane & 3) + 4 * (t % KPS);
-          const uint2 a = v0 ? __ldg(reinterpret_cast<const uint2*>(q0 + d0)) : make_uint2(0u, 0u);
-          const uint2 c = v1 ? __ldg(reinterpret_cast<const uint2*>(q1 + d0)) : make_uint2(0u, 0u);
+          const uint2 a = (v0 && d0 < Dr) ? __ldg(reinterpret_cast<const uint2*>(q0 + d0)) : make_uint2(0u, 0u);
+          const uint2 c = (v1 && d0 < Dr) ? __ldg(reinterpret_cast<const uint2*>(q1 + d0)) : make_uint2(0u, 0u);
           qa[t][0] = a.x; qa[t][1] = c.x; qa[t][2] = a.y; qa[t][3] = c.y;
           const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x));
           const float2 a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
@@ -429,10 +432,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       } else if constexpr (!INT8) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          qa[kk][0] = v0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + kk * 16 + cq)) : 0u;
-          qa[kk][1] = v1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + kk * 16 + cq)) : 0u;
-          qa[kk][2] = v0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + cq)) : 0u;
-          qa[kk][3] = v1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + cq)) : 0u;
+          const bool in_lo = kk * 16 + cq < Dr, in_hi = kk * 16 + 8 + cq < Dr;
+          qa[kk][0] = (v0 && in_lo) ? __ldg(reinterpret_cast<const uint32_t*>(q0 + kk * 16 + cq)) : 0u;
+          qa[kk][1] = (v1 && in_lo) ? __ldg(reinterpret_cast<const uint32_t*>(q1 + kk * 16 + cq)) : 0u;
+          qa[kk][2] = (v0 && in_hi) ? __ldg(reinterpret_cast<const uint32_t*>(q0 + kk * 16 + 8 + cq)) : 0u;
+          qa[kk][3] = (v1 && in_hi) ? __ldg(reinterpret_cast<const uint32_t*>(q1 + kk * 16 + 8 + cq)) : 0u;
         }
       } else {
         if (v0) q_s0 = __ldg(p.q_scale + (size_t)b * p.H_Q + head0 + g);
@@ -440,18 +444,24 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         // Slot 4c+i of k-step kk of the int8 MMA stands for head dimension
         // 32*kk + {2c, 2c+1, 8+2c, 9+2c}[i], slot 16+4c+i for the same plus 16: these are the values a
         // lane holds after ldmatrix of the fp16 K tile, so K needs no shuffling before it is quantised.
-        auto quant4 = [](const __half* src, float s) -> uint32_t {
-          const __half2 h01 = __ldg(reinterpret_cast<const __half2*>(src));
-          const __half2 h23 = __ldg(reinterpret_cast<const __half2*>(src + 8));
-          return quant_exact1(__low2float(h01), s) | (quant_exact1(__high2float(h01), s) << 8) |
-                 (quant_exact1(__low2float(h23), s) << 16) | (quant_exact1(__high2float(h23), s) << 24);
+        auto quant4 = [Dr](const __half* row, int d, float s) -> uint32_t {
+          uint32_t out = 0;
+          if (d < Dr) {
+            const __half2 h01 = __ldg(reinterpret_cast<const __half2*>(row + d));
+            out |= quant_exact1(__low2float(h01), s) | (quant_exact1(__high2float(h01), s) << 8);
+          }
+          if (d + 8 < Dr) {
+            const __half2 h23 = __ldg(reinterpret_cast<const __half2*>(row + d + 8));
+            out |= (quant_exact1(__low2float(h23), s) << 16) | (quant_exact1(__high2float(h23), s) << 24);
+          }
+          return out;
         };
 #pragma unroll
         for (int kk = 0; kk < D / 32; ++kk) {
-          qa[kk][0] = v0 ? quant4(q0 + kk * 32 + cq, q_s0) : 0u;
-          qa[kk][1] = v1 ? quant4(q1 + kk * 32 + cq, q_s1) : 0u;
-          qa[kk][2] = v0 ? quant4(q0 + kk * 32 + 16 + cq, q_s0) : 0u;
-          qa[kk][3] = v1 ? quant4(q1 + kk * 32 + 16 + cq, q_s1) : 0u;
+          qa[kk][0] = v0 ? quant4(q0, kk * 32 + cq, q_s0) : 0u;
+          qa[kk][1] = v1 ? quant4(q1, kk * 32 + cq, q_s1) : 0u;
+          qa[kk][2] = v0 ? quant4(q0, kk * 32 + 16 + cq, q_s0) : 0u;
+          qa[kk][3] = v1 ? quant4(q1, kk * 32 + 16 + cq, q_s1) : 0u;
         }
       }
     }
@@ -908,6 +918,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       float* part = p.partials + ((size_t)blockIdx.x * 2 + slot) * p.slot_rows * ROWLEN;
       for (int e = threadIdx.x; e < Gb * D; e += blockDim.x) {
         const int row = e / D, d = e - row * D;
+        if (d >= p.D_real) continue;      // padding columns
         float M = -INFINITY;
         for (int w = 0; w < W; ++w) M = fmaxf(M, mbuf[((size_t)w * p.slot_rows + row) * ROWLEN + D]);
         float L = 0.f, O = 0.f;
@@ -918,7 +929,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           O += rp[d] * f;
         }
         if (complete) {
-          p.out[((size_t)b * p.H_Q + head0 + row) * D + d] = __float2half_rn(O / L);
+          p.out[((size_t)b * p.H_Q + head0 + row) * p.D_real + d] = __float2half_rn(O / L);
         } else {
           part[row * ROWLEN + d] = O;
           if (d == 0) {
@@ -958,9 +969,10 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       __syncthreads();
       if (s_last_flag) {
         __threadfence();
-        __half* outp = p.out + ((size_t)b * p.H_Q + head0) * D;
+        __half* outp = p.out + ((size_t)b * p.H_Q + head0) * p.D_real;
         for (int e = threadIdx.x; e < Gb * D; e += blockDim.x) {
           const int row = e / D, d = e - row * D;
+          if (d >= p.D_real) continue;
           float M = -INFINITY;
           for (int c = first; c <= last; ++c) {
             const int slot = ((long long)c * per >= seg_start) ? 0 : 1;
@@ -975,7 +987,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
             L += __ldcg(part + row * ROWLEN + D + 1) * f;
             O += __ldcg(part + row * ROWLEN + d) * f;
           }
-          outp[(size_t)row * D + d] = __float2half_rn(O / L);
+          outp[(size_t)row * p.D_real + d] = __float2half_rn(O / L);
         }
       }
     }

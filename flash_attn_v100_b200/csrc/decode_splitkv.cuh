@@ -36,6 +36,7 @@ struct DecodeParams {
   unsigned int epoch;          // unique per launch; counters of other epochs read as zero
   int32_t* status;             // workspace: sticky status word
   int B, H_Q, H_KV, G;         // G = H_Q / H_KV
+  int D_real;                  // head dimension of the tensors (<= the padded one the kernel is built for)
   int n_gblk;                  // ceil(G / 16): query-head blocks per KV head
   int HV;                      // H_KV * n_gblk
   int mode, fixed_len, N;      // N: tokens per (b, h_kv) row in contiguous modes

@@ -33,7 +33,9 @@ def test_workspace_size_query_and_invalid_arguments():
     from flash_attn_v100_b200 import _lib
     lib = _lib.load()
     assert lib.fa_decode_workspace_bytes(64, 32, 8, 128) > 0
-    assert lib.fa_decode_workspace_bytes(64, 32, 8, 96) == 0      # head dim not built
+    assert lib.fa_decode_workspace_bytes(64, 32, 8, 96) == lib.fa_decode_workspace_bytes(64, 32, 8, 128)  # padded
+    assert lib.fa_decode_workspace_bytes(64, 32, 8, 100) == 0     # rows would not be 16-byte aligned
+    assert lib.fa_decode_workspace_bytes(64, 32, 8, 48) == 0      # below the smallest build
     assert lib.fa_decode_workspace_bytes(64, 32, 5, 128) == 0     # H_Q % H_KV != 0
     # validation happens before any CUDA call, so it can be exercised without a device
     rc = lib.fa_decode_gqa_f16(None, None, None, None, 1, 8, 8, 16, 64, 1, 0, None, 0, None)
@@ -46,7 +48,7 @@ def test_workspace_size_query_and_invalid_arguments():
     assert rc == -1 and b"less than sequence length" in lib.fa_last_error()
     rc = lib.fa_decode_gqa_f16(p, p, p, p, 1, 8, 3, 16, 64, 1, 0, None, 0, None)
     assert rc == -1 and b"divisible" in lib.fa_last_error()
-    rc = lib.fa_decode_gqa_f16(p, p, p, p, 1, 8, 8, 16, 80, 1, 0, None, 0, None)
+    rc = lib.fa_decode_gqa_f16(p, p, p, p, 1, 8, 8, 16, 84, 1, 0, None, 0, None)
     assert rc == -2 and b"not built" in lib.fa_last_error()
     rc = lib.fa_prefill_varlen_f16(p, p, p, p, None, 1, 16, 8, 8, 64, 16, 1, None)
     assert rc == -1 and b"cu_seqlens" in lib.fa_last_error()
@@ -88,4 +90,4 @@ def test_decode_workspace_layout_is_shape_independent_at_its_head():
         want = (want + 255) // 256 * 256
         assert lib.fa_decode_workspace_bytes(B, H_Q, H_KV, D) == want
     assert lib.fa_decode_workspace_bytes(2, 8, 3, 128) == 0      # H_Q not divisible by H_KV
-    assert lib.fa_decode_workspace_bytes(2, 8, 2, 96) == 0       # head dimension not built
+    assert lib.fa_decode_workspace_bytes(2, 8, 2, 100) == 0      # head dimension not built

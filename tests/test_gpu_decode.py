@@ -160,10 +160,10 @@ def test_error_paths_raise_runtime_error(fa):
     with pytest.raises(RuntimeError, match="block size mismatch"):
         fa.forward_paged_decode_gqa_fp16(q, k, k, torch.zeros(2, 1, dtype=torch.int32, device="cuda"),
                                          torch.ones(2, dtype=torch.int32, device="cuda"), 1)
-    q96 = torch.randn(2, 8, 1, 96, device="cuda", dtype=torch.float16)
-    k96 = torch.randn(2, 8, 32, 96, device="cuda", dtype=torch.float16)
+    q100 = torch.randn(2, 8, 1, 100, device="cuda", dtype=torch.float16)
+    k100 = torch.randn(2, 8, 32, 100, device="cuda", dtype=torch.float16)
     with pytest.raises(RuntimeError, match="not built"):
-        fa.forward_decode_gqa_fp16(q96, k96, k96, True, 31)
+        fa.forward_decode_gqa_fp16(q100, k100, k100, True, 31)
 
 
 def test_bad_page_id_is_reported_not_faulted(fa):
@@ -277,4 +277,40 @@ def test_split_segments_after_a_large_batch_on_the_same_workspace(fa):
     for it in range(60):
         out = fa.forward_decode_gqa_fp16(qc, kc2, vc2, True, 20)
         assert _err(out, ref) < TOL, it
+    _finish(fa)
+
+
+@pytest.mark.parametrize("D", [72, 80, 96, 112, 160, 192, 248])
+def test_head_dimensions_between_the_builds(fa, D):
+    """Any head dimension from 64 to 256 that is a multiple of 8 (the reference takes any D <= 256): the next
+    larger kernel build serves it, the missing columns read as zeros."""
+    torch.manual_seed(D)
+    B, H_Q, H_KV, N = 3, 8, 2, 77
+    q = torch.randn(B, H_Q, 1, D).half()
+    k = torch.randn(B, H_KV, N, D).half()
+    v = torch.randn(B, H_KV, N, D).half()
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    out = fa.forward_decode_gqa_fp16(qc, kc, vc, True, 60)
+    assert out.shape == q.shape
+    assert _err(out, orc.decode_gqa(q, k, v, True, 60, final_cast=False)) < TOL
+    lens = torch.tensor([0, 33, 76], dtype=torch.int32)
+    out = fa.forward_continuous_batching_fp16(qc, kc, vc, lens.cuda(), True)
+    assert _err(out, orc.continuous_batching_decode(q, k, v, lens, True, final_cast=False)) < TOL
+    seq_lens = torch.tensor([5, 0, 77], dtype=torch.int32)
+    kp, vp, bt, mnb = orc.build_paged_cache(k, v, seq_lens, [4, 1, 7, 0, 9, 3, 8, 2, 5, 6, 10, 11, 12, 13, 14])
+    out = fa.forward_paged_decode_gqa_fp16(qc, kp.cuda(), vp.cuda(), bt.cuda(), seq_lens.cuda(), mnb)
+    assert _err(out, orc.paged_decode(q, kp, vp, bt, seq_lens, final_cast=False)) < TOL
+    out = fa.forward_decode_sliding_window_gqa(qc, kc, vc, True, 70, 24, 3)
+    assert _err(out, orc.sliding_window_decode(q, k, v, True, 70, 24, 3, final_cast=False)) < TOL
+    if D % 16 == 0:
+        k8, ks = orc.quantize_kv_int8(k)
+        v8, vs = orc.quantize_kv_int8(v)
+        out = fa.forward_decode_int8_kv_cache_gqa(qc, k8.cuda(), v8.cuda(), ks.cuda(), vs.cuda(), 70)
+        assert _err(out, orc.decode_int8_kv_cache_gqa(q, k8, v8, ks, vs, 70, final_cast=False)) < TOL
+    qs = (q.abs().amax(-1).float().squeeze(-1) / 127).contiguous()
+    ksc = (k.abs().amax(-1).float() / 127).contiguous()
+    out, scores = fa.forward_decode_int8_gqa(qc, kc, vc, qs.cuda(), ksc.cuda(), 70, return_scores=True)
+    ref_out, ref_dots = orc.decode_int8_gqa(q, k, v, qs, ksc, 70, final_cast=False)
+    assert torch.equal(scores.cpu()[:, :, :71], ref_dots[:, :, :71])
+    assert _err(out, ref_out) < TOL
     _finish(fa)
