@@ -534,7 +534,13 @@ static int run_prefill(fa::PrefillParams& p, int D, cudaStream_t stream) {
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc != FA_OK) return rc;
+  // kernels are built for 64, 128 and 256 columns; a head dimension in between runs on the next larger build
+  const int Dp = padded_decode_d(D);
+  if (Dp == 0)
+    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (multiples of 8 from 64 to 256 are)", D);
+  p.D_real = D;
   p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+  D = Dp;
   cudaError_t e;
   const bool tc5_ok = fa::prefill_tc5_supported(p, D);
   if (g_prefill_impl == 2 && !tc5_ok)

@@ -21,7 +21,9 @@ struct PrefillParams {
   long long q_batch_stride, q_head_stride, q_tok_stride;     // elements
   long long kv_batch_stride, kv_head_stride, kv_tok_stride;  // elements
   int causal;
-  float scale_log2;           // log2(e) / sqrt(D)
+  int D_real;                 // head dimension of the tensors; the kernels are built for 64 / 128 / 256 columns
+                              // and take the columns [D_real, D) as zeros
+  float scale_log2;           // log2(e) / sqrt(D_real)
 };
 
 cudaError_t launch_prefill_mma(const PrefillParams& p, int D, cudaStream_t stream);

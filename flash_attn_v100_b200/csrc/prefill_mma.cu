@@ -26,14 +26,15 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 
 template <int D, int ROWS, int THREADS>
 __device__ __forceinline__ void load_tile(uint32_t smem_base, const __half* gbase, long long tok_stride,
-                                          int row0, int row_limit, int tid) {
-  // rows [row0, row0 + ROWS) of a sequence; rows >= row_limit are zero-filled
+                                          int row0, int row_limit, int real_chunks, int tid) {
+  // rows [row0, row0 + ROWS) of a sequence; rows >= row_limit and 16-byte chunks >= real_chunks (columns
+  // past the tensors' head dimension) are zero-filled
   constexpr int CH = D / 8;
 #pragma unroll
   for (int i = tid; i < ROWS * CH; i += THREADS) {
     const int r = i / CH, c = i - r * CH;
-    const bool ok = (row0 + r) < row_limit;
-    const __half* src = gbase + (long long)(ok ? (row0 + r) : 0) * tok_stride + c * 8;
+    const bool ok = (row0 + r) < row_limit && c < real_chunks;
+    const __half* src = gbase + (long long)(ok ? (row0 + r) : 0) * tok_stride + (ok ? c : 0) * 8;
     cp_async_16(smem_base + swz<D>(r, c), src, ok);
   }
 }
@@ -77,9 +78,10 @@ __global__ void __launch_bounds__(BM * 2) prefill_mma_kernel(const PrefillParams
   const int kv_end = p.causal ? ((q0 + BM) < len ? (q0 + BM) : len) : len;
   const int n_tiles = (kv_end + BN - 1) / BN;
 
-  load_tile<D, BM, THREADS>(sQ, qg, p.q_tok_stride, q0, len, tid);
-  load_tile<D, BN, THREADS>(sK0, kg, p.kv_tok_stride, 0, len, tid);
-  load_tile<D, BN, THREADS>(sV0, vg, p.kv_tok_stride, 0, len, tid);
+  const int real_chunks = p.D_real >> 3;
+  load_tile<D, BM, THREADS>(sQ, qg, p.q_tok_stride, q0, len, real_chunks, tid);
+  load_tile<D, BN, THREADS>(sK0, kg, p.kv_tok_stride, 0, len, real_chunks, tid);
+  load_tile<D, BN, THREADS>(sV0, vg, p.kv_tok_stride, 0, len, real_chunks, tid);
   cp_async_commit();
 
   float acc[NT_O][4];
@@ -91,8 +93,8 @@ __global__ void __launch_bounds__(BM * 2) prefill_mma_kernel(const PrefillParams
   for (int t = 0; t < n_tiles; ++t) {
     const int buf = t & 1;
     if (t + 1 < n_tiles) {
-      load_tile<D, BN, THREADS>(sK0 + (buf ^ 1) * BN * D * 2, kg, p.kv_tok_stride, (t + 1) * BN, len, tid);
-      load_tile<D, BN, THREADS>(sV0 + (buf ^ 1) * BN * D * 2, vg, p.kv_tok_stride, (t + 1) * BN, len, tid);
+      load_tile<D, BN, THREADS>(sK0 + (buf ^ 1) * BN * D * 2, kg, p.kv_tok_stride, (t + 1) * BN, len, real_chunks, tid);
+      load_tile<D, BN, THREADS>(sV0 + (buf ^ 1) * BN * D * 2, vg, p.kv_tok_stride, (t + 1) * BN, len, real_chunks, tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -202,13 +204,15 @@ __global__ void __launch_bounds__(BM * 2) prefill_mma_kernel(const PrefillParams
     __half* o = og + (long long)qrow0 * p.q_tok_stride;
 #pragma unroll
     for (int i = 0; i < NT_O; ++i)
-      *reinterpret_cast<__half2*>(o + i * 8 + cq) = __floats2half2_rn(acc[i][0] * inv0, acc[i][1] * inv0);
+      if (i * 8 < p.D_real)
+        *reinterpret_cast<__half2*>(o + i * 8 + cq) = __floats2half2_rn(acc[i][0] * inv0, acc[i][1] * inv0);
   }
   if (qrow0 + 8 < len) {
     __half* o = og + (long long)(qrow0 + 8) * p.q_tok_stride;
 #pragma unroll
     for (int i = 0; i < NT_O; ++i)
-      *reinterpret_cast<__half2*>(o + i * 8 + cq) = __floats2half2_rn(acc[i][2] * inv1, acc[i][3] * inv1);
+      if (i * 8 < p.D_real)
+        *reinterpret_cast<__half2*>(o + i * 8 + cq) = __floats2half2_rn(acc[i][2] * inv1, acc[i][3] * inv1);
   }
 }
 

@@ -62,6 +62,7 @@ struct Tc5Params {
   long long total;
   long long o_batch_stride, o_head_stride, o_tok_stride;
   int causal;
+  int D_real;      // head dimension of the tensors (columns [D_real, D) read as zeros through the tensor maps)
   int pair_heads;  // 1: two heads x same rows; 0: one head x two row blocks
   int dense;
   int n_hg, n_rb;  // head groups and row blocks of the item grid (items = n_rb * batch * n_hg)
@@ -668,7 +669,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             w.y = pack_half2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
             w.z = pack_half2(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
             w.w = pack_half2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
+            if (c * 32 + i * 8 < p.D_real) *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
           }
         }
       }
@@ -740,12 +741,14 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   bool ok;
   if (dense) {
     const long long qrows = (long long)pp.batch * pp.H_Q * pp.N, krows = (long long)pp.batch * pp.H_KV * pp.N;
-    ok = make_map3(enc, &qmap, pp.q, D, 1, qrows, D, D) && make_map3(enc, &kmap, pp.k, D, 1, krows, D, D) &&
-         make_map3(enc, &vmap, pp.v, D, 1, krows, D, D);
+    const int Dr = pp.D_real;   // extent of the innermost dimension: the boxes' columns past it are zero-filled
+    ok = make_map3(enc, &qmap, pp.q, Dr, 1, qrows, Dr, Dr) && make_map3(enc, &kmap, pp.k, Dr, 1, krows, Dr, Dr) &&
+         make_map3(enc, &vmap, pp.v, Dr, 1, krows, Dr, Dr);
   } else {
-    ok = make_map3(enc, &qmap, pp.q, D, pp.H_Q, pp.total, D, (long long)pp.H_Q * D) &&
-         make_map3(enc, &kmap, pp.k, D, pp.H_KV, pp.total, D, (long long)pp.H_KV * D) &&
-         make_map3(enc, &vmap, pp.v, D, pp.H_KV, pp.total, D, (long long)pp.H_KV * D);
+    const int Dr = pp.D_real;
+    ok = make_map3(enc, &qmap, pp.q, Dr, pp.H_Q, pp.total, Dr, (long long)pp.H_Q * Dr) &&
+         make_map3(enc, &kmap, pp.k, Dr, pp.H_KV, pp.total, Dr, (long long)pp.H_KV * Dr) &&
+         make_map3(enc, &vmap, pp.v, Dr, pp.H_KV, pp.total, Dr, (long long)pp.H_KV * Dr);
   }
   if (!ok) return cudaErrorInvalidValue;
   Tc5Params p;
@@ -755,6 +758,7 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   p.total = pp.total;
   p.o_batch_stride = pp.q_batch_stride; p.o_head_stride = pp.q_head_stride; p.o_tok_stride = pp.q_tok_stride;
   p.causal = pp.causal;
+  p.D_real = pp.D_real;
   p.pair_heads = ((pp.H_Q / pp.H_KV) % 2 == 0) ? 1 : 0;
   p.dense = dense ? 1 : 0;
   p.scale_log2 = pp.scale_log2;

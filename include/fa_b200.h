@@ -20,10 +20,10 @@
  *  - fp16 tensors are IEEE binary16; softmax scale is always 1/sqrt(D)
  *    (the reference wrappers compute it themselves, flash_attn_kernel.cu:265).
  *  - GQA head map everywhere: h_kv = h_q / (H_Q / H_KV) (flash_attn_kernel.cu:1662).
- *  - Supported head dims: decode operators take any multiple of 8 from 64 to 256
- *    (16 for the INT8 KV cache); a dimension between two kernel builds (64, 128,
- *    256) runs on the next larger one, the missing columns read as zeros.  Prefill
- *    operators take 64, 128 and 256.  The reference takes any D <= 256.
+ *  - Supported head dims: any multiple of 8 from 64 to 256 (multiples of 16 for
+ *    the INT8 KV cache).  Kernels are built for 64, 128 and 256 columns; a
+ *    dimension in between runs on the next larger build, the missing columns read
+ *    as zeros.  (The reference takes any D <= 256.)
  */
 #ifndef FA_B200_H_
 #define FA_B200_H_

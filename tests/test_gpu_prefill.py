@@ -131,3 +131,28 @@ def test_varlen_config3_shape_sample():
     out_r = fa.forward_varlen_prefill_fp16(q[idx].contiguous(), k[idx].contiguous(), v[idx].contiguous(),
                                            cu_r.cuda(), max(lens), True)
     assert torch.equal(out_r, out[idx])
+
+
+@pytest.mark.parametrize("D", [72, 96, 112, 160, 192, 248])
+def test_head_dimensions_between_the_builds(D):
+    """Head dimensions between the kernel builds (64, 128, 256) run on the next larger one; the reference
+    takes any D <= 256.  Dense GQA (causal and not) and packed varlen."""
+    import flash_attn_v100 as fa
+    torch.manual_seed(D)
+    B, H_Q, H_KV, N = 2, 4, 2, 150
+    q = torch.randn(B, H_Q, N, D).half()
+    k = torch.randn(B, H_KV, N, D).half()
+    v = torch.randn(B, H_KV, N, D).half()
+    for causal in (True, False):
+        out = fa.forward_prefill_gqa_fp16(q.cuda(), k.cuda(), v.cuda(), causal)
+        assert out.shape == q.shape
+        assert _err(out, orc.prefill_gqa(q, k, v, causal, final_cast=False)) < TOL, (D, causal)
+    lens = [37, 150, 1, 90]
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    total = int(cu[-1])
+    qp = torch.randn(total, H_Q, D).half()
+    kp = torch.randn(total, H_KV, D).half()
+    vp = torch.randn(total, H_KV, D).half()
+    out = fa.forward_varlen_prefill_fp16(qp.cuda(), kp.cuda(), vp.cuda(), cu.cuda(), max(lens), True)
+    ref = orc.varlen_prefill(qp, kp, vp, cu, True, final_cast=False)
+    assert _err(out, ref) < TOL, D
