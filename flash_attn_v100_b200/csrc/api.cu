@@ -43,10 +43,10 @@ int fail(int code, const char* fmt, ...) {
   } while (0)
 
 bool supported_d(int D) { return D == 64 || D == 128 || D == 256; }   // head dimensions the prefill kernels serve
-// Decode kernels are built for 64, 128 and 256 columns; any head dimension from 64 to 256 that keeps rows
+// Decode kernels are built for 64, 128 and 256 columns; any head dimension up to 256 that keeps rows
 // 16-byte aligned runs on the next larger build (the missing columns read as zeros through the tensor maps).
 int padded_decode_d(int D) {
-  if (D < 64 || D > 256 || D % 8 != 0) return 0;
+  if (D < 8 || D > 256 || D % 8 != 0) return 0;
   return D <= 64 ? 64 : (D <= 128 ? 128 : 256);
 }
 
@@ -271,7 +271,7 @@ int check_decode_common(const void* q, const void* k, const void* v, const void*
   FA_REQUIRE(H_Q % H_KV == 0, "H_Q must be divisible by H_KV");
   FA_REQUIRE(D <= 256, "D must be <= 256");
   if (padded_decode_d(D) == 0)
-    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (decode serves multiples of 8 from 64 to 256)", D);
+    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (decode serves multiples of 8 up to 256)", D);
   FA_REQUIRE((reinterpret_cast<uintptr_t>(k) & 15) == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0,
              "k and v must be 16-byte aligned");
   FA_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
@@ -498,7 +498,7 @@ int fa_paged_decode_gqa_f16_static_scratch(const void* q, const void* k_cache, c
   if (B <= 0 || H_Q <= 0 || H_KV <= 0 || H_Q % H_KV != 0)
     return fail(FA_ERR_INVALID_ARGUMENT, "B, H_Q, H_KV must be positive and H_Q divisible by H_KV");
   if (padded_decode_d(D) == 0)
-    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (decode serves multiples of 8 from 64 to 256)", D);
+    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (decode serves multiples of 8 up to 256)", D);
   const size_t need = fa::decode_workspace_bytes(B, H_Q, H_KV, padded_decode_d(D), kMaxDecodeCtas);
   if (need > kStaticScratchBytes)
     return fail(FA_ERR_WORKSPACE,
@@ -537,7 +537,7 @@ static int run_prefill(fa::PrefillParams& p, int D, cudaStream_t stream) {
   // kernels are built for 64, 128 and 256 columns; a head dimension in between runs on the next larger build
   const int Dp = padded_decode_d(D);
   if (Dp == 0)
-    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (multiples of 8 from 64 to 256 are)", D);
+    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (multiples of 8 up to 256 are)", D);
   p.D_real = D;
   p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
   D = Dp;

@@ -101,8 +101,8 @@ def _workspace(device, stream_int, B, H_Q, H_KV, D):
     (device, stream), grown on demand.  Calls on one stream are ordered, so they
     may share it."""
     lib = _lib.load()
-    _chk(64 <= D <= 256 and D % 8 == 0,
-         f"head dimension {D} is not built (decode serves multiples of 8 from 64 to 256)")
+    _chk(8 <= D <= 256 and D % 8 == 0,
+         f"head dimension {D} is not built (decode serves multiples of 8 up to 256)")
     need = int(lib.fa_decode_workspace_bytes(B, H_Q, H_KV, D))
     _chk(need > 0, f"unsupported decode configuration B={B} H_Q={H_Q} H_KV={H_KV} D={D}")
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream_int)

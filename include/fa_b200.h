@@ -20,7 +20,7 @@
  *  - fp16 tensors are IEEE binary16; softmax scale is always 1/sqrt(D)
  *    (the reference wrappers compute it themselves, flash_attn_kernel.cu:265).
  *  - GQA head map everywhere: h_kv = h_q / (H_Q / H_KV) (flash_attn_kernel.cu:1662).
- *  - Supported head dims: any multiple of 8 from 64 to 256 (multiples of 16 for
+ *  - Supported head dims: any multiple of 8 up to 256 (multiples of 16 for
  *    the INT8 KV cache).  Kernels are built for 64, 128 and 256 columns; a
  *    dimension in between runs on the next larger build, the missing columns read
  *    as zeros.  (The reference takes any D <= 256.)

@@ -35,7 +35,8 @@ def test_workspace_size_query_and_invalid_arguments():
     assert lib.fa_decode_workspace_bytes(64, 32, 8, 128) > 0
     assert lib.fa_decode_workspace_bytes(64, 32, 8, 96) == lib.fa_decode_workspace_bytes(64, 32, 8, 128)  # padded
     assert lib.fa_decode_workspace_bytes(64, 32, 8, 100) == 0     # rows would not be 16-byte aligned
-    assert lib.fa_decode_workspace_bytes(64, 32, 8, 48) == 0      # below the smallest build
+    assert lib.fa_decode_workspace_bytes(64, 32, 8, 48) == lib.fa_decode_workspace_bytes(64, 32, 8, 64)   # padded
+    assert lib.fa_decode_workspace_bytes(64, 32, 8, 4) == 0       # not a multiple of 8
     assert lib.fa_decode_workspace_bytes(64, 32, 5, 128) == 0     # H_Q % H_KV != 0
     # validation happens before any CUDA call, so it can be exercised without a device
     rc = lib.fa_decode_gqa_f16(None, None, None, None, 1, 8, 8, 16, 64, 1, 0, None, 0, None)

@@ -280,9 +280,9 @@ def test_split_segments_after_a_large_batch_on_the_same_workspace(fa):
     _finish(fa)
 
 
-@pytest.mark.parametrize("D", [72, 80, 96, 112, 160, 192, 248])
+@pytest.mark.parametrize("D", [8, 32, 48, 72, 80, 96, 112, 160, 192, 248])
 def test_head_dimensions_between_the_builds(fa, D):
-    """Any head dimension from 64 to 256 that is a multiple of 8 (the reference takes any D <= 256): the next
+    """Any head dimension up to 256 that is a multiple of 8 (the reference takes any D <= 256): the next
     larger kernel build serves it, the missing columns read as zeros."""
     torch.manual_seed(D)
     B, H_Q, H_KV, N = 3, 8, 2, 77
