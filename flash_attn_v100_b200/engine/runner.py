@@ -164,6 +164,13 @@ class GenerationRunner:
             kv.release(r)
         return out
 
+    def close(self):
+        """Release the peer-memory buffers (all ranks call it; no-op without peer collectives)."""
+        self._decode_cache.clear()
+        if self.model.comm is not None:
+            self.model.comm.close()
+            self.model.comm = None
+
     def last_timing_ms(self):
         """(prefill ms, decode ms) of the last generate() call; synchronises."""
         torch.cuda.synchronize(self.model.device)

@@ -38,6 +38,7 @@ def main():
     toks_pr_again = pr.generate(prompts, 16)
     torch.cuda.synchronize()
     pr.model.comm.check()
+    pr.close()
     peer_equal = torch.equal(toks_pr_graph, toks_pr) and torch.equal(toks_pr_again, toks_pr)
     err_peer = (logs_pr[0][2] - logs_tp[0][2]).abs().max().item()
     err_peer_dec = (logs_pr[1][2] - logs_tp[1][2]).abs().max().item() if torch.equal(toks_pr[:, 0], toks_tp[:, 0]) else 0.0
