@@ -544,16 +544,20 @@ def run_b200(args):
     if rank == 0 and world == 1 and args.workload == "paged_decode" and not args.no_cpu_baseline:
         host = wl.host_copy()
         torch.set_num_threads(os.cpu_count() or 1)
-        seqs = list(range(0, wl.B, 4))  # 16 of the 64 sequences
+        seqs = list(range(wl.B))          # the whole batch, repeated for about ten seconds of CPU work
         PagedDecode.cpu_reference(host, seqs[:2])
-        t0 = time.perf_counter()
-        ref = PagedDecode.cpu_reference(host, seqs)
-        dt = time.perf_counter() - t0
-        got = wl.step(fa)[torch.tensor(seqs, device=device)].float().cpu()
+        passes, dt, ref = 0, 0.0, None
+        while passes < 40 and dt < 10.0:
+            t0 = time.perf_counter()
+            ref = PagedDecode.cpu_reference(host, seqs)
+            dt += time.perf_counter() - t0
+            passes += 1
+        got = wl.step(fa).float().cpu()
         err = (got - ref.float()).abs().max().item()
-        cpu_baseline = {"value": len(seqs) / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                        "sample": f"{len(seqs)} of {wl.B} sequences of the same batch (every 4th), one pass, "
-                                  f"{dt:.2f} s; PyTorch fp32 CPU restatement of the reference's SDPA decode oracle",
+        cpu_baseline = {"value": passes * len(seqs) / dt, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                        "kind": "port",
+                        "sample": f"all {wl.B} sequences of the same batch, {passes} passes, {dt:.1f} s; PyTorch fp32 "
+                                  f"CPU restatement of the reference's SDPA decode oracle",
                         "max_abs_err_vs_gpu": err}
 
     if rank != 0:
