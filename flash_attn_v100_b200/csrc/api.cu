@@ -134,11 +134,12 @@ int make_rows_map_u8(CUtensorMap* map, const void* base, long long rows, int D) 
 // ---- decode tuning ----------------------------------------------------------
 fa::DecodeLaunchConfig g_cfg_override = {0, 0, 0};
 
-fa::DecodeLaunchConfig pick_decode_config(int D, int G, int slot_rows, int B, int kv_elem_bytes,
+fa::DecodeLaunchConfig pick_decode_config(int D, int G, int slot_rows, int B, int kv_elem_bytes, bool int8_qk,
                                           const DeviceInfo& di) {
   fa::DecodeLaunchConfig c;
   const bool half_m = G <= 8;  // kernels for at most 8 query heads per KV head: 128 threads, more CTAs per SM
   if (kv_elem_bytes == 1) c = {4, 2, (half_m && D <= 128) ? 3 : (D == 256 ? 1 : 2)};  // dequantisation-bound
+  else if (int8_qk && half_m && D == 128) c = {4, 2, 3};   // quantisation-bound: a third CTA hides its latency
   else if (D == 256) c = {4, 2, 1};
   else if (D == 128) c = {4, 2, 2};
   else c = {4, 4, 2};
@@ -209,7 +210,7 @@ int run_decode(const DecodeCall& c) {
   if (c.rows_total >= (1ll << 31)) return fail(FA_ERR_UNSUPPORTED, "KV cache has too many rows for one tensor map");
 
   const int kv_elem_bytes = c.kv8 ? 1 : 2;
-  fa::DecodeLaunchConfig cfg = pick_decode_config(Dp, G, slot_rows, c.B, kv_elem_bytes, di);
+  fa::DecodeLaunchConfig cfg = pick_decode_config(Dp, G, slot_rows, c.B, kv_elem_bytes, c.int8, di);
   fa::DecodeParams p;
   memset(&p, 0, sizeof(p));
   p.q = static_cast<const __half*>(c.q);

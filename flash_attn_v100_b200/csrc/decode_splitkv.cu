@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(1024) decode_plan_kernel(const DecodeParams p)
 #define FA_KV8_MINB 3
 #endif
 #ifndef FA_I8QK_MINB
-#define FA_I8QK_MINB 2
+#define FA_I8QK_MINB 3
 #endif
 // Threads per CTA and CTAs per SM the kernel is compiled for.  The half-M variants keep half the
 // accumulators, which leaves room for more resident CTAs (more pages in flight, more warps to hide
