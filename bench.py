@@ -127,21 +127,19 @@ class PagedDecode:
     B, H_Q, H_KV, D = 64, 32, 8, 128
 
     def __init__(self, device, seed):
-        from flash_attn_v100_b200.synthetic import make_paged_tables
+        from flash_attn_v100_b200.synthetic import make_paged_decode_batch
         self.device = device
-        # lengths and page placement are the same on every rank (seed 0), so that the work per GPU is
-        # fixed exactly under weak scaling; the tensor values are seeded by the rank
-        t = make_paged_tables(self.B, 512, 8192, 0)
+        # lengths and page placement are the same on every rank (table seed 0), so that the work per GPU
+        # is fixed exactly under weak scaling; the tensor values are seeded by the rank.  Everything is
+        # drawn on the host from seeded CPU generators: the reference arm (`--impl reference`) rebuilds
+        # exactly the batch of rank 0 and runs the CPU implementation on it.
+        t = make_paged_decode_batch(self.B, self.H_Q, self.H_KV, self.D, 512, 8192, table_seed=0, value_seed=seed)
         self.seq_lens_h, self.block_table_h, self.n_pages = t["seq_lens"], t["block_table"], t["n_pages"]
         self.max_blocks = t["max_num_blocks"]
-        g = torch.Generator(device=device).manual_seed(seed)
-        self.k_cache = torch.empty(self.n_pages, self.H_KV, 16, self.D, dtype=torch.float16, device=device)
-        self.v_cache = torch.empty_like(self.k_cache)
-        chunk = 2048
-        for s in range(0, self.n_pages, chunk):
-            e = min(s + chunk, self.n_pages)
-            self.k_cache[s:e] = torch.randn(e - s, self.H_KV, 16, self.D, generator=g, device=device).half()
-            self.v_cache[s:e] = torch.randn(e - s, self.H_KV, 16, self.D, generator=g, device=device).half()
+        self.k_cache = t["k_cache"].to(device)
+        self.v_cache = t["v_cache"].to(device)
+        q_host = t["q"]
+        del t
         # the per-step inputs live in ONE pinned host allocation (q | block_table | seq_lens), so that the
         # end-to-end step moves them with a single host-to-device copy
         q_bytes, bt_bytes = self.B * self.H_Q * self.D * 2, self.block_table_h.numel() * 4
@@ -150,7 +148,7 @@ class PagedDecode:
         self.q_h = self.in_h[:q_bytes].view(torch.float16).view(self.B, self.H_Q, 1, self.D)
         self.bt_h = self.in_h[q_bytes:q_bytes + bt_bytes].view(torch.int32).view(self.block_table_h.shape)
         self.sl_h = self.in_h[q_bytes + bt_bytes:].view(torch.int32)
-        self.q_h.copy_(torch.randn(self.B, self.H_Q, 1, self.D, generator=torch.Generator().manual_seed(seed)).half())
+        self.q_h.copy_(q_host)
         self.bt_h.copy_(self.block_table_h)
         self.sl_h.copy_(self.seq_lens_h)
         self.in_d = torch.empty(self._in_off[3], dtype=torch.uint8, device=device)
@@ -165,12 +163,17 @@ class PagedDecode:
         self.alg_flops = 4 * self.H_Q * self.D * tokens
         self.launches_per_step = 1  # one fused split-KV kernel (scan + work + merge)
 
-    def config(self):
+    @classmethod
+    def config_of(cls, seq_lens, n_pages):
+        """The `config` of the headline line; both arms (GPU and CPU reference) print exactly this."""
         return {"workload": "paged_gqa_decode B=64 H_Q=32 H_KV=8 D=128 page=16 seq_lens~U[512,8192] (BASELINE configs[1])",
-                "batch_per_gpu": self.B, "tokens_attended_per_gpu": int(self.seq_lens_h.sum()),
-                "kv_bytes_per_gpu": int(self.k_cache.numel() * 4),
+                "batch_per_gpu": cls.B, "tokens_attended_per_gpu": int(seq_lens.sum()),
+                "kv_bytes_per_gpu": int(n_pages) * cls.H_KV * 16 * cls.D * 2 * 2,
                 "l2": "inputs larger than L2 (KV pool >> 126 MB), no flush",
                 "partition": "independent batch per rank (same lengths on every rank, values seeded by rank)"}
+
+    def config(self):
+        return self.config_of(self.seq_lens_h, self.n_pages)
 
     def step(self, fa):
         return fa.forward_paged_decode_gqa_fp16(self.q, self.k_cache, self.v_cache, self.bt, self.sl, self.max_blocks)
@@ -371,6 +374,60 @@ class VarlenPrefill:
     step_e2e = None
 
 
+class HeadShardedPagedDecode:
+    """ONE paged-decode batch of the headline shape split over the ranks by KV-head group (the reference's
+    multi-GPU partition, tensor_parallel.py:435-457 and :553-571): rank r holds KV heads
+    [r*8/N, (r+1)*8/N) of every page and the 32/N query heads that map to them; block_table and seq_lens are
+    replicated; no collective.  Strong scaling: the bytes per rank shrink with N (141 MB at N=8, about the size
+    of L2), so the step rotates over N distinct K/V pools of the same shape."""
+    name = "paged_decode_head_sharded"
+    metric = "paged_gqa_decode_tokens_per_s"
+    unit = "tokens/s"
+    bound = "hbm"
+    dtype = "fp16"
+    B, H_Q, H_KV, D = 64, 32, 8, 128
+
+    def __init__(self, device, rank, world):
+        from flash_attn_v100_b200.sharding import head_shard
+        from flash_attn_v100_b200.synthetic import make_paged_tables
+        self.shard = head_shard(self.H_Q, self.H_KV, rank, world)
+        self.hq = self.shard.q_heads[1] - self.shard.q_heads[0]
+        self.hkv = self.shard.kv_heads[1] - self.shard.kv_heads[0]
+        t = make_paged_tables(self.B, 512, 8192, 0)      # the global batch: same tables on every rank
+        self.max_blocks, self.n_pages = t["max_num_blocks"], t["n_pages"]
+        self.bt, self.sl = t["block_table"].to(device), t["seq_lens"].to(device)
+        g = torch.Generator(device=device).manual_seed(977 + rank)
+        self.pools = []
+        for _ in range(max(world, 1)):
+            k = torch.empty(self.n_pages, self.hkv, 16, self.D, dtype=torch.float16, device=device)
+            v = torch.empty_like(k)
+            for s0 in range(0, self.n_pages, 4096):
+                e = min(s0 + 4096, self.n_pages)
+                k[s0:e] = torch.randn(e - s0, self.hkv, 16, self.D, generator=g, device=device).half()
+                v[s0:e] = torch.randn(e - s0, self.hkv, 16, self.D, generator=g, device=device).half()
+            self.pools.append((k, v))
+        self.q = torch.randn(self.B, self.hq, 1, self.D, generator=g, device=device, dtype=torch.float16)
+        self.turn = 0
+        tokens = int(t["seq_lens"].sum())
+        pages = int(((t["seq_lens"] + 15) // 16).sum())
+        self.alg_bytes = decode_algorithmic_bytes(tokens, pages, self.B, self.hq, self.hkv, self.D)   # per rank
+        self.alg_flops = 4 * self.hq * self.D * tokens
+        self.units_per_step = self.B
+        self.launches_per_step = 1
+
+    def config(self):
+        return {"workload": "paged_gqa_decode B=64 H_Q=32 H_KV=8 D=128 (BASELINE configs[1]), ONE batch split by "
+                            "KV-head group", "kv_heads_per_rank": self.hkv, "q_heads_per_rank": self.hq,
+                "kv_bytes_per_rank": int(self.pools[0][0].numel() * 4), "pools_rotated": len(self.pools),
+                "l2": "the step rotates over as many distinct K/V pools as there are ranks (1.13 GB in all), so no "
+                      "launch finds its pages in L2"}
+
+    def step(self, fa):
+        k, v = self.pools[self.turn % len(self.pools)]
+        self.turn += 1
+        return fa.forward_paged_decode_gqa_fp16(self.q, k, v, self.bt, self.sl, self.max_blocks)
+
+
 WORKLOADS = {w.name: w for w in (PagedDecode, ContigDecode, Int8Decode, Int8KVDecode, SlidingWindowDecode, VarlenPrefill)}
 
 
@@ -437,6 +494,7 @@ def dist_setup(n_gpus):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")   # plain NVLink paths only (see collectives_record)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29500")
         torch.cuda.set_device(local)
@@ -501,6 +559,102 @@ def time_steps(fn, steps, world, device, flush=None):
     return max_over_ranks(ms, world, device)
 
 
+def measure(fn, steps, world, device, flush=None, min_seconds=0.5, max_blocks=400):
+    """Repeat the block of exactly `steps` timed steps until the blocks add up to `min_seconds` of device
+    time (every block is bracketed and reduced over the ranks as in time_steps).  The reported step time
+    is the median block; the fastest block and the number of blocks are kept beside it."""
+    blocks = []
+    while True:
+        blocks.append(time_steps(fn, steps, world, device, flush))   # the same number on every rank
+        if sum(blocks) >= min_seconds * 1e3 or len(blocks) >= max_blocks:
+            break
+    ordered = sorted(blocks)
+    return {"ms_block": ordered[len(ordered) // 2], "ms_block_min": ordered[0], "blocks": len(blocks),
+            "timed_seconds": sum(blocks) * 1e-3}
+
+
+def roofline_of(wl, ms_per_step, peaks, peak_src):
+    if wl.bound == "hbm":
+        achieved, peak, unit = wl.alg_bytes / (ms_per_step * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+    else:
+        achieved, peak, unit = wl.alg_flops / (ms_per_step * 1e-3) / 1e12, peaks["bf16_tflops"], "TFLOP/s"
+    return {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+            "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "peak_source": peak_src,
+            "algorithmic_bytes_per_launch": wl.alg_bytes, "algorithmic_flops_per_launch": wl.alg_flops,
+            "frac_of_nominal": achieved / (8000.0 if wl.bound == "hbm" else 2250.0),
+            "duration": "CUDA-event time of one step on the launching stream (median block of `steps` steps)"}
+
+
+def timed_record(wl, fa, steps, warmup, world, device, rank, local, peaks, peak_src):
+    """Warm up, then time `wl.step` in blocks of `steps` with the clocks sampled across the timed blocks."""
+    import flash_attn_v100_b200
+    for _ in range(max(warmup, 3)):
+        wl.step(fa)
+    torch.cuda.synchronize()
+    flash_attn_v100_b200.check_async_errors()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    m = measure(lambda: wl.step(fa), steps, world, device, getattr(wl, "flush", None))
+    clocks = sampler.stop() if rank == 0 else None
+    flash_attn_v100_b200.check_async_errors()
+    ms_per_step = m["ms_block"] / steps
+    return {"workload": wl.name, "metric": wl.metric, "value": wl.units_per_step * world / (ms_per_step * 1e-3),
+            "unit": wl.unit, "ms_per_step": ms_per_step, "ms_per_step_min": m["ms_block_min"] / steps,
+            "steps": steps, "blocks": m["blocks"], "timed_seconds": m["timed_seconds"], "dtype": wl.dtype,
+            "roofline": roofline_of(wl, ms_per_step, peaks, peak_src), "clocks": clocks, "config": wl.config(),
+            "gpu_launches": wl.launches_per_step * steps * m["blocks"]}
+
+
+def collectives_record(rank, world, device, iters=200):
+    """The decode step's all-reduce message (256 x 4096 bf16 = 2 MB) through the library's peer-memory kernel
+    and through NCCL: exactness against the fp32 rank-order sum, device time (max over ranks), algorithmic
+    NVLink bytes per rank 2*(N-1)/N*n*2 over that time, and the kernel's status word."""
+    import torch.distributed as dist
+    from flash_attn_v100_b200.comm import PeerCollectives
+    rows, cols = 256, 4096
+    n = rows * cols
+    pc = PeerCollectives(dist.group.WORLD, device, n * 2)
+    g = torch.Generator(device=device).manual_seed(4242 + rank)
+    x = torch.randn(rows, cols, generator=g, device=device).bfloat16()
+    parts = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(parts, x)
+    acc = torch.zeros(rows, cols, dtype=torch.float32, device=device)
+    for part in parts:                         # rank order, fp32, one rounding: what the kernel computes
+        acc += part.float()
+    want = acc.bfloat16()
+    v = pc.view(0, (rows, cols), torch.bfloat16)
+    v.copy_(x)
+    pc.all_reduce_(v)
+    torch.cuda.synchronize()
+    exact = bool(torch.equal(v, want))
+    y = torch.zeros(rows, cols, dtype=torch.bfloat16, device=device)
+    v.zero_()                                  # zeros stay zeros however often they are summed
+
+    def timed(fn):
+        for _ in range(10):
+            fn()
+        return time_steps(fn, iters, world, device) / iters * 1e3   # microseconds, max over ranks
+
+    us_peer = timed(lambda: pc.all_reduce_(v))
+    us_nccl = timed(lambda: dist.all_reduce(y))
+    status_ok = True
+    try:
+        pc.check()
+    except RuntimeError:
+        status_ok = False
+    flag = torch.tensor([1 if (exact and status_ok) else 0], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    pc.close()
+    link_bytes = 2.0 * (world - 1) / world * n * 2
+    return {"message": "256 x 4096 bf16 (2 MB), sum all-reduce, in place", "peer_us": us_peer, "nccl_us": us_nccl,
+            "nvlink_bytes_per_rank": link_bytes, "peer_gbs_per_rank": link_bytes / us_peer / 1e3,
+            "nccl_gbs_per_rank": link_bytes / us_nccl / 1e3, "exact_vs_fp32_rank_order_sum_all_ranks": bool(flag.item()),
+            "peer_status_clean": status_ok, "nvls": "off (NCCL_NVLS_ENABLE=0); peer kernel uses plain peer loads/stores",
+            "link_peak_gbs": 770.0}
+
+
 def run_b200(args):
     rank, world, local = dist_setup(args.gpus)
     device = torch.device("cuda", local)
@@ -510,38 +664,24 @@ def run_b200(args):
     peaks, peak_src = load_peaks()
 
     wl = WORKLOADS[args.workload](device, seed=rank)
-    for _ in range(max(args.warmup, 3)):
-        wl.step(fa)
-    torch.cuda.synchronize()
-    flash_attn_v100_b200.check_async_errors()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-    flush = getattr(wl, "flush", None)
-    ms = time_steps(lambda: wl.step(fa), args.steps, world, device, flush)
-    # keep the GPU under load long enough for a few clock samples
-    t_end = time.time() + 1.0
-    while rank == 0 and time.time() < t_end:
-        wl.step(fa)
-    torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
+    head = timed_record(wl, fa, args.steps, args.warmup, world, device, rank, local, peaks, peak_src)
+    headline = args.workload == "paged_decode"
 
     e2e = None
     if wl.step_e2e is not None:
         for _ in range(3):
             wl.step_e2e(fa)
-        ms_e2e = time_steps(lambda: wl.step_e2e(fa), args.steps, world, device)
+        m = measure(lambda: wl.step_e2e(fa), args.steps, world, device)
+        ms_e2e = m["ms_block"] / args.steps
         h2d, d2h = wl.e2e_bytes()
-        e2e = {"value": wl.units_per_step * world * args.steps / (ms_e2e * 1e-3), "unit": wl.unit,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps,
+        e2e = {"value": wl.units_per_step * world / (ms_e2e * 1e-3), "unit": wl.unit,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "blocks": m["blocks"],
                "note": "q, block_table and seq_lens copied from pinned host memory and the output read back every "
                        "step through the Python operator API; the KV pool is resident device state"}
     flash_attn_v100_b200.check_async_errors()
 
     cpu_baseline = None
-    if rank == 0 and world == 1 and args.workload == "paged_decode" and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and headline and not args.no_cpu_baseline:
         host = wl.host_copy()
         torch.set_num_threads(os.cpu_count() or 1)
         seqs = list(range(wl.B))          # the whole batch, repeated for about ten seconds of CPU work
@@ -559,82 +699,106 @@ def run_b200(args):
                         "sample": f"all {wl.B} sequences of the same batch, {passes} passes, {dt:.1f} s; PyTorch fp32 "
                                   f"CPU restatement of the reference's SDPA decode oracle",
                         "max_abs_err_vs_gpu": err}
+        del host, ref
+
+    extra = {}
+    if headline and not args.headline_only:
+        t1_ms = head["ms_per_step"]       # one GPU holding all eight KV heads of a batch of this shape
+        del wl
+        torch.cuda.empty_cache()
+        # (1) the same batch shape split by KV-head group over the ranks: strong scaling, no collective
+        if 8 % world == 0:
+            hs = HeadShardedPagedDecode(device, rank, world)
+            rec = timed_record(hs, fa, args.steps, args.warmup, world, device, rank, local, peaks, peak_src)
+            ms = rec["ms_per_step"]       # max over ranks: the step of the global batch ends with the slowest shard
+            rec.update(ms_per_step=ms, us_per_rank_step=ms * 1e3, value=hs.B / (ms * 1e-3),
+                       hbm_gbs_per_gpu=hs.alg_bytes / (ms * 1e-3) / 1e9, scaling="strong",
+                       strong_scaling_efficiency_vs_one_gpu=t1_ms / (world * ms),
+                       one_gpu_ms_per_step=t1_ms)
+            rec["roofline"] = roofline_of(hs, ms, peaks, peak_src)
+            rec["roofline"]["traffic"] = None
+            extra["head_sharded"] = rec
+            del hs
+            torch.cuda.empty_cache()
+        # (2) the rest of the metric: causal varlen prefill and INT8 decode, on one GPU
+        if world == 1:
+            sec = []
+            for cls in (VarlenPrefill, Int8Decode):
+                w2 = cls(device, 0)
+                sec.append(timed_record(w2, fa, args.steps, args.warmup, 1, device, rank, local, peaks, peak_src))
+                del w2
+                torch.cuda.empty_cache()
+            flash_attn_v100_b200.check_prefill_errors()
+            extra["secondary"] = sec
+        # (3) the multi-GPU pieces of the engine slice that only a multi-GPU run can show
+        if world > 1:
+            extra["collectives"] = collectives_record(rank, world, device)
+            try:
+                from flash_attn_v100_b200.engine.selfcheck import tp_consistency_check
+                extra["tp_engine_check"] = tp_consistency_check(rank, world, device)
+            except Exception as ex:   # a failed check is a result, not a crash of the benchmark line
+                extra["tp_engine_check"] = {"ok": False, "error": repr(ex)[:300]}
 
     if rank != 0:
         return
-    sec = ms * 1e-3
-    ms_per_step = ms / args.steps
-    value = wl.units_per_step * world * args.steps / sec
-    if wl.bound == "hbm":
-        achieved = wl.alg_bytes / (ms_per_step * 1e-3) / 1e9
-        peak = peaks["hbm_gbs"]
-        r_unit = "GB/s"
-    else:
-        achieved = wl.alg_flops / (ms_per_step * 1e-3) / 1e12
-        peak = peaks["bf16_tflops"]
-        r_unit = "TFLOP/s"
     line = {
-        "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded N(0,1) fp16, random page permutation)",
-        "config": wl.config(),
-        "hbm_gbs_per_gpu": (wl.alg_bytes / (ms_per_step * 1e-3) / 1e9),
-        "roofline": {"bound": wl.bound, "achieved": achieved, "peak": peak, "unit": r_unit, "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "peak_source": peak_src,
-                     "algorithmic_bytes_per_launch": wl.alg_bytes, "algorithmic_flops_per_launch": wl.alg_flops,
-                     "frac_of_nominal": achieved / (8000.0 if wl.bound == "hbm" else 2250.0),
-                     "duration": "CUDA-event time of one step on the launching stream"},
-        "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": wl.launches_per_step * args.steps,
-        "clocks": clocks, "impl": "b200",
+        "metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": head["dtype"],
+        "data": "synthetic (seeded N(0,1) fp16 drawn on the host, random page permutation)",
+        "config": head["config"],
+        "timing": {"blocks": head["blocks"], "timed_seconds": head["timed_seconds"],
+                   "ms_per_step_median_block": head["ms_per_step"], "ms_per_step_fastest_block": head["ms_per_step_min"],
+                   "note": "the block of `steps` steps is repeated until at least 0.5 s of device time is covered; "
+                           "value and ms_per_step are the median block; clocks are sampled across all blocks"},
+        "hbm_gbs_per_gpu": head["roofline"]["achieved"] if head["roofline"]["bound"] == "hbm" else None,
+        "roofline": head["roofline"],
+        "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": head["gpu_launches"],
+        "clocks": head["clocks"], "impl": "b200",
     }
+    line.update(extra)
     print(json.dumps(line), flush=True)
 
 
 def run_reference(args):
     """The reference's CPU implementation of the path: its PyTorch eager fp32 oracle
     (restated in oracle/, since the reference tree is not present on a GPU box),
-    on all host cores, over a bounded sample of the same workload."""
+    on all host cores.  One step = the WHOLE headline batch, rebuilt from the same
+    seeds as the batch rank 0 of the GPU arm runs (identical tensors)."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
+    from flash_attn_v100_b200.synthetic import make_paged_decode_batch
     from oracle import attention_oracle as orc
     torch.set_num_threads(os.cpu_count() or 1)
-    B, H_Q, H_KV, D = 64, 32, 8, 128
-    sample = 8
-    w = orc.make_paged_workload(B, H_Q, H_KV, D, 512, 8192, seed=0, fill=False)
-    # materialise only the pages of the sampled sequences (keeps host memory and set-up time bounded)
-    seqs = list(range(0, B, B // sample))
-    g = torch.Generator().manual_seed(0)
-    rows, tables = [], []
-    base = 0
-    for b in seqs:
-        n = (int(w["seq_lens"][b]) + 15) // 16
-        tables.append(torch.arange(base, base + n, dtype=torch.int32))
-        base += n
-    kc = torch.randn(base, H_KV, 16, D, generator=g).half()
-    vc = torch.randn(base, H_KV, 16, D, generator=g).half()
-    bt = torch.full((len(seqs), max(t.numel() for t in tables)), -1, dtype=torch.int32)
-    for i, t in enumerate(tables):
-        bt[i, : t.numel()] = t
-    q = w["q"][seqs]
-    sl = w["seq_lens"][seqs]
-    for _ in range(max(args.warmup, 1)):
-        orc.paged_decode(q[:2], kc, vc, bt[:2], sl[:2])
+    B, H_Q, H_KV, D = PagedDecode.B, PagedDecode.H_Q, PagedDecode.H_KV, PagedDecode.D
+    w = make_paged_decode_batch(B, H_Q, H_KV, D, 512, 8192, table_seed=0, value_seed=0)
+    q, kc, vc, bt, sl = w["q"], w["k_cache"], w["v_cache"], w["block_table"], w["seq_lens"]
+    for _ in range(max(min(args.warmup, 2), 1)):
+        orc.paged_decode(q[:4], kc, vc, bt[:4], sl[:4])
+    # bounded: about a minute of CPU work at most (one pass over the batch takes under a second)
+    steps = args.steps
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    done = 0
+    for _ in range(steps):
         orc.paged_decode(q, kc, vc, bt, sl)
-    dt = (time.perf_counter() - t0) / args.steps
-    value = len(seqs) / dt
+        done += 1
+        if time.perf_counter() - t0 > 90.0:
+            break
+    dt = (time.perf_counter() - t0) / done
+    value = B / dt
     cores = torch.get_num_threads()
-    desc = (f"{len(seqs)} of {B} sequences (every {B // sample}th) of the paged-decode batch per step; "
-            "PyTorch fp32 CPU restatement of the reference's SDPA decode oracle (test_decode.py:9-19)")
+    desc = (f"all {B} sequences of the paged-decode batch per step (same seeded tensors as rank 0 of the GPU arm), "
+            f"{done} steps timed; PyTorch fp32 CPU restatement of the reference's SDPA decode oracle "
+            "(test_decode.py:9-19)")
     line = {
         "impl": "reference", "metric": PagedDecode.metric, "value": value, "unit": "tokens/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (CPU)", "data": "synthetic",
-        "config": {"workload": "paged_gqa_decode B=64 H_Q=32 H_KV=8 D=128 page=16 seq_lens~U[512,8192] (BASELINE configs[1])",
-                   "sample": desc},
+        "steps": done, "warmup": max(min(args.warmup, 2), 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (CPU)",
+        "data": "synthetic (seeded N(0,1) fp16 drawn on the host, random page permutation)",
+        "config": PagedDecode.config_of(sl, w["n_pages"]),
+        "note": "one CPU process whatever --gpus says: its value does not grow with N",
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -656,6 +820,8 @@ def main():
     ap.add_argument("--engine-requests", type=int, default=256)
     ap.add_argument("--engine-prefill-chunk", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="skip the head-sharded, secondary (prefill, INT8) and multi-GPU records of the default run")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -279,11 +279,53 @@ int check_decode_common(const void* q, const void* k, const void* v, const void*
   return FA_OK;
 }
 
+// ---- built-in decode scratch (fa_paged_decode_gqa_f16_static_scratch) -------
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, not a device
+// address, so the device address is looked up once per device and cached.
+void* g_static_scratch_ptr[64] = {nullptr};
+std::mutex g_static_scratch_mu;
+
+// Set-up, once per device, with that device current.  The status word and the arrival counters
+// (the first kWsInitBytes of any decode workspace) must be zero before the first launch, exactly as
+// fa_decode_workspace_init leaves a caller-owned workspace; everything behind them is written
+// before it is read.  The clear is finished before the address is handed to any caller, so it can
+// never wipe a status bit that a concurrent call has set.
+int static_scratch_for_current_device(void** out, cudaStream_t stream) {
+  int dev = 0;
+  FA_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(FA_ERR_CUDA, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_static_scratch_mu);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    FA_CUDA(cudaGetSymbolAddress(&ptr, g_static_decode_scratch));
+    if (ptr == nullptr) return fail(FA_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    FA_CUDA(cudaMemsetAsync(ptr, 0, fa::kWsInitBytes, stream));
+    FA_CUDA(cudaStreamSynchronize(stream));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return FA_OK;
+}
+
+int check_paged_args(const void* q, const void* k_cache, const void* v_cache, const void* out,
+                     const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q, int H_KV, int D,
+                     int64_t num_pages, int block_table_stride) {
+  int rc = check_decode_common(q, k_cache, v_cache, out, B, H_Q, H_KV, D);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(block_table && seq_lens, "null block_table / seq_lens");
+  FA_REQUIRE(num_pages > 0, "num_pages must be positive");
+  FA_REQUIRE(block_table_stride > 0, "block_table_stride must be positive");
+  return FA_OK;
+}
+
 }  // namespace
 
 extern "C" {
 
-int fa_version(void) { return 100; }
+int fa_version(void) { return 101; }
 
 const char* fa_last_error(void) { return g_err; }
 
@@ -293,13 +335,24 @@ size_t fa_decode_workspace_bytes(int B, int H_Q, int H_KV, int D) {
 }
 
 int fa_decode_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
-  FA_REQUIRE(workspace != nullptr && workspace_bytes >= fa::kWsInitBytes, "workspace missing or too small");
+  if (workspace == nullptr) {   // the built-in scratch of fa_paged_decode_gqa_f16_static_scratch
+    int rc = static_scratch_for_current_device(&workspace, static_cast<cudaStream_t>(stream));
+    if (rc != FA_OK) return rc;
+    workspace_bytes = fa::kWsInitBytes;
+  }
+  FA_REQUIRE(workspace_bytes >= fa::kWsInitBytes, "workspace too small");
   FA_CUDA(cudaMemsetAsync(workspace, 0, fa::kWsInitBytes, static_cast<cudaStream_t>(stream)));
   return FA_OK;
 }
 
 int fa_decode_status(const void* workspace, void* stream, int* host_status_out) {
-  FA_REQUIRE(workspace != nullptr && host_status_out != nullptr, "null pointer");
+  FA_REQUIRE(host_status_out != nullptr, "null pointer");
+  if (workspace == nullptr) {   // the built-in scratch of fa_paged_decode_gqa_f16_static_scratch
+    void* builtin = nullptr;
+    int rc = static_scratch_for_current_device(&builtin, static_cast<cudaStream_t>(stream));
+    if (rc != FA_OK) return rc;
+    workspace = builtin;
+  }
   int32_t v = 0;
   FA_CUDA(cudaMemcpyAsync(&v, static_cast<const uint8_t*>(workspace) + fa::kWsStatusOffset, 4, cudaMemcpyDeviceToHost,
                           static_cast<cudaStream_t>(stream)));
@@ -318,11 +371,9 @@ int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_ca
                             const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q, int H_KV, int D,
                             int64_t num_pages, int block_table_stride, int64_t max_seq_len, void* workspace,
                             size_t workspace_bytes, void* stream) {
-  int rc = check_decode_common(q, k_cache, v_cache, out, B, H_Q, H_KV, D);
+  int rc = check_paged_args(q, k_cache, v_cache, out, block_table, seq_lens, B, H_Q, H_KV, D, num_pages,
+                            block_table_stride);
   if (rc != FA_OK) return rc;
-  FA_REQUIRE(block_table && seq_lens, "null block_table / seq_lens");
-  FA_REQUIRE(num_pages > 0, "num_pages must be positive");
-  FA_REQUIRE(block_table_stride > 0, "block_table_stride must be positive");
   DecodeCall c{};
   c.q = q; c.k = k_cache; c.v = v_cache; c.out = out;
   c.block_table = block_table; c.lens = seq_lens;
@@ -458,47 +509,19 @@ int fa_decode_int8_kv_cache_gqa(const void* q, const void* k_int8, const void* v
 // ---------------------------------------------------------------------------
 // Paged decode for callers that cannot allocate device memory.
 //
-// The split-KV scratch (status word, page prefix sums, per-CTA partial results)
-// lives in a fixed array that is part of the loaded module image, so the call
-// needs no cudaMalloc and no caller-provided workspace.  Every device that loads
-// the library holds these bytes until the process exits.
+// The split-KV scratch (status word, arrival counters, page prefix sums, per-CTA
+// partial results) lives in a fixed array that is part of the loaded module image,
+// so the call needs no cudaMalloc and no caller-provided workspace.  Every device
+// that loads the library holds these bytes until the process exits.
 // ---------------------------------------------------------------------------
-constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB
-static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
-
-namespace {
-// In host code the array's name is only a handle for the runtime, not a device
-// address, so the device address is looked up once per device and cached.
-void* g_static_scratch_ptr[64] = {nullptr};
-std::mutex g_static_scratch_mu;
-
-int static_scratch_for_current_device(void** out, cudaStream_t stream) {
-  int dev = 0;
-  FA_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(FA_ERR_CUDA, "device ordinal %d out of range", dev);
-  std::lock_guard<std::mutex> lk(g_static_scratch_mu);
-  if (g_static_scratch_ptr[dev] == nullptr) {
-    void* ptr = nullptr;
-    FA_CUDA(cudaGetSymbolAddress(&ptr, g_static_decode_scratch));
-    if (ptr == nullptr) return fail(FA_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
-    // the status word must start at zero; everything else is written before it is read
-    FA_CUDA(cudaMemsetAsync(ptr, 0, 256, stream));
-    g_static_scratch_ptr[dev] = ptr;
-  }
-  *out = g_static_scratch_ptr[dev];
-  return FA_OK;
-}
-}  // namespace
-
 int fa_paged_decode_gqa_f16_static_scratch(const void* q, const void* k_cache, const void* v_cache, void* out,
                                            const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q,
                                            int H_KV, int D, int64_t num_pages, int block_table_stride,
                                            int64_t max_seq_len, void* stream) {
-  // argument errors first, so that a bad call never touches the device
-  if (B <= 0 || H_Q <= 0 || H_KV <= 0 || H_Q % H_KV != 0)
-    return fail(FA_ERR_INVALID_ARGUMENT, "B, H_Q, H_KV must be positive and H_Q divisible by H_KV");
-  if (padded_decode_d(D) == 0)
-    return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (decode serves multiples of 8 up to 256)", D);
+  // every argument check comes first, so that a bad call never touches the device
+  int rc = check_paged_args(q, k_cache, v_cache, out, block_table, seq_lens, B, H_Q, H_KV, D, num_pages,
+                            block_table_stride);
+  if (rc != FA_OK) return rc;
   const size_t need = fa::decode_workspace_bytes(B, H_Q, H_KV, padded_decode_d(D), kMaxDecodeCtas);
   if (need > kStaticScratchBytes)
     return fail(FA_ERR_WORKSPACE,
@@ -506,7 +529,7 @@ int fa_paged_decode_gqa_f16_static_scratch(const void* q, const void* k_cache, c
                 "fa_paged_decode_gqa_f16 with a caller-owned workspace",
                 need, (size_t)kStaticScratchBytes);
   void* scratch = nullptr;
-  int rc = static_scratch_for_current_device(&scratch, static_cast<cudaStream_t>(stream));
+  rc = static_scratch_for_current_device(&scratch, static_cast<cudaStream_t>(stream));
   if (rc != FA_OK) return rc;
   return fa_paged_decode_gqa_f16(q, k_cache, v_cache, out, block_table, seq_lens, B, H_Q, H_KV, D, num_pages,
                                  block_table_stride, max_seq_len, scratch, kStaticScratchBytes, stream);

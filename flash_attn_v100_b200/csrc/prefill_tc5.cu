@@ -40,15 +40,26 @@ namespace fa {
 
 __device__ int g_prefill_status = 0;
 
-#ifdef FA_TC5_TRACE
-// Debug build only: clock64() timeline of one CTA (events per role, KV step and phase).
-__device__ long long g_tc5_trace[8 * 64 * 8];
-#define TC5_TRACE(role, step, ev)                                                     \
-  do {                                                                                \
-    if (trace_on && (step) < 64) g_tc5_trace[((role) * 64 + (step)) * 8 + (ev)] = clock64(); \
+#ifdef FA_TC5_PROF
+// Instrumented build only (-DFA_TC5_PROF): cycles that one thread of each role spends in each kind of
+// wait, summed over all CTAs.  Roles: 0 copy lane, 1/2 MMA lanes, 3/4 the thread of row 0 of each softmax group.
+__device__ unsigned long long g_tc5_prof[5 * 16];
+#define PROF_WAIT(role, cat, stmt)                                                     \
+  do {                                                                                 \
+    const long long prof_a_ = clock64();                                               \
+    stmt;                                                                              \
+    if (prof_on) prof_smem[(role) * 16 + (cat)] += (unsigned long long)(clock64() - prof_a_); \
   } while (0)
+#define PROF_MARK(var) const long long var = clock64()
+#define PROF_SPAN(role, cat, a, b) \
+  do { if (prof_on) prof_smem[(role) * 16 + (cat)] += (unsigned long long)((b) - (a)); } while (0)
+#define PROF_COUNT(role, cat) \
+  do { if (prof_on) prof_smem[(role) * 16 + (cat)] += 1ull; } while (0)
 #else
-#define TC5_TRACE(role, step, ev) do { } while (0)
+#define PROF_WAIT(role, cat, stmt) do { stmt; } while (0)
+#define PROF_MARK(var) do { } while (0)
+#define PROF_SPAN(role, cat, a, b) do { } while (0)
+#define PROF_COUNT(role, cat) do { } while (0)
 #endif
 
 namespace {
@@ -171,13 +182,13 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
-// 2^x for x <= ~8 on the FMA/ALU pipes (keeps the MUFU free for the other half of the row):
+// 2^x (x clamped to [-125, 126]) on the FMA/ALU pipes (keeps the MUFU free for the other half of the row):
 // round-to-nearest split x = n + f with the 1.5*2^23 trick, degree-3 minimax polynomial for 2^f on
 // [-0.5, 0.5] (relative error 7.7e-5, below fp16 resolution), exponent added through the integer bits.
 __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   const float kMagic = 12582912.f;
-  x.x = fmaxf(x.x, -125.f);
-  x.y = fmaxf(x.y, -125.f);
+  x.x = fminf(fmaxf(x.x, -125.f), 126.f);   // 2^126 still trips every overflow check downstream
+  x.y = fminf(fmaxf(x.y, -125.f), 126.f);
   const float2 t = fadd2(x, make_float2(kMagic, kMagic));
   const float2 n = fadd2(t, make_float2(-kMagic, -kMagic));
   const float2 f = ffma2(n, make_float2(-1.f, -1.f), x);
@@ -187,6 +198,58 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   r.x = __int_as_float(__float_as_int(r.x) + (__float_as_int(t.x) << 23));
   r.y = __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23));
   return r;
+}
+
+// Which of the 16 value pairs of a 32-column chunk are exponentiated by the polynomial: NPOLY pairs of
+// every eight, spread evenly so that polynomial and MUFU work interleave in the instruction stream.
+template <int NPOLY>
+__device__ __forceinline__ constexpr bool pair_uses_poly(int i) {
+  return (((i & 7) * NPOLY) % 8) < NPOLY;
+}
+
+// One 32-column chunk of a score row: P = exp2(s * scale - m) as fp16 pairs, written to tensor memory at
+// `taddr` (16 columns); the fp32 sum of the chunk is added to `rs`.
+template <int NPOLY>
+__device__ __forceinline__ void exp_chunk_store(const float (&s)[32], float2 sc2, float2 nm2, float2& rs,
+                                                uint32_t taddr) {
+  uint32_t pk[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 x = ffma2(make_float2(s[2 * i], s[2 * i + 1]), sc2, nm2);
+    float2 e;
+    if (pair_uses_poly<NPOLY>(i)) {
+      e = exp2_poly2(x);
+    } else {
+      e.x = fast_exp2(x.x);
+      e.y = fast_exp2(x.y);
+    }
+    rs = fadd2(rs, e);
+    pk[i] = pack_half2(e.x, e.y);
+  }
+  tc_st16(taddr, pk);
+}
+
+__device__ __forceinline__ void zero_chunk_store(uint32_t taddr) {
+  uint32_t pk[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) pk[i] = 0u;
+  tc_st16(taddr, pk);
+}
+
+// Maximum of a 128-value score row held in registers (two chains per chunk of three-input maxima).
+__device__ __forceinline__ float row_max128(const float (&sv)[4][32]) {
+  float mxc[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float a0 = fmaxf(sv[c][0], sv[c][1]), a1 = fmaxf(sv[c][2], sv[c][3]);
+#pragma unroll
+    for (int i = 4; i < 32; i += 4) {
+      a0 = fmax3(a0, sv[c][i], sv[c][i + 1]);
+      a1 = fmax3(a1, sv[c][i + 2], sv[c][i + 3]);
+    }
+    mxc[c] = fmaxf(a0, a1);
+  }
+  return fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
 }
 
 // Shared-memory matrix descriptor for 128-byte-swizzled tiles made of 128-byte rows.
@@ -255,7 +318,12 @@ __device__ __forceinline__ bool tc5_decode_item(const Tc5Params& p, long long it
   return it.n_kv[0] > 0;  // tile 0 holds the earlier rows: if it is empty the item is empty
 }
 
-template <int D, bool POLY>
+// NPOLY: value pairs of every eight whose exp2 runs as a polynomial on the FMA pipes (0..4);
+// PSPLIT: 32-column chunks of P handed to the PV MMA with the first barrier (1..3);
+// SM: softmax scheme on tiles that need no masking (see the softmax role): 0 row maximum and rescale
+// decision first, 1 row maximum first but exponentials against the carried-over m, 2 first part
+// exponentiated while the maximum is formed, 3 no maximum, parts validated through their sums.
+template <int D, int NPOLY, int PSPLIT, int SM>
 __global__ void __launch_bounds__(384, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                    const __grid_constant__ CUtensorMap vmap, const Tc5Params p) {
@@ -268,7 +336,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t O_COL0 = 256;
-  constexpr int kPSplit = 2;                 // P is handed to the PV MMA in two parts: 32*kPSplit keys, then the rest
+  constexpr int kPSplit = PSPLIT;            // P is handed to the PV MMA in two parts: 32*kPSplit keys, then the rest
   constexpr int kItemQ = 4;                  // depth of the per-CTA item queue
   constexpr int kItemConsumers = 2 + 256;    // two MMA lanes + every softmax thread
 
@@ -283,7 +351,8 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   constexpr int B_QFULL = 0, B_QEMPTY = 2, B_KFULL = B_QEMPTY + 2, B_KEMPTY = B_KFULL + KV_STAGES,
                 B_VFULL = B_KEMPTY + KV_STAGES, B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES,
                 B_PLO = B_SFULL + 2, B_PHI = B_PLO + 2, B_OFULL = B_PHI + 2, B_TOKEN = B_OFULL + 2,
-                B_IFULL = B_TOKEN + 2, B_IEMPTY = B_IFULL + kItemQ, B_COUNT = B_IEMPTY + kItemQ;
+                B_OLO = B_TOKEN + 2, B_IFULL = B_OLO + 2, B_IEMPTY = B_IFULL + kItemQ,
+                B_COUNT = B_IEMPTY + kItemQ;
   volatile long long* item_slot = reinterpret_cast<volatile long long*>(bars + B_COUNT);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT + kItemQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -291,8 +360,11 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long n_items = (long long)p.n_rb * p.batch * p.n_hg;
-#ifdef FA_TC5_TRACE
-  bool trace_on = false;   // set by each role while it processes the first item of CTA 0
+#ifdef FA_TC5_PROF
+  unsigned long long* prof_smem = reinterpret_cast<unsigned long long*>(bars + 64);
+  if (threadIdx.x < 5 * 16) prof_smem[threadIdx.x] = 0ull;
+  bool prof_on = false;    // true in the one thread per role that keeps the counters
+  const long long prof_start = clock64();
 #endif
 
   // ---- set-up (once per CTA) --------------------------------------------------------
@@ -311,6 +383,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       mbar_init(bar(B_PHI + t), 128);
       mbar_init(bar(B_OFULL + t), 1);
       mbar_init(bar(B_TOKEN + t), 1);
+      mbar_init(bar(B_OLO + t), 1);
     }
     for (int i = 0; i < kItemQ; ++i) {
       mbar_init(bar(B_IFULL + i), 1);
@@ -342,6 +415,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     // ============================ TMA producer ======================================
     if (lane == 0) {
+#ifdef FA_TC5_PROF
+      prof_on = true;
+#endif
       uint32_t kv_it = 0;
       uint32_t q_used[2] = {0, 0};   // how often each Q buffer has been filled
       for (uint32_t ic = 0;; ++ic) {
@@ -350,20 +426,20 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         Tc5Item it;
         long long item;
         bool have = false;
-        while (true) {
+        PROF_WAIT(0, 0, while (true) {
           item = (long long)atomicAdd(p.item_counter, 1ULL);
           if (item >= n_items) break;
           if (tc5_decode_item(p, item, it)) { have = true; break; }
-        }
+        });
         const int slot = ic % kItemQ;
-        if (ic >= kItemQ) wait_or_abort(bar(B_IEMPTY + slot), ((ic / kItemQ) & 1u) ^ 1u, abort_flag);
+        if (ic >= kItemQ) PROF_WAIT(0, 1, wait_or_abort(bar(B_IEMPTY + slot), ((ic / kItemQ) & 1u) ^ 1u, abort_flag));
         item_slot[slot] = have ? item : -1;
         mbar_arrive(bar(B_IFULL + slot));
         if (!have) break;
         const int n_act = it.n_kv[1] > 0 ? 2 : 1;
         // Q buffers are free once the last QK of their previous item has completed
         for (int t = 0; t < n_act; ++t) {
-          if (q_used[t] > 0) wait_or_abort(bar(B_QEMPTY + t), (q_used[t] - 1) & 1u, abort_flag);
+          if (q_used[t] > 0) PROF_WAIT(0, 2, wait_or_abort(bar(B_QEMPTY + t), (q_used[t] - 1) & 1u, abort_flag));
           mbar_expect_tx(bar(B_QFULL + t), TILE_BYTES);
 #pragma unroll
           for (int sl = 0; sl < NSLAB; ++sl)
@@ -374,13 +450,13 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         for (int j = 0; j < it.n_max; ++j, ++kv_it) {
           const int st = kv_it % KV_STAGES;
           const uint32_t ph = (kv_it / KV_STAGES) & 1u;
-          if (kv_it >= KV_STAGES) wait_or_abort(bar(B_KEMPTY + st), ph ^ 1u, abort_flag);
+          if (kv_it >= KV_STAGES) PROF_WAIT(0, 3, wait_or_abort(bar(B_KEMPTY + st), ph ^ 1u, abort_flag));
           mbar_expect_tx(bar(B_KFULL + st), TILE_BYTES);
 #pragma unroll
           for (int sl = 0; sl < NSLAB; ++sl)
             tma_load_3d(sK + st * TILE_BYTES + sl * SLAB, &kmap, sl * 64, it.kv_c1, it.kv_c2 + j * BN,
                         bar(B_KFULL + st));
-          if (kv_it >= KV_STAGES) wait_or_abort(bar(B_VEMPTY + st), ph ^ 1u, abort_flag);
+          if (kv_it >= KV_STAGES) PROF_WAIT(0, 4, wait_or_abort(bar(B_VEMPTY + st), ph ^ 1u, abort_flag));
           mbar_expect_tx(bar(B_VFULL + st), TILE_BYTES);
 #pragma unroll
           for (int sl = 0; sl < NSLAB; ++sl)
@@ -400,6 +476,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     // (a lane whose tile does not use a stage arrives on it directly).
     const int t = warp == 1 ? 0 : 1;
     if (lane == 0) {
+#ifdef FA_TC5_PROF
+      prof_on = true;
+#endif
       constexpr uint32_t TILE16 = TILE_BYTES >> 4;
       const uint64_t qd = smem_desc(sQ + (uint32_t)t * TILE_BYTES, 16, 1024);
       const uint64_t kd0 = smem_desc(sK, 16, 1024);
@@ -427,7 +506,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       for (uint32_t ic = 0;; ++ic) {
         if (*abort_flag) break;
         const int slot = ic % kItemQ;
-        wait_or_abort(bar(B_IFULL + slot), (ic / kItemQ) & 1u, abort_flag);
+        PROF_WAIT(1 + t, 0, wait_or_abort(bar(B_IFULL + slot), (ic / kItemQ) & 1u, abort_flag));
         const long long item = item_slot[slot];
         mbar_arrive(bar(B_IEMPTY + slot));
         if (item < 0 || item >= n_items) break;
@@ -435,12 +514,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         tc5_decode_item(p, item, it);
         const bool other_active = it.n_kv[1] > 0;   // tile 0 is always active in a non-empty item
         const int n_mine = it.n_kv[t];
-#ifdef FA_TC5_TRACE
-        trace_on = (blockIdx.x == 0 && ic == 0);
-#endif
         auto take_token = [&]() {
           if (!other_active) return;
-          wait_or_abort(bar(B_TOKEN + t), tok_waits & 1u, abort_flag);
+          PROF_WAIT(1 + t, 6, wait_or_abort(bar(B_TOKEN + t), tok_waits & 1u, abort_flag));
           ++tok_waits;
         };
         auto pass_token = [&]() {
@@ -448,11 +524,11 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         };
         if (n_mine > 0) {
           // block 0: S = Q K_0^T
-          wait_or_abort(bar(B_QFULL + t), q_cnt & 1u, abort_flag);
+          PROF_WAIT(1 + t, 1, wait_or_abort(bar(B_QFULL + t), q_cnt & 1u, abort_flag));
           ++q_cnt;
           {
             const int st = kv_it % KV_STAGES;
-            wait_or_abort(bar(B_KFULL + st), (kv_it / KV_STAGES) & 1u, abort_flag);
+            PROF_WAIT(1 + t, 2, wait_or_abort(bar(B_KFULL + st), (kv_it / KV_STAGES) & 1u, abort_flag));
             tc_fence_after();
             if (t == 1) take_token();
             issue_qk(st);
@@ -468,24 +544,20 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             const bool more = j + 1 < n_mine;
             const int st1 = (g + 1) % KV_STAGES;
             const uint32_t ph1 = ((g + 1) / KV_STAGES) & 1u;
-            TC5_TRACE(4 + 2 * t, j, 0);
-            wait_or_abort(bar(B_VFULL + st), ph, abort_flag);
-            if (more) wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag);
-            wait_or_abort(bar(B_PLO + t), blk & 1u, abort_flag);
-            TC5_TRACE(4 + 2 * t, j, 1);
+            PROF_COUNT(1 + t, 14);
+            PROF_WAIT(1 + t, 3, wait_or_abort(bar(B_VFULL + st), ph, abort_flag));
+            if (more) PROF_WAIT(1 + t, 4, wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag));
+            PROF_WAIT(1 + t, 5, wait_or_abort(bar(B_PLO + t), blk & 1u, abort_flag));
             // tile 1's block j+1 follows tile 0's block j+1; tile 0's block j+1 follows tile 1's
             // block j, which exists unless tile 1 has already run out of KV tiles
             if (t == 1 || j <= it.n_kv[1]) take_token();
-            TC5_TRACE(4 + 2 * t, j, 2);
             tc_fence_after();
             issue_pv(st, j > 0 ? 1u : 0u, 0);
-            TC5_TRACE(4 + 2 * t, j, 3);
-            wait_or_abort(bar(B_PHI + t), blk & 1u, abort_flag);
+            if (SM == 3) tc_commit(bar(B_OLO + t));   // lets the softmax rescale O between the two parts
+            PROF_WAIT(1 + t, 7, wait_or_abort(bar(B_PHI + t), blk & 1u, abort_flag));
             tc_fence_after();
-            TC5_TRACE(4 + 2 * t, j, 4);
             issue_pv(st, 1u, 1);
             if (more) issue_qk(st1);
-            TC5_TRACE(4 + 2 * t, j, 5);
             pass_token();
             tc_commit(bar(B_OFULL + t));
             tc_commit(bar(B_VEMPTY + st));
@@ -494,7 +566,6 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
               tc_commit(bar(B_KEMPTY + st1));
               if (j + 2 == n_mine) tc_commit(bar(B_QEMPTY + t));   // that was the last QK of this item
             }
-            TC5_TRACE(4 + 2 * t, j, 6);
           }
           if (other_active) {
             // balance the token barriers before the next item: tile 0 hands tile 1 the token for a
@@ -516,9 +587,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           const uint32_t g = kv_it + (uint32_t)j;
           const int st = g % KV_STAGES;
           const uint32_t ph = (g / KV_STAGES) & 1u;
-          wait_or_abort(bar(B_KFULL + st), ph, abort_flag);
+          PROF_WAIT(1 + t, 8, wait_or_abort(bar(B_KFULL + st), ph, abort_flag));
           mbar_arrive(bar(B_KEMPTY + st));
-          wait_or_abort(bar(B_VFULL + st), ph, abort_flag);
+          PROF_WAIT(1 + t, 8, wait_or_abort(bar(B_VFULL + st), ph, abort_flag));
           mbar_arrive(bar(B_VEMPTY + st));
         }
         kv_it += (uint32_t)it.n_max;
@@ -529,17 +600,29 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ============================ softmax groups ====================================
+    // Thread = one query row.  State per row: a reference exponent m (any finite number works as long as
+    // P = exp2(s * scale - m) stays inside the fp16 range; it starts at 0 and is raised to a row maximum
+    // only when a score leaves the window below), the row sum l relative to m, and O in tensor memory,
+    // also relative to m.
+    //   The first KV tile of an item and tiles that need masking take the full path: row maximum first,
+    //   m raised when it grows by more than 2^8 (O rescaled in tensor memory), then the exponentials.
+    //   Other tiles run one of the schemes SM selects; all of them keep m unless a score leaves the fp16
+    //   window above it.
     const int t = (warp - 4) >> 2;
     const int wq = warp & 3;                   // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;            // row within the tile == TMEM lane
     const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
     const uint32_t tS = lane_base + (uint32_t)t * 128u;
     const uint32_t tO = lane_base + O_COL0 + (uint32_t)t * D;
+#ifdef FA_TC5_PROF
+    prof_on = (row == 0);
+#endif
+    const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
     uint32_t blk = 0;
     for (uint32_t ic = 0;; ++ic) {
       if (*abort_flag) break;
       const int slot = ic % kItemQ;
-      wait_or_abort(bar(B_IFULL + slot), (ic / kItemQ) & 1u, abort_flag);
+      PROF_WAIT(3 + t, 0, wait_or_abort(bar(B_IFULL + slot), (ic / kItemQ) & 1u, abort_flag));
       const long long item = item_slot[slot];
       mbar_arrive(bar(B_IEMPTY + slot));
       if (item < 0 || item >= n_items) break;
@@ -547,16 +630,13 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       tc5_decode_item(p, item, it);
       const int n_mine = it.n_kv[t];
       if (n_mine == 0) continue;
-#ifdef FA_TC5_TRACE
-      trace_on = (blockIdx.x == 0 && ic == 0 && lane == 0 && wq == 0);
-#endif
       const int len = it.len;
       const int grow = it.row0[t] + row;       // row within the sequence
-      float m = -INFINITY, l = 0.f;
+      float m = 0.f, l = 0.f;
       for (int j = 0; j < n_mine; ++j, ++blk) {
-        TC5_TRACE(t, j, 0);
-        wait_or_abort(bar(B_SFULL + t), blk & 1u, abort_flag);
-        TC5_TRACE(t, j, 1);
+        PROF_COUNT(3 + t, 14);
+        PROF_WAIT(3 + t, 1, wait_or_abort(bar(B_SFULL + t), blk & 1u, abort_flag));
+        PROF_MARK(prof_t_s);
         tc_fence_after();
         const int k0 = j * BN;
         const bool need_mask = (k0 + BN > len) || (p.causal && (k0 + BN - 1 > it.row0[t]));
@@ -567,89 +647,203 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         tc_ld32(tS + 64, sv[2]);
         tc_ld32(tS + 96, sv[3]);
         tc_wait_ld();
-        TC5_TRACE(t, j, 2);
-        if (need_mask) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int kk = k0 + c * 32 + i;
-              if (kk >= len || (p.causal && kk > grow)) sv[c][i] = -INFINITY;
-            }
-        }
-        float mxc[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float a0 = fmaxf(sv[c][0], sv[c][1]), a1 = fmaxf(sv[c][2], sv[c][3]);
-#pragma unroll
-          for (int i = 4; i < 32; i += 4) {
-            a0 = fmax3(a0, sv[c][i], sv[c][i + 1]);
-            a1 = fmax3(a1, sv[c][i + 2], sv[c][i + 3]);
-          }
-          mxc[c] = fmaxf(a0, a1);
-        }
-        const float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
-        const float m_new = fmaxf(m, mx * p.scale_log2);
-        const bool grow_big = m_new > m + 8.f;   // also true for the first tile (m = -inf)
-        const float alpha = grow_big ? fast_exp2(m - m_new) : 1.f;
-        if (j > 0 && __any_sync(0xffffffffu, grow_big)) {
-          // O_t must hold the result of PV(t, j-1) before it is rescaled
-          wait_or_abort(bar(B_OFULL + t), (blk - 1) & 1u, abort_flag);
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            float o[32];
-            tc_ld32(tO + c * 32, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tc_st32(tO + c * 32, o);
-          }
-          tc_wait_st();
-        }
-        if (grow_big) m = m_new;
-        l *= alpha;
-        TC5_TRACE(t, j, 3);
-        // ---- P = exp2(S * scale - m), fp16, written over the first 64 columns of S ----
-        const float neg_m = (m == -INFINITY) ? 0.f : -m;
-        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
         float2 rs2[4];
+        bool full_path = SM == 0 || need_mask || j == 0;
+        if (SM == 1 && !full_path) {
+          // row maximum first, but no dependent chain behind it: the exponentials use the carried-over m
+          const float mxs = row_max128(sv) * p.scale_log2;
+          if (__any_sync(0xffffffffu, !(mxs <= m + 8.f))) {
+            full_path = true;
+          } else {
+            const float2 nm2 = make_float2(-m, -m);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          rs2[c] = make_float2(0.f, 0.f);
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float2 x = ffma2(make_float2(sv[c][2 * i], sv[c][2 * i + 1]), sc2, nm2);
-            if (POLY && (i & 3) == 0) {
-              // every fourth pair on the FMA/ALU pipes (measured neutral: 803 vs 810 TFLOP/s; larger shares
-              // are slower, the row is bound by dependent latencies rather than by the MUFU alone)
-              const float2 e = exp2_poly2(x);
-              rs2[c] = fadd2(rs2[c], e);
-              pk[i] = pack_half2(e.x, e.y);
-            } else {
-              float2 e;
-              e.x = fast_exp2(x.x);
-              e.y = fast_exp2(x.y);
-              rs2[c] = fadd2(rs2[c], e);
-              pk[i] = pack_half2(e.x, e.y);
+            for (int c = 0; c < 4; ++c) {
+              rs2[c] = make_float2(0.f, 0.f);
+              exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
+              if (c == kPSplit - 1 || c == 3) {
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar((c == 3 ? B_PHI : B_PLO) + t));
+              }
             }
+            l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
           }
-          tc_st16(tS + c * 16, pk);
-          if (c == kPSplit - 1 || c == 3) {
-            // the first kPSplit chunks / the rest of P are in tensor memory: let the PV MMA start on them
-            TC5_TRACE(t, j, c == 3 ? 6 : 4);
+        }
+        if (SM == 2 && !full_path) {
+          // speculative: the first part is exponentiated while the row maximum is being formed
+          const float mxs = row_max128(sv) * p.scale_log2;
+          const bool inside = mxs <= m + 8.f;   // false for NaN
+          const float2 nm2 = make_float2(-m, -m);
+#pragma unroll
+          for (int c = 0; c < kPSplit; ++c) {
+            rs2[c] = make_float2(0.f, 0.f);
+            exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
+          }
+          if (__any_sync(0xffffffffu, !inside)) {
+            full_path = true;   // nothing has been handed over yet: the chunks are redone below
+          } else {
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(bar((c == 3 ? B_PHI : B_PLO) + t));
-            TC5_TRACE(t, j, c == 3 ? 7 : 5);
+            mbar_arrive(bar(B_PLO + t));
+#pragma unroll
+            for (int c = kPSplit; c < 4; ++c) {
+              rs2[c] = make_float2(0.f, 0.f);
+              exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(B_PHI + t));
+            l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
           }
         }
-        l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
+        if (SM == 3 && !full_path) {
+          // No maximum at all on the common path.  Each part of P is exponentiated against the carried-over
+          // m and checked through its own sum: a part whose sum is at most 2^15 holds no value above 2^15,
+          // so nothing overflowed fp16 (a stale m within 2^8 of the row maximum gives sums <= 2^14 and never
+          // trips the check).  A part that fails is redone against a raised m after O and l have been
+          // rescaled; O may be rescaled once the MMAs issued so far have completed: PV of the previous
+          // step for the first part, the first-part PV of this step (barrier B_OLO) for the second.
+          auto redo_part = [&](const int c0, const int c1, const uint32_t wait_bar, const uint32_t wait_parity) {
+            PROF_COUNT(3 + t, 7);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              if (c < c0 || c >= c1) continue;
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) mx = fmax3(mx, sv[c][i], sv[c][i + 1]);
+            }
+            const float m_new = fmaxf(m, mx * p.scale_log2);
+            const float alpha = fast_exp2(m - m_new);
+            PROF_WAIT(3 + t, 2, wait_or_abort(wait_bar, wait_parity, abort_flag));
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              float o[32];
+              tc_ld32(tO + c * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] *= alpha;
+              tc_st32(tO + c * 32, o);
+            }
+            tc_wait_st();
+            m = m_new;
+            l *= alpha;
+            const float2 nm2r = make_float2(-m, -m);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              if (c < c0 || c >= c1) continue;
+              rs2[c] = make_float2(0.f, 0.f);
+              exp_chunk_store<NPOLY>(sv[c], sc2, nm2r, rs2[c], tS + c * 16);
+            }
+          };
+          {
+            const float2 nm2 = make_float2(-m, -m);
+#pragma unroll
+            for (int c = 0; c < kPSplit; ++c) {
+              rs2[c] = make_float2(0.f, 0.f);
+              exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
+            }
+          }
+          float part = 0.f;
+#pragma unroll
+          for (int c = 0; c < kPSplit; ++c) part += rs2[c].x + rs2[c].y;
+          if (__any_sync(0xffffffffu, !(part <= 32768.f))) {
+            redo_part(0, kPSplit, bar(B_OFULL + t), (blk - 1) & 1u);
+            part = 0.f;
+#pragma unroll
+            for (int c = 0; c < kPSplit; ++c) part += rs2[c].x + rs2[c].y;
+          }
+          l += part;
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(B_PLO + t));
+          {
+            const float2 nm2 = make_float2(-m, -m);
+#pragma unroll
+            for (int c = kPSplit; c < 4; ++c) {
+              rs2[c] = make_float2(0.f, 0.f);
+              exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
+            }
+          }
+          part = 0.f;
+#pragma unroll
+          for (int c = kPSplit; c < 4; ++c) part += rs2[c].x + rs2[c].y;
+          if (__any_sync(0xffffffffu, !(part <= 32768.f))) {
+            redo_part(kPSplit, 4, bar(B_OLO + t), blk & 1u);
+            part = 0.f;
+#pragma unroll
+            for (int c = kPSplit; c < 4; ++c) part += rs2[c].x + rs2[c].y;
+          }
+          l += part;
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(B_PHI + t));
+        }
+        if (full_path) {
+          PROF_COUNT(3 + t, 6);
+          // keys of this tile that the row may attend: [k0, k0 + lim); chunks past the warp's largest
+          // lim are stored as zeros without any exponentials (upper part of a causal diagonal tile)
+          int lim = BN;
+          if (need_mask) {
+            lim = len - k0;
+            if (p.causal && grow - k0 + 1 < lim) lim = grow - k0 + 1;
+            if (lim > BN) lim = BN;
+          }
+          const int lim_max = need_mask ? __reduce_max_sync(0xffffffffu, lim) : BN;
+          const int lim_min = need_mask ? __reduce_min_sync(0xffffffffu, lim) : BN;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (c * 32 + 32 > lim_min) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (c * 32 + i >= lim) sv[c][i] = -INFINITY;
+            }
+          }
+          const float mxs = row_max128(sv) * p.scale_log2;
+          const float m_new = (j == 0) ? mxs : fmaxf(m, mxs);
+          const bool grow_big = (j == 0) || (m_new > m + 8.f);
+          const float alpha = (j > 0 && grow_big) ? fast_exp2(m - m_new) : 1.f;
+          if (j > 0 && __any_sync(0xffffffffu, grow_big)) {
+            // O_t must hold the result of PV(t, j-1) before it is rescaled
+            PROF_WAIT(3 + t, 2, wait_or_abort(bar(B_OFULL + t), (blk - 1) & 1u, abort_flag));
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              float o[32];
+              tc_ld32(tO + c * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] *= alpha;
+              tc_st32(tO + c * 32, o);
+            }
+            tc_wait_st();
+          }
+          if (grow_big) m = m_new;
+          l *= alpha;
+          // ---- P = exp2(S * scale - m), fp16, written over the first 64 columns of S ----
+          const float neg_m = (m == -INFINITY) ? 0.f : -m;
+          const float2 nm2 = make_float2(neg_m, neg_m);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            rs2[c] = make_float2(0.f, 0.f);
+            if (c * 32 < lim_max) exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
+            else zero_chunk_store(tS + c * 16);
+            if (c == kPSplit - 1 || c == 3) {
+              // the first kPSplit chunks / the rest of P are in tensor memory: let the PV MMA start on them
+              tc_wait_st();
+              tc_fence_before();
+              mbar_arrive(bar((c == 3 ? B_PHI : B_PLO) + t));
+            }
+          }
+          l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
+        }
+        PROF_MARK(prof_t_e);
+        PROF_SPAN(3 + t, 4, prof_t_s, prof_t_e);
       }
       // ---- epilogue: O / l -> fp16 -> global.  The next item's first PV of this tile cannot be
       // issued before these threads have produced its P, i.e. after these loads have completed.
-      wait_or_abort(bar(B_OFULL + t), (blk - 1) & 1u, abort_flag);
+      PROF_WAIT(3 + t, 3, wait_or_abort(bar(B_OFULL + t), (blk - 1) & 1u, abort_flag));
+      PROF_MARK(prof_t_o);
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __half* orow;
@@ -674,12 +868,23 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         }
       }
       tc_fence_before();
+      PROF_MARK(prof_t_x);
+      PROF_SPAN(3 + t, 5, prof_t_o, prof_t_x);
     }
   }
 
   // ---- tear-down ------------------------------------------------------------------
+#ifdef FA_TC5_PROF
+  if (prof_on) {
+    const int role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 3 ? 2 : 3 + ((warp - 4) >> 2);
+    prof_smem[role * 16 + 15] += (unsigned long long)(clock64() - prof_start);
+  }
+#endif
   tc_fence_before();
   __syncthreads();
+#ifdef FA_TC5_PROF
+  if (threadIdx.x < 5 * 16) atomicAdd(&g_tc5_prof[threadIdx.x], prof_smem[threadIdx.x]);
+#endif
   if (warp == 2) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -733,6 +938,39 @@ cudaError_t next_item_counter(unsigned long long** out, cudaStream_t stream) {
 
 bool g_tc5_poly = false;  // true: a quarter of the exponentials evaluated as a polynomial on the FMA pipes
 
+using Tc5Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Tc5Params);
+
+#ifdef FA_TC5_SWEEP
+// Tuning build only (-DFA_TC5_SWEEP): every variant below is compiled and one is picked at run time.
+int g_tc5_variant = 0;
+template <int D>
+Tc5Kernel sweep_kernel(int v) {
+  switch (v) {
+    case 1: return prefill_tc5_kernel<D, 0, 2, 1>;
+    case 2: return prefill_tc5_kernel<D, 0, 2, 2>;
+    case 3: return prefill_tc5_kernel<D, 0, 2, 3>;
+    case 4: return prefill_tc5_kernel<D, 2, 2, 3>;
+    case 5: return prefill_tc5_kernel<D, 3, 2, 3>;
+    case 6: return prefill_tc5_kernel<D, 4, 2, 3>;
+    case 7: return prefill_tc5_kernel<D, 0, 3, 3>;
+    case 8: return prefill_tc5_kernel<D, 2, 3, 3>;
+    case 9: return prefill_tc5_kernel<D, 0, 1, 3>;
+    case 10: return prefill_tc5_kernel<D, 2, 2, 1>;
+    case 11: return prefill_tc5_kernel<D, 3, 3, 3>;
+    default: return prefill_tc5_kernel<D, 0, 2, 0>;
+  }
+}
+#endif
+
+template <int D>
+Tc5Kernel pick_kernel() {
+#ifdef FA_TC5_SWEEP
+  return sweep_kernel<D>(g_tc5_variant);
+#else
+  return g_tc5_poly ? prefill_tc5_kernel<D, 2, 2, 3> : prefill_tc5_kernel<D, 0, 2, 3>;
+#endif
+}
+
 template <int D>
 cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t stream) {
   EncodeTiledFn enc = reinterpret_cast<EncodeTiledFn>(encode_fn);
@@ -764,8 +1002,11 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   p.scale_log2 = pp.scale_log2;
   constexpr int KV_STAGES = (D == 128) ? 2 : 4;
   constexpr size_t TILE = (size_t)(D / 64) * 128 * 128;
-  const size_t smem = 1024 + (2 + 2 * KV_STAGES) * TILE + 64 * 8 + 16;  // tiles + barriers, item queue, flags
-  auto kern = g_tc5_poly ? prefill_tc5_kernel<D, true> : prefill_tc5_kernel<D, false>;
+  size_t smem = 1024 + (2 + 2 * KV_STAGES) * TILE + 64 * 8 + 16;  // tiles + barriers, item queue, flags
+#ifdef FA_TC5_PROF
+  smem += 5 * 16 * 8;
+#endif
+  Tc5Kernel kern = pick_kernel<D>();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int max_len = dense ? pp.N : pp.max_seqlen;
@@ -798,9 +1039,21 @@ cudaError_t launch_prefill_tc5(const PrefillParams& p, int D, void* encode_fn, c
   return cudaErrorInvalidValue;
 }
 
-#ifdef FA_TC5_TRACE
-extern "C" int fa_debug_read_tc5_trace(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_tc5_trace, sizeof(long long) * n);
+#ifdef FA_TC5_PROF
+// Instrumented build only: copy the wait counters to the host (and optionally clear them).
+extern "C" int fa_debug_read_tc5_prof(unsigned long long* host, int clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(host, g_tc5_prof, sizeof(unsigned long long) * 5 * 16);
+  if (e == cudaSuccess && clear) {
+    static const unsigned long long zeros[5 * 16] = {0};
+    e = cudaMemcpyToSymbol(g_tc5_prof, zeros, sizeof(zeros));
+  }
+  return (int)e;
+}
+#endif
+#ifdef FA_TC5_SWEEP
+extern "C" int fa_debug_tc5_set_variant(int v) {
+  g_tc5_variant = v;
+  return 0;
 }
 #endif
 

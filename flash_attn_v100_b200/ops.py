@@ -24,7 +24,8 @@ PAGE_BLOCK_SIZE = 16  # flash_attn_kernel.cu:3389
 MAX_D_LARGE = 256     # flash_attn_kernel.cu:36
 SUPPORTED_D = (64, 128, 256)
 
-_workspaces: Dict[Tuple[int, int, int], torch.Tensor] = {}
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+_retired_workspaces: list = []
 
 
 def _chk(cond: bool, msg: str) -> None:
@@ -99,16 +100,34 @@ def _stream_ptr(device, stream_int=None):
 def _workspace(device, stream_int, B, H_Q, H_KV, D):
     """Scratch for split-KV decode, owned by the library shim: one buffer per
     (device, stream), grown on demand.  Calls on one stream are ordered, so they
-    may share it."""
+    may share it.
+
+    A buffer that has been handed to a launch is never freed: a captured CUDA graph
+    keeps its address in its kernel parameters, and a kernel on a stream that the
+    caching allocator does not track (the `_stream` variants) may still be using it
+    when a larger one replaces it.  Replaced buffers are therefore parked in
+    `_retired_workspaces` for the life of the process (a few MiB each, and growth is
+    rare: the size is dominated by the per-CTA partial results, which do not depend on
+    the batch size)."""
     lib = _lib.load()
     _chk(8 <= D <= 256 and D % 8 == 0,
          f"head dimension {D} is not built (decode serves multiples of 8 up to 256)")
     need = int(lib.fa_decode_workspace_bytes(B, H_Q, H_KV, D))
     _chk(need > 0, f"unsupported decode configuration B={B} H_Q={H_Q} H_KV={H_KV} D={D}")
-    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_int)
+    dev_index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (dev_index, stream_int)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:
-        ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        if ws is not None:
+            _retired_workspaces.append(ws)
+        ws = torch.empty(max(2 * need, 8 << 20), dtype=torch.uint8, device=device)
+        current = torch.cuda.current_stream(device)
+        if int(current.cuda_stream) != int(stream_int):
+            # the block may have been released by work still queued on torch's stream: the foreign
+            # stream must not touch it before that work has finished
+            ev = torch.cuda.Event()
+            ev.record(current)
+            torch.cuda.ExternalStream(stream_int, device=device).wait_event(ev)
         _lib.check(lib.fa_decode_workspace_init(_ptr(ws), ws.numel(), ctypes.c_void_p(stream_int)))
         _workspaces[key] = ws
     return ws

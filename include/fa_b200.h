@@ -60,13 +60,17 @@ size_t fa_decode_workspace_bytes(int B, int H_Q, int H_KV, int D);
 
 /* Zero the status word and the arrival counters at the head of a workspace.  REQUIRED once
  * after allocating it, before its first use (the counters must not start from arbitrary
- * bytes); afterwards the kernels keep them consistent, whatever shapes the workspace serves. */
+ * bytes); afterwards the kernels keep them consistent, whatever shapes the workspace serves.
+ * workspace == NULL (workspace_bytes ignored) re-initialises the built-in scratch of
+ * fa_paged_decode_gqa_f16_static_scratch, i.e. clears its status word. */
 int fa_decode_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Read back (synchronously: it waits for `stream`) the sticky device-side status
  * word of a workspace: 0 = clean; bit 0 = a bounded wait on a copy barrier ran
  * out; bit 1 = a block_table entry used by a sequence was outside [0, num_pages).
- * Results of a launch that set a bit are undefined (but no fault is raised). */
+ * Results of a launch that set a bit are undefined (but no fault is raised).
+ * workspace == NULL reads the status word of the built-in scratch of
+ * fa_paged_decode_gqa_f16_static_scratch. */
 int fa_decode_status(const void* workspace, void* stream, int* host_status_out);
 
 /* Tuning hook for the decode kernels: consumer warps per CTA, copy-ring depth per
@@ -113,16 +117,24 @@ int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_ca
  *  - Limit: shapes whose fa_decode_workspace_bytes(B, H_Q, H_KV, D) exceeds 8 MiB
  *    are rejected with FA_ERR_WORKSPACE (nothing is launched).  The benchmark shape
  *    (B=64, 32/8 heads, D=128) needs 4.7 MiB.
- *  - The first call on each device looks up the array's device address (and clears
- *    its status word); make that first call outside of any stream capture.
+ *  - The first call on each device (of this function, or of fa_decode_status /
+ *    fa_decode_workspace_init with a NULL workspace) looks up the array's device
+ *    address and clears the part that must start at zero: the status word and the
+ *    arrival counters of split segments (the same bytes fa_decode_workspace_init
+ *    clears in a caller-owned workspace).  It waits for that clear on `stream`, so
+ *    make this first call outside of any stream capture.
  *  - Nothing in this call allocates or frees device memory.
+ *  - Every argument is validated before the device is touched.
  *  - All calls on a device share the one array, and it keeps whatever the previous
- *    call left in it (each call rewrites every part it later reads).  Two calls that
- *    can overlap on the GPU - different streams without an ordering between them -
- *    race on it; order them, or give all but one of them a workspace of their own
- *    through fa_paged_decode_gqa_f16.
- *  - The device status word of the built-in scratch is not exposed through
- *    fa_decode_status.
+ *    call left in it: the counters return to "no arrivals" at the end of every launch,
+ *    prefix sums and partial results are rewritten by each call before it reads them.
+ *    Two calls that can overlap on the GPU - different streams without an ordering
+ *    between them - race on it; order them, or give all but one of them a workspace of
+ *    their own through fa_paged_decode_gqa_f16.
+ *  - Device-side conditions (a bounded wait that ran out, a block_table entry outside
+ *    the pool) are recorded in the array's status word like in any workspace: read it
+ *    with fa_decode_status(NULL, stream, &status) and clear it with
+ *    fa_decode_workspace_init(NULL, 0, stream).
  */
 int fa_paged_decode_gqa_f16_static_scratch(const void* q, const void* k_cache, const void* v_cache,
                                            void* out, const int32_t* block_table,
