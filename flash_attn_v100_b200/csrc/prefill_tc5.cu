@@ -16,7 +16,7 @@
 //   warps 4-7   softmax of tile 0 (thread = one query row = one TMEM lane)
 //   warps 8-11  softmax of tile 1
 // The two softmax groups ping-pong: while one group turns S_0 into P_0, the tensor core
-// runs the other tile's MMAs.  P is written back to tensor memory as fp16 over the first
+// runs the other tile's MMAs.  P is written back to tensor memory as fp16 over the second
 // half of the S columns it came from and is the A operand of the PV MMA (no shared-memory
 // round trip).  Softmax is fp32, base 2, online across KV tiles; O is rescaled in tensor
 // memory only when a row maximum grows by more than 2^8 (stale maxima keep P <= 256, exact
@@ -55,7 +55,13 @@ __device__ unsigned long long g_tc5_prof[5 * 16];
   do { if (prof_on) prof_smem[(role) * 16 + (cat)] += (unsigned long long)((b) - (a)); } while (0)
 #define PROF_COUNT(role, cat) \
   do { if (prof_on) prof_smem[(role) * 16 + (cat)] += 1ull; } while (0)
+// cross-role latencies: one role stamps the clock, another adds the time since that stamp
+#define PROF_STAMP(idx) do { if (prof_on) prof_smem[5 * 16 + (idx)] = (unsigned long long)clock64(); } while (0)
+#define PROF_SINCE(role, cat, idx) \
+  do { if (prof_on) prof_smem[(role) * 16 + (cat)] += (unsigned long long)clock64() - prof_smem[5 * 16 + (idx)]; } while (0)
 #else
+#define PROF_STAMP(idx) do { } while (0)
+#define PROF_SINCE(role, cat, idx) do { } while (0)
 #define PROF_WAIT(role, cat, stmt) do { stmt; } while (0)
 #define PROF_MARK(var) do { } while (0)
 #define PROF_SPAN(role, cat, a, b) do { } while (0)
@@ -209,7 +215,7 @@ __device__ __forceinline__ constexpr bool pair_uses_poly(int i) {
 
 // One 32-column chunk of a score row: P = exp2(s * scale - m) as fp16 pairs, written to tensor memory at
 // `taddr` (16 columns); the fp32 sum of the chunk is added to `rs`.
-template <int NPOLY>
+template <int NPOLY, int DBG = 0>
 __device__ __forceinline__ void exp_chunk_store(const float (&s)[32], float2 sc2, float2 nm2, float2& rs,
                                                 uint32_t taddr) {
   uint32_t pk[16];
@@ -217,14 +223,16 @@ __device__ __forceinline__ void exp_chunk_store(const float (&s)[32], float2 sc2
   for (int i = 0; i < 16; ++i) {
     const float2 x = ffma2(make_float2(s[2 * i], s[2 * i + 1]), sc2, nm2);
     float2 e;
-    if (pair_uses_poly<NPOLY>(i)) {
+    if (DBG & 1) {   // timing experiments only: no exponential
+      e = x;
+    } else if (pair_uses_poly<NPOLY>(i)) {
       e = exp2_poly2(x);
     } else {
       e.x = fast_exp2(x.x);
       e.y = fast_exp2(x.y);
     }
     rs = fadd2(rs, e);
-    pk[i] = pack_half2(e.x, e.y);
+    pk[i] = (DBG & 8) ? __float_as_uint(e.x) : pack_half2(e.x, e.y);   // DBG 8: no conversion
   }
   tc_st16(taddr, pk);
 }
@@ -320,10 +328,11 @@ __device__ __forceinline__ bool tc5_decode_item(const Tc5Params& p, long long it
 
 // NPOLY: value pairs of every eight whose exp2 runs as a polynomial on the FMA pipes (0..4);
 // PSPLIT: 32-column chunks of P handed to the PV MMA with the first barrier (1..3);
-// SM: softmax scheme on tiles that need no masking (see the softmax role): 0 row maximum and rescale
-// decision first, 1 row maximum first but exponentials against the carried-over m, 2 first part
-// exponentiated while the maximum is formed, 3 no maximum, parts validated through their sums.
-template <int D, int NPOLY, int PSPLIT, int SM>
+// SM: 0 every tile takes the full softmax path (row maximum and rescale decision first); 1 tiles that need no
+// masking take the fast path described in the softmax role.
+// DBG (tuning builds only, results are wrong): 1 no exp2, 2 no PV MMAs, 4 no QK MMAs, 8 no fp16 conversion,
+// 16 the softmax hands over at once without computing anything.
+template <int D, int NPOLY, int PSPLIT, int SM, int DBG = 0>
 __global__ void __launch_bounds__(384, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                    const __grid_constant__ CUtensorMap vmap, const Tc5Params p) {
@@ -336,6 +345,8 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t O_COL0 = 256;
+  constexpr uint32_t P_COL = 64;             // P (fp16, 64 columns) lies over the SECOND half of its S: writing the
+                                             // first part of P leaves the first half of S intact in tensor memory
   constexpr int kPSplit = PSPLIT;            // P is handed to the PV MMA in two parts: 32*kPSplit keys, then the rest
   constexpr int kItemQ = 4;                  // depth of the per-CTA item queue
   constexpr int kItemConsumers = 2 + 256;    // two MMA lanes + every softmax thread
@@ -350,9 +361,8 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   // barrier indices
   constexpr int B_QFULL = 0, B_QEMPTY = 2, B_KFULL = B_QEMPTY + 2, B_KEMPTY = B_KFULL + KV_STAGES,
                 B_VFULL = B_KEMPTY + KV_STAGES, B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES,
-                B_PLO = B_SFULL + 2, B_PHI = B_PLO + 2, B_OFULL = B_PHI + 2, B_TOKEN = B_OFULL + 2,
-                B_OLO = B_TOKEN + 2, B_IFULL = B_OLO + 2, B_IEMPTY = B_IFULL + kItemQ,
-                B_COUNT = B_IEMPTY + kItemQ;
+                B_PLO = B_SFULL + 2, B_PHI = B_PLO + 2, B_TOKEN = B_PHI + 2,
+                B_IFULL = B_TOKEN + 2, B_IEMPTY = B_IFULL + kItemQ, B_COUNT = B_IEMPTY + kItemQ;
   volatile long long* item_slot = reinterpret_cast<volatile long long*>(bars + B_COUNT);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT + kItemQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -381,9 +391,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       mbar_init(bar(B_SFULL + t), 1);
       mbar_init(bar(B_PLO + t), 128);
       mbar_init(bar(B_PHI + t), 128);
-      mbar_init(bar(B_OFULL + t), 1);
       mbar_init(bar(B_TOKEN + t), 1);
-      mbar_init(bar(B_OLO + t), 1);
     }
     for (int i = 0; i < kItemQ; ++i) {
       mbar_init(bar(B_IFULL + i), 1);
@@ -499,7 +507,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         // first part: the keys whose P arrives with the first barrier (kPSplit chunks of 32 keys)
 #pragma unroll
         for (int ks = half ? 2 * kPSplit : 0; ks < (half ? BN / 16 : 2 * kPSplit); ++ks) {
-          tc_mma_ts(dO, dS + (uint32_t)ks * 8u, b0 + (uint32_t)ks * 128u, IDESC_PV, (acc | (ks > 0 ? 1u : 0u)));
+          tc_mma_ts(dO, dS + P_COL + (uint32_t)ks * 8u, b0 + (uint32_t)ks * 128u, IDESC_PV, (acc | (ks > 0 ? 1u : 0u)));
         }
       };
       uint32_t kv_it = 0, q_cnt = 0, blk = 0, tok_waits = 0;
@@ -531,11 +539,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             PROF_WAIT(1 + t, 2, wait_or_abort(bar(B_KFULL + st), (kv_it / KV_STAGES) & 1u, abort_flag));
             tc_fence_after();
             if (t == 1) take_token();
-            issue_qk(st);
+            if (!(DBG & 4)) issue_qk(st);
             pass_token();
             tc_commit(bar(B_SFULL + t));
-            tc_commit(bar(B_KEMPTY + st));
-            if (n_mine == 1) tc_commit(bar(B_QEMPTY + t));
           }
           for (int j = 0; j < n_mine; ++j, ++blk) {
             const uint32_t g = kv_it + (uint32_t)j;
@@ -548,24 +554,26 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             PROF_WAIT(1 + t, 3, wait_or_abort(bar(B_VFULL + st), ph, abort_flag));
             if (more) PROF_WAIT(1 + t, 4, wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag));
             PROF_WAIT(1 + t, 5, wait_or_abort(bar(B_PLO + t), blk & 1u, abort_flag));
+            PROF_SINCE(1 + t, 9, 2 + t);      // P_lo arrival (row 0) -> seen by the MMA lane
             // tile 1's block j+1 follows tile 0's block j+1; tile 0's block j+1 follows tile 1's
             // block j, which exists unless tile 1 has already run out of KV tiles
             if (t == 1 || j <= it.n_kv[1]) take_token();
             tc_fence_after();
-            issue_pv(st, j > 0 ? 1u : 0u, 0);
-            if (SM == 3) tc_commit(bar(B_OLO + t));   // lets the softmax rescale O between the two parts
+            if (!(DBG & 2)) issue_pv(st, j > 0 ? 1u : 0u, 0);
             PROF_WAIT(1 + t, 7, wait_or_abort(bar(B_PHI + t), blk & 1u, abort_flag));
+            PROF_SINCE(1 + t, 10, 4 + t);     // P_hi arrival (row 0) -> seen by the MMA lane
+            PROF_MARK(prof_t_i);
             tc_fence_after();
-            issue_pv(st, 1u, 1);
-            if (more) issue_qk(st1);
+            if (!(DBG & 2)) issue_pv(st, 1u, 1);
+            if (more && !(DBG & 4)) issue_qk(st1);
             pass_token();
-            tc_commit(bar(B_OFULL + t));
-            tc_commit(bar(B_VEMPTY + st));
-            if (more) {
-              tc_commit(bar(B_SFULL + t));
-              tc_commit(bar(B_KEMPTY + st1));
-              if (j + 2 == n_mine) tc_commit(bar(B_QEMPTY + t));   // that was the last QK of this item
-            }
+            // ONE commit per batch (a tcgen05.commit costs the tensor pipe about as much as an MMA): the
+            // batch barrier tells the softmax group that S(j+1) is complete and O holds PV(j); that group
+            // passes the news on to the copy lane (K / V stages and the Q buffer that have become free)
+            tc_commit(bar(B_SFULL + t));
+            PROF_STAMP(t);
+            PROF_MARK(prof_t_c);
+            PROF_SPAN(1 + t, 11, prof_t_i, prof_t_c);   // issue of PV_hi + QK + commit
           }
           if (other_active) {
             // balance the token barriers before the next item: tile 0 hands tile 1 the token for a
@@ -601,24 +609,33 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ============================ softmax groups ====================================
     // Thread = one query row.  State per row: a reference exponent m (any finite number works as long as
-    // P = exp2(s * scale - m) stays inside the fp16 range; it starts at 0 and is raised to a row maximum
-    // only when a score leaves the window below), the row sum l relative to m, and O in tensor memory,
-    // also relative to m.
-    //   The first KV tile of an item and tiles that need masking take the full path: row maximum first,
-    //   m raised when it grows by more than 2^8 (O rescaled in tensor memory), then the exponentials.
-    //   Other tiles run one of the schemes SM selects; all of them keep m unless a score leaves the fp16
-    //   window above it.
+    // P = exp2(s * scale - m) stays inside the fp16 range), the row sum l relative to m, and O in tensor
+    // memory, also relative to m.
+    //   full path (first KV tile of an item, tiles that need masking, rows that left the window below):
+    //     row maximum first, m raised when the maximum grows by more than 2^8 with O rescaled in tensor
+    //     memory, then the exponentials.
+    //   fast path (SM 1, other tiles): no dependent chain in front of the exponentials.  The first part of P
+    //     is exponentiated against the m carried over from the previous step while the raw maximum of the
+    //     second part is formed in the same instruction stream; the step goes ahead if the first part's sum
+    //     shows that nothing exceeded 2^15 and the second part's maximum stays below m + 15 (so P fits fp16);
+    //     otherwise nothing has been handed over yet and the step is redone on the full path.
+    // The group also forwards what a completed MMA batch implies: the batch barrier B_SFULL of step j says
+    // that PV(j-1) and QK(j) are done, so V stage j-1 and K stage j (and, after the last QK, the Q buffer) are
+    // free; the thread of row 0 arrives on the copy lane's barriers for them.
     const int t = (warp - 4) >> 2;
     const int wq = warp & 3;                   // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;            // row within the tile == TMEM lane
     const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
     const uint32_t tS = lane_base + (uint32_t)t * 128u;
+    const uint32_t tP = tS + P_COL;
     const uint32_t tO = lane_base + O_COL0 + (uint32_t)t * D;
 #ifdef FA_TC5_PROF
     prof_on = (row == 0);
 #endif
     const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
-    uint32_t blk = 0;
+    uint32_t sph = 0;        // completed phases of B_SFULL[t] that this thread has consumed
+    uint32_t pph = 0;        // KV steps of this tile so far: phase of B_PLO / B_PHI
+    uint32_t kv_it = 0;      // KV tiles of all items so far: ring stage of K / V
     for (uint32_t ic = 0;; ++ic) {
       if (*abort_flag) break;
       const int slot = ic % kItemQ;
@@ -629,15 +646,25 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       Tc5Item it;
       tc5_decode_item(p, item, it);
       const int n_mine = it.n_kv[t];
+      const uint32_t kv0 = kv_it;
+      kv_it += (uint32_t)it.n_max;
       if (n_mine == 0) continue;
       const int len = it.len;
       const int grow = it.row0[t] + row;       // row within the sequence
       float m = 0.f, l = 0.f;
-      for (int j = 0; j < n_mine; ++j, ++blk) {
+      for (int j = 0; j < n_mine; ++j, ++pph) {
         PROF_COUNT(3 + t, 14);
-        PROF_WAIT(3 + t, 1, wait_or_abort(bar(B_SFULL + t), blk & 1u, abort_flag));
+        PROF_WAIT(3 + t, 1, wait_or_abort(bar(B_SFULL + t), sph & 1u, abort_flag));
+        ++sph;
+        if (j > 0) PROF_SINCE(3 + t, 8, t);   // commit issued by the MMA lane -> batch seen complete here
         PROF_MARK(prof_t_s);
         tc_fence_after();
+        if (row == 0) {
+          // QK(j) is complete: K stage j is free; so is PV(j-1): V stage j-1
+          mbar_arrive(bar(B_KEMPTY + (int)((kv0 + (uint32_t)j) % KV_STAGES)));
+          if (j > 0) mbar_arrive(bar(B_VEMPTY + (int)((kv0 + (uint32_t)j - 1u) % KV_STAGES)));
+          if (j == n_mine - 1) mbar_arrive(bar(B_QEMPTY + t));   // that was the last QK of this item
+        }
         const int k0 = j * BN;
         const bool need_mask = (k0 + BN > len) || (p.causal && (k0 + BN - 1 > it.row0[t]));
         // ---- the whole score row of this thread: 128 fp32 values, one round trip ----
@@ -648,136 +675,62 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         tc_ld32(tS + 96, sv[3]);
         tc_wait_ld();
         float2 rs2[4];
+        if (DBG & 16) {
+          tc_fence_before();
+          PROF_STAMP(2 + t);
+          mbar_arrive(bar(B_PLO + t));
+          PROF_STAMP(4 + t);
+          mbar_arrive(bar(B_PHI + t));
+          continue;
+        }
         bool full_path = SM == 0 || need_mask || j == 0;
         if (SM == 1 && !full_path) {
-          // row maximum first, but no dependent chain behind it: the exponentials use the carried-over m
-          const float mxs = row_max128(sv) * p.scale_log2;
-          if (__any_sync(0xffffffffu, !(mxs <= m + 8.f))) {
-            full_path = true;
-          } else {
-            const float2 nm2 = make_float2(-m, -m);
+          float mx2 = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              rs2[c] = make_float2(0.f, 0.f);
-              exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
-              if (c == kPSplit - 1 || c == 3) {
-                tc_wait_st();
-                tc_fence_before();
-                mbar_arrive(bar((c == 3 ? B_PHI : B_PLO) + t));
-              }
+          for (int c = kPSplit; c < 4; ++c) {
+            float a0 = fmaxf(sv[c][0], sv[c][1]), a1 = fmaxf(sv[c][2], sv[c][3]);
+#pragma unroll
+            for (int i = 4; i < 32; i += 4) {
+              a0 = fmax3(a0, sv[c][i], sv[c][i + 1]);
+              a1 = fmax3(a1, sv[c][i + 2], sv[c][i + 3]);
             }
-            l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
+            mx2 = fmax3(mx2, a0, a1);
           }
-        }
-        if (SM == 2 && !full_path) {
-          // speculative: the first part is exponentiated while the row maximum is being formed
-          const float mxs = row_max128(sv) * p.scale_log2;
-          const bool inside = mxs <= m + 8.f;   // false for NaN
           const float2 nm2 = make_float2(-m, -m);
 #pragma unroll
           for (int c = 0; c < kPSplit; ++c) {
             rs2[c] = make_float2(0.f, 0.f);
-            exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
-          }
-          if (__any_sync(0xffffffffu, !inside)) {
-            full_path = true;   // nothing has been handed over yet: the chunks are redone below
-          } else {
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(B_PLO + t));
-#pragma unroll
-            for (int c = kPSplit; c < 4; ++c) {
-              rs2[c] = make_float2(0.f, 0.f);
-              exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
-            }
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(B_PHI + t));
-            l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
-          }
-        }
-        if (SM == 3 && !full_path) {
-          // No maximum at all on the common path.  Each part of P is exponentiated against the carried-over
-          // m and checked through its own sum: a part whose sum is at most 2^15 holds no value above 2^15,
-          // so nothing overflowed fp16 (a stale m within 2^8 of the row maximum gives sums <= 2^14 and never
-          // trips the check).  A part that fails is redone against a raised m after O and l have been
-          // rescaled; O may be rescaled once the MMAs issued so far have completed: PV of the previous
-          // step for the first part, the first-part PV of this step (barrier B_OLO) for the second.
-          auto redo_part = [&](const int c0, const int c1, const uint32_t wait_bar, const uint32_t wait_parity) {
-            PROF_COUNT(3 + t, 7);
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              if (c < c0 || c >= c1) continue;
-#pragma unroll
-              for (int i = 0; i < 32; i += 2) mx = fmax3(mx, sv[c][i], sv[c][i + 1]);
-            }
-            const float m_new = fmaxf(m, mx * p.scale_log2);
-            const float alpha = fast_exp2(m - m_new);
-            PROF_WAIT(3 + t, 2, wait_or_abort(wait_bar, wait_parity, abort_flag));
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              float o[32];
-              tc_ld32(tO + c * 32, o);
-              tc_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] *= alpha;
-              tc_st32(tO + c * 32, o);
-            }
-            tc_wait_st();
-            m = m_new;
-            l *= alpha;
-            const float2 nm2r = make_float2(-m, -m);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              if (c < c0 || c >= c1) continue;
-              rs2[c] = make_float2(0.f, 0.f);
-              exp_chunk_store<NPOLY>(sv[c], sc2, nm2r, rs2[c], tS + c * 16);
-            }
-          };
-          {
-            const float2 nm2 = make_float2(-m, -m);
-#pragma unroll
-            for (int c = 0; c < kPSplit; ++c) {
-              rs2[c] = make_float2(0.f, 0.f);
-              exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
-            }
+            exp_chunk_store<NPOLY, DBG>(sv[c], sc2, nm2, rs2[c], tP + c * 16);
           }
           float part = 0.f;
 #pragma unroll
           for (int c = 0; c < kPSplit; ++c) part += rs2[c].x + rs2[c].y;
-          if (__any_sync(0xffffffffu, !(part <= 32768.f))) {
-            redo_part(0, kPSplit, bar(B_OFULL + t), (blk - 1) & 1u);
-            part = 0.f;
-#pragma unroll
-            for (int c = 0; c < kPSplit; ++c) part += rs2[c].x + rs2[c].y;
-          }
-          l += part;
-          tc_wait_st();
-          tc_fence_before();
-          mbar_arrive(bar(B_PLO + t));
-          {
-            const float2 nm2 = make_float2(-m, -m);
+          const bool inside = (part <= 32768.f) && (mx2 * p.scale_log2 <= m + 15.f);   // false for NaN
+          if (__any_sync(0xffffffffu, !inside)) {
+            // nothing has been handed over yet: the step is redone below.  The first half of S is still
+            // intact in tensor memory (P lies over the second half, which the registers hold)
+            full_path = true;
+            tc_ld32(tS, sv[0]);
+            tc_ld32(tS + 32, sv[1]);
+            tc_wait_ld();
+          } else {
+            tc_wait_st();
+            tc_fence_before();
+            PROF_STAMP(2 + t);
+            mbar_arrive(bar(B_PLO + t));
 #pragma unroll
             for (int c = kPSplit; c < 4; ++c) {
               rs2[c] = make_float2(0.f, 0.f);
-              exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
+              exp_chunk_store<NPOLY, DBG>(sv[c], sc2, nm2, rs2[c], tP + c * 16);
             }
-          }
-          part = 0.f;
-#pragma unroll
-          for (int c = kPSplit; c < 4; ++c) part += rs2[c].x + rs2[c].y;
-          if (__any_sync(0xffffffffu, !(part <= 32768.f))) {
-            redo_part(kPSplit, 4, bar(B_OLO + t), blk & 1u);
-            part = 0.f;
+            tc_wait_st();
+            tc_fence_before();
+            PROF_STAMP(4 + t);
+            mbar_arrive(bar(B_PHI + t));
 #pragma unroll
             for (int c = kPSplit; c < 4; ++c) part += rs2[c].x + rs2[c].y;
+            l += part;
           }
-          l += part;
-          tc_wait_st();
-          tc_fence_before();
-          mbar_arrive(bar(B_PHI + t));
         }
         if (full_path) {
           PROF_COUNT(3 + t, 6);
@@ -804,9 +757,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           const bool grow_big = (j == 0) || (m_new > m + 8.f);
           const float alpha = (j > 0 && grow_big) ? fast_exp2(m - m_new) : 1.f;
           if (j > 0 && __any_sync(0xffffffffu, grow_big)) {
-            // O_t must hold the result of PV(t, j-1) before it is rescaled
-            PROF_WAIT(3 + t, 2, wait_or_abort(bar(B_OFULL + t), (blk - 1) & 1u, abort_flag));
-            tc_fence_after();
+            // O_t holds the result of PV(t, j-1): the batch barrier waited for above covers it
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               float o[32];
@@ -820,18 +771,19 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           }
           if (grow_big) m = m_new;
           l *= alpha;
-          // ---- P = exp2(S * scale - m), fp16, written over the first 64 columns of S ----
+          // ---- P = exp2(S * scale - m), fp16, written over the last 64 columns of S ----
           const float neg_m = (m == -INFINITY) ? 0.f : -m;
           const float2 nm2 = make_float2(neg_m, neg_m);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             rs2[c] = make_float2(0.f, 0.f);
-            if (c * 32 < lim_max) exp_chunk_store<NPOLY>(sv[c], sc2, nm2, rs2[c], tS + c * 16);
-            else zero_chunk_store(tS + c * 16);
+            if (c * 32 < lim_max) exp_chunk_store<NPOLY, DBG>(sv[c], sc2, nm2, rs2[c], tP + c * 16);
+            else zero_chunk_store(tP + c * 16);
             if (c == kPSplit - 1 || c == 3) {
               // the first kPSplit chunks / the rest of P are in tensor memory: let the PV MMA start on them
               tc_wait_st();
               tc_fence_before();
+              PROF_STAMP((c == 3 ? 4 : 2) + t);
               mbar_arrive(bar((c == 3 ? B_PHI : B_PLO) + t));
             }
           }
@@ -840,11 +792,14 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         PROF_MARK(prof_t_e);
         PROF_SPAN(3 + t, 4, prof_t_s, prof_t_e);
       }
-      // ---- epilogue: O / l -> fp16 -> global.  The next item's first PV of this tile cannot be
-      // issued before these threads have produced its P, i.e. after these loads have completed.
-      PROF_WAIT(3 + t, 3, wait_or_abort(bar(B_OFULL + t), (blk - 1) & 1u, abort_flag));
+      // ---- epilogue: O / l -> fp16 -> global.  The batch barrier of the last step covers PV(n-1).  The
+      // next item's first PV of this tile cannot be issued before these threads have produced its P, i.e.
+      // after these loads have completed.
+      PROF_WAIT(3 + t, 3, wait_or_abort(bar(B_SFULL + t), sph & 1u, abort_flag));
+      ++sph;
       PROF_MARK(prof_t_o);
       tc_fence_after();
+      if (row == 0) mbar_arrive(bar(B_VEMPTY + (int)((kv0 + (uint32_t)n_mine - 1u) % KV_STAGES)));
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __half* orow;
       if (p.dense) orow = p.out + (long long)it.seq * p.o_batch_stride + (long long)it.head[t] * p.o_head_stride +
@@ -947,16 +902,14 @@ template <int D>
 Tc5Kernel sweep_kernel(int v) {
   switch (v) {
     case 1: return prefill_tc5_kernel<D, 0, 2, 1>;
-    case 2: return prefill_tc5_kernel<D, 0, 2, 2>;
-    case 3: return prefill_tc5_kernel<D, 0, 2, 3>;
-    case 4: return prefill_tc5_kernel<D, 2, 2, 3>;
-    case 5: return prefill_tc5_kernel<D, 3, 2, 3>;
-    case 6: return prefill_tc5_kernel<D, 4, 2, 3>;
-    case 7: return prefill_tc5_kernel<D, 0, 3, 3>;
-    case 8: return prefill_tc5_kernel<D, 2, 3, 3>;
-    case 9: return prefill_tc5_kernel<D, 0, 1, 3>;
-    case 10: return prefill_tc5_kernel<D, 2, 2, 1>;
-    case 11: return prefill_tc5_kernel<D, 3, 3, 3>;
+    case 2: return prefill_tc5_kernel<D, 0, 2, 1, 1>;         // no exp2
+    case 3: return prefill_tc5_kernel<D, 0, 1, 1>;
+    case 4: return prefill_tc5_kernel<D, 0, 2, 1, 16>;        // no softmax at all
+    case 5: return prefill_tc5_kernel<D, 0, 2, 1, 16 | 2>;    // no softmax, QK only
+    case 6: return prefill_tc5_kernel<D, 0, 2, 1, 16 | 4>;    // no softmax, PV only
+    case 7: return prefill_tc5_kernel<D, 0, 3, 1>;
+    case 8: return prefill_tc5_kernel<D, 2, 2, 1>;
+    case 9: return prefill_tc5_kernel<D, 4, 2, 1>;
     default: return prefill_tc5_kernel<D, 0, 2, 0>;
   }
 }
@@ -967,7 +920,7 @@ Tc5Kernel pick_kernel() {
 #ifdef FA_TC5_SWEEP
   return sweep_kernel<D>(g_tc5_variant);
 #else
-  return g_tc5_poly ? prefill_tc5_kernel<D, 2, 2, 3> : prefill_tc5_kernel<D, 0, 2, 3>;
+  return g_tc5_poly ? prefill_tc5_kernel<D, 2, 2, 1> : prefill_tc5_kernel<D, 0, 2, 1>;
 #endif
 }
 
@@ -1004,7 +957,7 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   constexpr size_t TILE = (size_t)(D / 64) * 128 * 128;
   size_t smem = 1024 + (2 + 2 * KV_STAGES) * TILE + 64 * 8 + 16;  // tiles + barriers, item queue, flags
 #ifdef FA_TC5_PROF
-  smem += 5 * 16 * 8;
+  smem += (5 * 16 + 8) * 8;
 #endif
   Tc5Kernel kern = pick_kernel<D>();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
