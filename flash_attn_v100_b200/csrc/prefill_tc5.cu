@@ -16,7 +16,7 @@
 //   warps 4-7   softmax of tile 0 (thread = one query row = one TMEM lane)
 //   warps 8-11  softmax of tile 1
 // The two softmax groups ping-pong: while one group turns S_0 into P_0, the tensor core
-// runs the other tile's MMAs.  P is written back to tensor memory as fp16 over the second
+// runs the other tile's MMAs.  P is written back to tensor memory as fp16 over the first
 // half of the S columns it came from and is the A operand of the PV MMA (no shared-memory
 // round trip).  Softmax is fp32, base 2, online across KV tiles; O is rescaled in tensor
 // memory only when a row maximum grows by more than 2^8 (stale maxima keep P <= 256, exact
@@ -98,6 +98,14 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   return false;
 }
 
+// Bounded wait that does not look at the abort flag: used on the way out, to let asynchronous copies and
+// MMAs that are still in flight finish before shared and tensor memory are given up.
+__device__ __forceinline__ void drain_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kTc5MaxPolls; ++i)
+    if (mbar_try_wait(bar, parity)) return;
+  atomicOr(&g_prefill_status, kStatusWaitTimeout);
+}
+
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
                                             uint32_t bar) {
   asm volatile(
@@ -112,17 +120,27 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// The MMA role runs with its whole warp converged and lets one elected lane issue (elect.sync): the
+// addresses and descriptors are then uniform across the warp, which keeps the instruction stream of the
+// issuing warp short (it shares its scheduler with four softmax warps).  Commits are issued the same way,
+// so that they track the MMAs of the same thread.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  __syncwarp();
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar)
+      : "memory");
 }
 
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -130,9 +148,10 @@ __device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint
 __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -150,16 +169,14 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const float (&v)[32]) {
-  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
       : "memory");
 }
 __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -201,8 +218,9 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
   float2 r = ffma2(make_float2(0.05508868f, 0.05508868f), f, make_float2(0.24260405f, 0.24260405f));
   r = ffma2(r, f, make_float2(0.69327623f, 0.69327623f));
   r = ffma2(r, f, make_float2(0.99992895f, 0.99992895f));
-  r.x = __int_as_float(__float_as_int(r.x) + (__float_as_int(t.x) << 23));
-  r.y = __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23));
+  // bits(r) + (n << 23): one integer multiply-add each (the low bits of t hold n; overflow of the product is meant)
+  r.x = __uint_as_float(__float_as_uint(t.x) * 0x800000u + __float_as_uint(r.x));
+  r.y = __uint_as_float(__float_as_uint(t.y) * 0x800000u + __float_as_uint(r.y));
   return r;
 }
 
@@ -242,22 +260,6 @@ __device__ __forceinline__ void zero_chunk_store(uint32_t taddr) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) pk[i] = 0u;
   tc_st16(taddr, pk);
-}
-
-// Maximum of a 128-value score row held in registers (two chains per chunk of three-input maxima).
-__device__ __forceinline__ float row_max128(const float (&sv)[4][32]) {
-  float mxc[4];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    float a0 = fmaxf(sv[c][0], sv[c][1]), a1 = fmaxf(sv[c][2], sv[c][3]);
-#pragma unroll
-    for (int i = 4; i < 32; i += 4) {
-      a0 = fmax3(a0, sv[c][i], sv[c][i + 1]);
-      a1 = fmax3(a1, sv[c][i + 2], sv[c][i + 3]);
-    }
-    mxc[c] = fmaxf(a0, a1);
-  }
-  return fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
 }
 
 // Shared-memory matrix descriptor for 128-byte-swizzled tiles made of 128-byte rows.
@@ -327,13 +329,12 @@ __device__ __forceinline__ bool tc5_decode_item(const Tc5Params& p, long long it
 }
 
 // NPOLY: value pairs of every eight whose exp2 runs as a polynomial on the FMA pipes (0..4);
-// PSPLIT: 32-column chunks of P handed to the PV MMA with the first barrier (1..3);
 // SM: 0 every tile takes the full softmax path (row maximum and rescale decision first); 1 tiles that need no
 // masking take the fast path described in the softmax role.
 // DBG (tuning builds only, results are wrong): 1 no exp2, 2 no PV MMAs, 4 no QK MMAs, 8 no fp16 conversion,
-// 16 the softmax hands over at once without computing anything.
-template <int D, int NPOLY, int PSPLIT, int SM, int DBG = 0>
-__global__ void __launch_bounds__(384, 1)
+// 16 the softmax hands over at once without computing anything, 32 no turn taking between the tiles (valid results).
+template <int D, int NPOLY, int SM, int DBG = 0>
+__global__ void __launch_bounds__(640, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                    const __grid_constant__ CUtensorMap vmap, const Tc5Params p) {
   constexpr int BM = 128, BN = 128;
@@ -345,11 +346,13 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t O_COL0 = 256;
-  constexpr uint32_t P_COL = 64;             // P (fp16, 64 columns) lies over the SECOND half of its S: writing the
-                                             // first part of P leaves the first half of S intact in tensor memory
-  constexpr int kPSplit = PSPLIT;            // P is handed to the PV MMA in two parts: 32*kPSplit keys, then the rest
+  // P (fp16, 64 columns = four quarters of 16) lies over columns [16, 80) of its S, and the quarters hold the
+  // keys of the score chunks 0, 1, 3, 2 in that order.  With this placement every quarter is written over
+  // score columns that its writer already holds in registers (see the softmax role), so the two threads of a
+  // row never overwrite scores the other one still has to read from tensor memory.
+  constexpr uint32_t P_COL = 16;
   constexpr int kItemQ = 4;                  // depth of the per-CTA item queue
-  constexpr int kItemConsumers = 2 + 256;    // two MMA lanes + every softmax thread
+  constexpr int kItemConsumers = 1 + 2 + 16; // the copy lane, two MMA lanes, one arrival per softmax warp
 
   extern __shared__ uint8_t smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
@@ -361,17 +364,21 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   // barrier indices
   constexpr int B_QFULL = 0, B_QEMPTY = 2, B_KFULL = B_QEMPTY + 2, B_KEMPTY = B_KFULL + KV_STAGES,
                 B_VFULL = B_KEMPTY + KV_STAGES, B_VEMPTY = B_VFULL + KV_STAGES, B_SFULL = B_VEMPTY + KV_STAGES,
-                B_PLO = B_SFULL + 2, B_PHI = B_PLO + 2, B_TOKEN = B_PHI + 2,
-                B_IFULL = B_TOKEN + 2, B_IEMPTY = B_IFULL + kItemQ, B_COUNT = B_IEMPTY + kItemQ;
+                B_PFULL = B_SFULL + 2, B_TOKEN = B_PFULL + 2,
+                B_IFULL = B_TOKEN + 2, B_IEMPTY = B_IFULL + kItemQ, B_PAIR = B_IEMPTY + kItemQ,
+                B_DRAIN = B_PAIR + 8, B_TURN = B_DRAIN + 2, B_COUNT = B_TURN + 2;
   volatile long long* item_slot = reinterpret_cast<volatile long long*>(bars + B_COUNT);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT + kItemQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // exchange area of the softmax role: per tile, three slots of [half][row] floats, and one redo tag per row quadrant
+  float* xchg = reinterpret_cast<float*>(bars + 64);
+  volatile uint32_t* redo_tag = reinterpret_cast<volatile uint32_t*>(xchg + 2 * 3 * 2 * 128);
   auto bar = [&](int i) -> uint32_t { return smem_u32(bars + i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long n_items = (long long)p.n_rb * p.batch * p.n_hg;
 #ifdef FA_TC5_PROF
-  unsigned long long* prof_smem = reinterpret_cast<unsigned long long*>(bars + 64);
+  unsigned long long* prof_smem = reinterpret_cast<unsigned long long*>(xchg + 2 * 3 * 2 * 128 + 8);
   if (threadIdx.x < 5 * 16) prof_smem[threadIdx.x] = 0ull;
   bool prof_on = false;    // true in the one thread per role that keeps the counters
   const long long prof_start = clock64();
@@ -389,15 +396,18 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       mbar_init(bar(B_QFULL + t), 1);
       mbar_init(bar(B_QEMPTY + t), 1);
       mbar_init(bar(B_SFULL + t), 1);
-      mbar_init(bar(B_PLO + t), 128);
-      mbar_init(bar(B_PHI + t), 128);
+      mbar_init(bar(B_PFULL + t), 8);     // one arrival per softmax warp of the tile
       mbar_init(bar(B_TOKEN + t), 1);
+      mbar_init(bar(B_DRAIN + t), 1);
+      mbar_init(bar(B_TURN + t), 8);      // one arrival per softmax warp of the OTHER tile
     }
+    for (int i = 0; i < 8; ++i) mbar_init(bar(B_PAIR + i), 64);   // the two warps that share 32 query rows
     for (int i = 0; i < kItemQ; ++i) {
       mbar_init(bar(B_IFULL + i), 1);
       mbar_init(bar(B_IEMPTY + i), kItemConsumers);
     }
     *abort_flag = 0;
+    for (int i = 0; i < 8; ++i) redo_tag[i] = 0u;
     mbar_fence_init();
     fence_proxy_async();
     tma_prefetch_desc(&qmap);
@@ -430,20 +440,14 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       uint32_t q_used[2] = {0, 0};   // how often each Q buffer has been filled
       for (uint32_t ic = 0;; ++ic) {
         if (*abort_flag) break;
-        // claim the next non-empty item and publish it (-1: no more items)
-        Tc5Item it;
-        long long item;
-        bool have = false;
-        PROF_WAIT(0, 0, while (true) {
-          item = (long long)atomicAdd(p.item_counter, 1ULL);
-          if (item >= n_items) break;
-          if (tc5_decode_item(p, item, it)) { have = true; break; }
-        });
+        // next item from the queue that warp 2 fills (-1: no more items)
         const int slot = ic % kItemQ;
-        if (ic >= kItemQ) PROF_WAIT(0, 1, wait_or_abort(bar(B_IEMPTY + slot), ((ic / kItemQ) & 1u) ^ 1u, abort_flag));
-        item_slot[slot] = have ? item : -1;
-        mbar_arrive(bar(B_IFULL + slot));
-        if (!have) break;
+        PROF_WAIT(0, 0, wait_or_abort(bar(B_IFULL + slot), (ic / kItemQ) & 1u, abort_flag));
+        const long long item = item_slot[slot];
+        mbar_arrive(bar(B_IEMPTY + slot));
+        if (item < 0 || item >= n_items) break;
+        Tc5Item it;
+        tc5_decode_item(p, item, it);
         const int n_act = it.n_kv[1] > 0 ? 2 : 1;
         // Q buffers are free once the last QK of their previous item has completed
         for (int t = 0; t < n_act; ++t) {
@@ -472,6 +476,17 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
                         bar(B_VFULL + st));
         }
       }
+      // On the way out every copy issued above must have landed (on a regular exit they all have been
+      // consumed; after an abort some may still be in flight): the last fill of every stage and Q buffer.
+      for (int st = 0; st < KV_STAGES; ++st) {
+        if (kv_it > (uint32_t)st) {
+          const uint32_t last = kv_it - 1u - ((kv_it - 1u - (uint32_t)st) % KV_STAGES);   // last tile of this stage
+          drain_wait(bar(B_KFULL + st), (last / KV_STAGES) & 1u);
+          drain_wait(bar(B_VFULL + st), (last / KV_STAGES) & 1u);
+        }
+      }
+      for (int t = 0; t < 2; ++t)
+        if (q_used[t] > 0) drain_wait(bar(B_QFULL + t), (q_used[t] - 1u) & 1u);
     }
   } else if (warp == 1 || warp == 3) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
@@ -483,9 +498,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
     // overlap the other lane's MMAs.  K/V stages are released when BOTH lanes have committed
     // (a lane whose tile does not use a stage arrives on it directly).
     const int t = warp == 1 ? 0 : 1;
-    if (lane == 0) {
+    {
 #ifdef FA_TC5_PROF
-      prof_on = true;
+      prof_on = (lane == 0);
 #endif
       constexpr uint32_t TILE16 = TILE_BYTES >> 4;
       const uint64_t qd = smem_desc(sQ + (uint32_t)t * TILE_BYTES, 16, 1024);
@@ -494,6 +509,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       const uint32_t dS = tmem_base + (uint32_t)t * 128u;
       const uint32_t dO = tmem_base + O_COL0 + (uint32_t)t * D;
       auto issue_qk = [&](int st) {
+        __syncwarp();   // the lanes leave their barrier waits one by one; elect.sync needs them together
         const uint64_t b0 = kd0 + (uint64_t)((uint32_t)st * TILE16);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
@@ -502,12 +518,14 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           tc_mma_ss(dS, qd + off, b0 + off, IDESC_QK, ks > 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int st, uint32_t acc, int half) {
+      auto issue_pv = [&](int st, uint32_t acc) {
+        __syncwarp();
         const uint64_t b0 = vd0 + (uint64_t)((uint32_t)st * TILE16);
-        // first part: the keys whose P arrives with the first barrier (kPSplit chunks of 32 keys)
 #pragma unroll
-        for (int ks = half ? 2 * kPSplit : 0; ks < (half ? BN / 16 : 2 * kPSplit); ++ks) {
-          tc_mma_ts(dO, dS + P_COL + (uint32_t)ks * 8u, b0 + (uint32_t)ks * 128u, IDESC_PV, (acc | (ks > 0 ? 1u : 0u)));
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          // P quarter ks / 2 holds the keys of score chunk {0, 1, 3, 2}[ks / 2]: pick the matching rows of V
+          const int kv = ks < 4 ? ks : (ks ^ 2);
+          tc_mma_ts(dO, dS + P_COL + (uint32_t)ks * 8u, b0 + (uint32_t)kv * 128u, IDESC_PV, (acc | (ks > 0 ? 1u : 0u)));
         }
       };
       uint32_t kv_it = 0, q_cnt = 0, blk = 0, tok_waits = 0;
@@ -516,7 +534,8 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         const int slot = ic % kItemQ;
         PROF_WAIT(1 + t, 0, wait_or_abort(bar(B_IFULL + slot), (ic / kItemQ) & 1u, abort_flag));
         const long long item = item_slot[slot];
-        mbar_arrive(bar(B_IEMPTY + slot));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_IEMPTY + slot));
         if (item < 0 || item >= n_items) break;
         Tc5Item it;
         tc5_decode_item(p, item, it);
@@ -528,7 +547,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           ++tok_waits;
         };
         auto pass_token = [&]() {
-          if (other_active) mbar_arrive(bar(B_TOKEN + (t ^ 1)));
+          if (other_active && lane == 0) mbar_arrive(bar(B_TOKEN + (t ^ 1)));
         };
         if (n_mine > 0) {
           // block 0: S = Q K_0^T
@@ -553,18 +572,14 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             PROF_COUNT(1 + t, 14);
             PROF_WAIT(1 + t, 3, wait_or_abort(bar(B_VFULL + st), ph, abort_flag));
             if (more) PROF_WAIT(1 + t, 4, wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag));
-            PROF_WAIT(1 + t, 5, wait_or_abort(bar(B_PLO + t), blk & 1u, abort_flag));
-            PROF_SINCE(1 + t, 9, 2 + t);      // P_lo arrival (row 0) -> seen by the MMA lane
+            PROF_WAIT(1 + t, 5, wait_or_abort(bar(B_PFULL + t), blk & 1u, abort_flag));
+            PROF_SINCE(1 + t, 9, 2 + t);      // P arrival (row 0's warp) -> seen by the MMA lane
             // tile 1's block j+1 follows tile 0's block j+1; tile 0's block j+1 follows tile 1's
             // block j, which exists unless tile 1 has already run out of KV tiles
             if (t == 1 || j <= it.n_kv[1]) take_token();
-            tc_fence_after();
-            if (!(DBG & 2)) issue_pv(st, j > 0 ? 1u : 0u, 0);
-            PROF_WAIT(1 + t, 7, wait_or_abort(bar(B_PHI + t), blk & 1u, abort_flag));
-            PROF_SINCE(1 + t, 10, 4 + t);     // P_hi arrival (row 0) -> seen by the MMA lane
             PROF_MARK(prof_t_i);
             tc_fence_after();
-            if (!(DBG & 2)) issue_pv(st, 1u, 1);
+            if (!(DBG & 2)) issue_pv(st, j > 0 ? 1u : 0u);
             if (more && !(DBG & 4)) issue_qk(st1);
             pass_token();
             // ONE commit per batch (a tcgen05.commit costs the tensor pipe about as much as an MMA): the
@@ -596,52 +611,131 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           const int st = g % KV_STAGES;
           const uint32_t ph = (g / KV_STAGES) & 1u;
           PROF_WAIT(1 + t, 8, wait_or_abort(bar(B_KFULL + st), ph, abort_flag));
-          mbar_arrive(bar(B_KEMPTY + st));
+          if (lane == 0) mbar_arrive(bar(B_KEMPTY + st));
           PROF_WAIT(1 + t, 8, wait_or_abort(bar(B_VFULL + st), ph, abort_flag));
-          mbar_arrive(bar(B_VEMPTY + st));
+          if (lane == 0) mbar_arrive(bar(B_VEMPTY + st));
         }
         kv_it += (uint32_t)it.n_max;
       }
+      // every MMA of this lane must be complete before tensor memory is released
+      tc_commit(bar(B_DRAIN + t));
+      drain_wait(bar(B_DRAIN + t), 0u);
     }
   } else if (warp == 2) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    // ============================ item claimer ======================================
+    // Claims work items from the global counter, skips the empty ones (row blocks past the end of a
+    // sequence) and publishes the others through the item queue, up to kItemQ items ahead of the slowest
+    // role: the latency of the global atomic stays off every other role's path.
+    if (lane == 0) {
+      for (uint32_t ic = 0;; ++ic) {
+        if (*abort_flag) break;
+        Tc5Item it;
+        long long item;
+        bool have = false;
+        while (true) {
+          item = (long long)atomicAdd(p.item_counter, 1ULL);
+          if (item >= n_items) break;
+          if (tc5_decode_item(p, item, it)) { have = true; break; }
+        }
+        const int slot = ic % kItemQ;
+        if (ic >= kItemQ) wait_or_abort(bar(B_IEMPTY + slot), ((ic / kItemQ) & 1u) ^ 1u, abort_flag);
+        item_slot[slot] = have ? item : -1;
+        mbar_arrive(bar(B_IFULL + slot));
+        if (!have) break;
+      }
+    }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     // ============================ softmax groups ====================================
-    // Thread = one query row.  State per row: a reference exponent m (any finite number works as long as
-    // P = exp2(s * scale - m) stays inside the fp16 range), the row sum l relative to m, and O in tensor
-    // memory, also relative to m.
-    //   full path (first KV tile of an item, tiles that need masking, rows that left the window below):
-    //     row maximum first, m raised when the maximum grows by more than 2^8 with O rescaled in tensor
-    //     memory, then the exponentials.
-    //   fast path (SM 1, other tiles): no dependent chain in front of the exponentials.  The first part of P
-    //     is exponentiated against the m carried over from the previous step while the raw maximum of the
-    //     second part is formed in the same instruction stream; the step goes ahead if the first part's sum
-    //     shows that nothing exceeded 2^15 and the second part's maximum stays below m + 15 (so P fits fp16);
-    //     otherwise nothing has been handed over yet and the step is redone on the full path.
-    // The group also forwards what a completed MMA batch implies: the batch barrier B_SFULL of step j says
-    // that PV(j-1) and QK(j) are done, so V stage j-1 and K stage j (and, after the last QK, the Q buffer) are
-    // free; the thread of row 0 arrives on the copy lane's barriers for them.
-    const int t = (warp - 4) >> 2;
+    // Sixteen warps: two per (query tile, row quadrant).  TWO threads share a query row: thread h of the pair
+    // handles chunk h (32 columns) of the first part of the row and chunk 2 + h of the second part, half of the
+    // O columns in every rescale and in the epilogue, and keeps the sum of its own columns.  Two warps per
+    // scheduler and tile hide each other's tensor-memory round trips and MUFU latency; the row state that
+    // must agree between the two threads (the reference exponent m) changes only on paths where they meet
+    // at a 64-thread named barrier.
+    // State per row: m (any finite number works as long as P = exp2(s * scale - m) stays inside the fp16
+    // range), the partial row sums relative to m, and O in tensor memory, also relative to m.
+    //   full path (first KV tile of an item, tiles that need masking, rows that left the window below): the
+    //     two halves exchange their maxima through shared memory, m is raised when the row maximum grows by
+    //     more than 2^8 with O rescaled in tensor memory, then the exponentials.
+    //   fast path (SM 1, other tiles): no dependent chain in front of the exponentials.  The first-part chunk is
+    //     exponentiated against the m carried over from the previous step while the raw maximum of the
+    //     second-part chunk is formed in the same instruction stream; the step goes ahead if the first part's
+    //     sum shows that nothing exceeded 2^15 and the second part's maximum stays below m + 15 (so P fits
+    //     fp16) in BOTH warps of the pair (a tag in shared memory and the named barrier); otherwise nothing
+    //     has been handed over yet and the step is redone on the full path.
+    const int t = (warp - 4) >> 3;
+    const int h = ((warp - 4) >> 2) & 1;       // which thread of the row pair
     const int wq = warp & 3;                   // TMEM lane quadrant of this warp
     const int row = wq * 32 + lane;            // row within the tile == TMEM lane
     const uint32_t lane_base = tmem_base + ((uint32_t)(wq * 32) << 16);
     const uint32_t tS = lane_base + (uint32_t)t * 128u;
     const uint32_t tP = tS + P_COL;
-    const uint32_t tO = lane_base + O_COL0 + (uint32_t)t * D;
+    const uint32_t tO = lane_base + O_COL0 + (uint32_t)t * D + (uint32_t)h * (D / 2);
+    const int c_lo = h, c_hi = 2 + h;          // my 32-column chunks of the score row
+    const int q_lo = h, q_hi = 3 - h;          // the quarters of P that their exponentials go to
+    const uint32_t pair_bar = bar(B_PAIR + t * 4 + wq);
+    uint32_t pair_ph = 0;    // completed phases of the pair barrier
+    float* xch = xchg + t * (3 * 2 * 128);     // [slot][half][row]
+    volatile uint32_t* my_tag = redo_tag + t * 4 + wq;
+    // meeting point of the two warps of a row pair (orders their shared-memory exchange); a bounded wait like
+    // every other wait of this kernel
+    auto pair_sync = [&]() {
+      mbar_arrive(pair_bar);
+      wait_or_abort(pair_bar, pair_ph & 1u, abort_flag);
+      ++pair_ph;
+    };
+    // hand-over of a finished P tile to the MMA lane: one arrival per warp
+    auto hand_over = [&]() {
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_PFULL + t));
+    };
 #ifdef FA_TC5_PROF
-    prof_on = (row == 0);
+    prof_on = (h == 0 && row == 0);
 #endif
+    // The exponentials of the two tiles take turns (tile 0, tile 1, tile 0, ...).  Both tiles share the four
+    // MUFU pipes: when their softmax phases coincide each takes twice as long and the MMAs of both tiles end
+    // up back to back as well, and nothing pulls such a lock-step apart again.  Taking turns makes the
+    // half-period offset between the tiles (one tile's softmax under the other tile's MMAs) the stable
+    // state.  Only when both tiles walk the same KV steps (head-pair mode).
+    const bool take_turns = !(DBG & 32) && p.pair_heads != 0;
+    auto turn_wait = [&](const uint32_t step) {
+      if (!take_turns) return;
+      if (t == 0) { if (step > 0) wait_or_abort(bar(B_TURN + 0), (step - 1u) & 1u, abort_flag); }
+      else wait_or_abort(bar(B_TURN + 1), step & 1u, abort_flag);
+    };
+    auto turn_pass = [&]() {
+      if (!take_turns) return;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_TURN + (t ^ 1)));
+    };
     const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
     uint32_t sph = 0;        // completed phases of B_SFULL[t] that this thread has consumed
-    uint32_t pph = 0;        // KV steps of this tile so far: phase of B_PLO / B_PHI
+    uint32_t pph = 0;        // KV steps of this tile so far: tags of the redo vote, slots of the exchange
     uint32_t kv_it = 0;      // KV tiles of all items so far: ring stage of K / V
+    // What a completed MMA batch implies is passed on to the copy lane by this role, as soon as the batch
+    // barrier is seen (the copies that refill the stages have a latency of more than half a KV step, so an
+    // early release matters): the barrier seen at the start of step j says that QK(j) and PV(j-1) are done,
+    // so K stage j and V stage j-1 (and, after the last QK, the Q buffer) are free.  The three arrivals are
+    // made by lane 0 of three different warps, one instruction each.  (A thread that takes part in every
+    // step can never fall behind the barrier's phases; a separate forwarding thread could, by two phases,
+    // and a parity wait cannot tell that apart from "not yet".)
+    const int fwd = (h == 0 && lane == 0) ? wq : -1;   // 0: K stage, 1: V stage, 2: Q buffer
+    auto forward_step = [&](const uint32_t kv0, const int j, const int n_mine) {
+      if (fwd == 0) mbar_arrive(bar(B_KEMPTY + (int)((kv0 + (uint32_t)j) % KV_STAGES)));
+      if (fwd == 1 && j > 0) mbar_arrive(bar(B_VEMPTY + (int)((kv0 + (uint32_t)j - 1u) % KV_STAGES)));
+      if (fwd == 2 && j == n_mine - 1) mbar_arrive(bar(B_QEMPTY + t));
+    };
     for (uint32_t ic = 0;; ++ic) {
       if (*abort_flag) break;
       const int slot = ic % kItemQ;
       PROF_WAIT(3 + t, 0, wait_or_abort(bar(B_IFULL + slot), (ic / kItemQ) & 1u, abort_flag));
       const long long item = item_slot[slot];
-      mbar_arrive(bar(B_IEMPTY + slot));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_IEMPTY + slot));
       if (item < 0 || item >= n_items) break;
       Tc5Item it;
       tc5_decode_item(p, item, it);
@@ -659,81 +753,78 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         if (j > 0) PROF_SINCE(3 + t, 8, t);   // commit issued by the MMA lane -> batch seen complete here
         PROF_MARK(prof_t_s);
         tc_fence_after();
-        if (row == 0) {
-          // QK(j) is complete: K stage j is free; so is PV(j-1): V stage j-1
-          mbar_arrive(bar(B_KEMPTY + (int)((kv0 + (uint32_t)j) % KV_STAGES)));
-          if (j > 0) mbar_arrive(bar(B_VEMPTY + (int)((kv0 + (uint32_t)j - 1u) % KV_STAGES)));
-          if (j == n_mine - 1) mbar_arrive(bar(B_QEMPTY + t));   // that was the last QK of this item
-        }
+        forward_step(kv0, j, n_mine);
         const int k0 = j * BN;
         const bool need_mask = (k0 + BN > len) || (p.causal && (k0 + BN - 1 > it.row0[t]));
-        // ---- the whole score row of this thread: 128 fp32 values, one round trip ----
-        float sv[4][32];
-        tc_ld32(tS, sv[0]);
-        tc_ld32(tS + 32, sv[1]);
-        tc_ld32(tS + 64, sv[2]);
-        tc_ld32(tS + 96, sv[3]);
-        tc_wait_ld();
-        float2 rs2[4];
+        // ---- my half of the score row: chunk c_lo (kept in registers) and chunk c_hi (read for its maximum,
+        // read again when its turn comes).  Where P is written: thread 0 of the pair writes quarter 0 over
+        // columns 16-31 (its own chunk 0, in registers) and later quarter 3 over columns 64-79 (its own chunk 2,
+        // after its second read); thread 1 writes quarter 1 over columns 32-47 and later quarter 2 over
+        // columns 48-63 (both its own chunk 1, in registers).  Chunk 3 is never overwritten.
+        float sv[32], sw[32];
+        float2 rs_lo = make_float2(0.f, 0.f), rs_hi = make_float2(0.f, 0.f);
         if (DBG & 16) {
-          tc_fence_before();
+          tc_ld32(tS + c_lo * 32, sv);
+          tc_ld32(tS + c_hi * 32, sw);
+          tc_wait_ld();
+          turn_wait(pph);
+          turn_pass();
           PROF_STAMP(2 + t);
-          mbar_arrive(bar(B_PLO + t));
-          PROF_STAMP(4 + t);
-          mbar_arrive(bar(B_PHI + t));
+          hand_over();
           continue;
         }
         bool full_path = SM == 0 || need_mask || j == 0;
+        bool lo_loaded = false;
         if (SM == 1 && !full_path) {
-          float mx2 = -INFINITY;
+          PROF_MARK(pf0);
+          tc_ld32(tS + c_hi * 32, sw);
+          tc_wait_ld();
+          PROF_MARK(pf1);
+          float a0 = fmaxf(sw[0], sw[1]), a1 = fmaxf(sw[2], sw[3]);
 #pragma unroll
-          for (int c = kPSplit; c < 4; ++c) {
-            float a0 = fmaxf(sv[c][0], sv[c][1]), a1 = fmaxf(sv[c][2], sv[c][3]);
-#pragma unroll
-            for (int i = 4; i < 32; i += 4) {
-              a0 = fmax3(a0, sv[c][i], sv[c][i + 1]);
-              a1 = fmax3(a1, sv[c][i + 2], sv[c][i + 3]);
-            }
-            mx2 = fmax3(mx2, a0, a1);
+          for (int i = 4; i < 32; i += 4) {
+            a0 = fmax3(a0, sw[i], sw[i + 1]);
+            a1 = fmax3(a1, sw[i + 2], sw[i + 3]);
           }
+          tc_ld32(tS + c_lo * 32, sv);      // (one chunk in registers at a time: 104 registers per thread)
+          tc_wait_ld();
+          PROF_MARK(pf2);
+          lo_loaded = true;
+          turn_wait(pph);
           const float2 nm2 = make_float2(-m, -m);
-#pragma unroll
-          for (int c = 0; c < kPSplit; ++c) {
-            rs2[c] = make_float2(0.f, 0.f);
-            exp_chunk_store<NPOLY, DBG>(sv[c], sc2, nm2, rs2[c], tP + c * 16);
-          }
-          float part = 0.f;
-#pragma unroll
-          for (int c = 0; c < kPSplit; ++c) part += rs2[c].x + rs2[c].y;
-          const bool inside = (part <= 32768.f) && (mx2 * p.scale_log2 <= m + 15.f);   // false for NaN
-          if (__any_sync(0xffffffffu, !inside)) {
-            // nothing has been handed over yet: the step is redone below.  The first half of S is still
-            // intact in tensor memory (P lies over the second half, which the registers hold)
-            full_path = true;
-            tc_ld32(tS, sv[0]);
-            tc_ld32(tS + 32, sv[1]);
+          exp_chunk_store<NPOLY, DBG>(sv, sc2, nm2, rs_lo, tP + q_lo * 16);
+          const bool inside = (rs_lo.x + rs_lo.y <= 32768.f) && (fmaxf(a0, a1) * p.scale_log2 <= m + 15.f);   // false for NaN
+          const uint32_t tag = pph + 1u;
+          if (__any_sync(0xffffffffu, !inside) && lane == 0) *my_tag = tag;
+          PROF_MARK(pf3);
+          tc_ld32(tS + c_hi * 32, sw);        // chunk c_hi again: in flight across the pair barrier
+          pair_sync();
+          PROF_MARK(pf4);
+          if (*my_tag == tag) {
+            // nothing has been handed over yet: the step is redone below (chunk c_lo is still in registers)
             tc_wait_ld();
+            full_path = true;
+            rs_lo = make_float2(0.f, 0.f);
           } else {
-            tc_wait_st();
-            tc_fence_before();
+            tc_wait_ld();
+            PROF_MARK(pf6);
+            exp_chunk_store<NPOLY, DBG>(sw, sc2, nm2, rs_hi, tP + q_hi * 16);
+            turn_pass();
+            PROF_MARK(pf7);
             PROF_STAMP(2 + t);
-            mbar_arrive(bar(B_PLO + t));
-#pragma unroll
-            for (int c = kPSplit; c < 4; ++c) {
-              rs2[c] = make_float2(0.f, 0.f);
-              exp_chunk_store<NPOLY, DBG>(sv[c], sc2, nm2, rs2[c], tP + c * 16);
-            }
-            tc_wait_st();
-            tc_fence_before();
-            PROF_STAMP(4 + t);
-            mbar_arrive(bar(B_PHI + t));
-#pragma unroll
-            for (int c = kPSplit; c < 4; ++c) part += rs2[c].x + rs2[c].y;
-            l += part;
+            hand_over();
+            PROF_MARK(pf8);
+            PROF_SPAN(3 + t, 9, pf0, pf1);    // first tensor-memory read
+            PROF_SPAN(3 + t, 10, pf1, pf2);   // maximum + second read
+            PROF_SPAN(3 + t, 11, pf2, pf3);   // first exponentials + vote
+            PROF_SPAN(3 + t, 12, pf3, pf4);   // pair barrier
+            PROF_SPAN(3 + t, 2, pf4, pf6);    // third read
+            PROF_SPAN(3 + t, 7, pf6, pf7);    // second exponentials
+            PROF_SPAN(3 + t, 6, pf7, pf8);    // wait for the P stores, hand over
+            l += (rs_lo.x + rs_lo.y) + (rs_hi.x + rs_hi.y);
           }
         }
         if (full_path) {
-          PROF_COUNT(3 + t, 6);
           // keys of this tile that the row may attend: [k0, k0 + lim); chunks past the warp's largest
           // lim are stored as zeros without any exponentials (upper part of a causal diagonal tile)
           int lim = BN;
@@ -744,94 +835,150 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           }
           const int lim_max = need_mask ? __reduce_max_sync(0xffffffffu, lim) : BN;
           const int lim_min = need_mask ? __reduce_min_sync(0xffffffffu, lim) : BN;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          auto mask_chunk = [&](float (&v)[32], const int c) {
             if (c * 32 + 32 > lim_min) {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                if (c * 32 + i >= lim) sv[c][i] = -INFINITY;
+                if (c * 32 + i >= lim) v[i] = -INFINITY;
             }
+          };
+          auto max_chunk = [&](const float (&v)[32]) {
+            float a0 = fmaxf(v[0], v[1]), a1 = fmaxf(v[2], v[3]);
+#pragma unroll
+            for (int i = 4; i < 32; i += 4) {
+              a0 = fmax3(a0, v[i], v[i + 1]);
+              a1 = fmax3(a1, v[i + 2], v[i + 3]);
+            }
+            return fmaxf(a0, a1);
+          };
+          tc_ld32(tS + c_hi * 32, sw);
+          tc_wait_ld();
+          mask_chunk(sw, c_hi);
+          const float mx_hi = max_chunk(sw);
+          if (!lo_loaded) {
+            tc_ld32(tS + c_lo * 32, sv);
+            tc_wait_ld();
           }
-          const float mxs = row_max128(sv) * p.scale_log2;
+          mask_chunk(sv, c_lo);
+          const float mxl = fmaxf(mx_hi, max_chunk(sv));
+          // the other half of the row lives in the partner warp
+          float* slot_f = xch + (int)(pph & 1u) * (2 * 128);
+          slot_f[h * 128 + row] = mxl;
+          pair_sync();
+          const float mxs = fmaxf(mxl, slot_f[(h ^ 1) * 128 + row]) * p.scale_log2;
           const float m_new = (j == 0) ? mxs : fmaxf(m, mxs);
           const bool grow_big = (j == 0) || (m_new > m + 8.f);
           const float alpha = (j > 0 && grow_big) ? fast_exp2(m - m_new) : 1.f;
           if (j > 0 && __any_sync(0xffffffffu, grow_big)) {
-            // O_t holds the result of PV(t, j-1): the batch barrier waited for above covers it
+            // O_t holds the result of PV(t, j-1): the batch barrier waited for above covers it.  My half.
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
-              float o[32];
-              tc_ld32(tO + c * 32, o);
+              float o[16];
+              tc_ld16(tO + c * 16, o);
               tc_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] *= alpha;
-              tc_st32(tO + c * 32, o);
+              for (int i = 0; i < 16; ++i) o[i] *= alpha;
+              tc_st16(tO + c * 16, reinterpret_cast<const uint32_t(&)[16]>(o));
             }
-            tc_wait_st();
           }
           if (grow_big) m = m_new;
           l *= alpha;
-          // ---- P = exp2(S * scale - m), fp16, written over the last 64 columns of S ----
+          // ---- P = exp2(S * scale - m), fp16 ----
           const float neg_m = (m == -INFINITY) ? 0.f : -m;
           const float2 nm2 = make_float2(neg_m, neg_m);
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            rs2[c] = make_float2(0.f, 0.f);
-            if (c * 32 < lim_max) exp_chunk_store<NPOLY, DBG>(sv[c], sc2, nm2, rs2[c], tP + c * 16);
-            else zero_chunk_store(tP + c * 16);
-            if (c == kPSplit - 1 || c == 3) {
-              // the first kPSplit chunks / the rest of P are in tensor memory: let the PV MMA start on them
-              tc_wait_st();
-              tc_fence_before();
-              PROF_STAMP((c == 3 ? 4 : 2) + t);
-              mbar_arrive(bar((c == 3 ? B_PHI : B_PLO) + t));
-            }
-          }
-          l += (rs2[0].x + rs2[0].y) + (rs2[1].x + rs2[1].y) + (rs2[2].x + rs2[2].y) + (rs2[3].x + rs2[3].y);
+          if (!lo_loaded) turn_wait(pph);     // (a redone step has taken its turn already)
+          if (c_lo * 32 < lim_max) exp_chunk_store<NPOLY, DBG>(sv, sc2, nm2, rs_lo, tP + q_lo * 16);
+          else zero_chunk_store(tP + q_lo * 16);
+          tc_ld32(tS + c_hi * 32, sw);        // chunk c_hi again (its columns are written by nobody but me)
+          tc_wait_ld();
+          mask_chunk(sw, c_hi);
+          if (c_hi * 32 < lim_max) exp_chunk_store<NPOLY, DBG>(sw, sc2, nm2, rs_hi, tP + q_hi * 16);
+          else zero_chunk_store(tP + q_hi * 16);
+          turn_pass();
+          PROF_STAMP(2 + t);
+          hand_over();                        // waits for the O rescale stores as well
+          l += (rs_lo.x + rs_lo.y) + (rs_hi.x + rs_hi.y);
         }
         PROF_MARK(prof_t_e);
         PROF_SPAN(3 + t, 4, prof_t_s, prof_t_e);
       }
-      // ---- epilogue: O / l -> fp16 -> global.  The batch barrier of the last step covers PV(n-1).  The
-      // next item's first PV of this tile cannot be issued before these threads have produced its P, i.e.
-      // after these loads have completed.
+      // ---- epilogue: O / l -> fp16 -> global, my half of the columns.  The batch barrier of the last step
+      // covers PV(n-1).  The next item's first PV of this tile cannot be issued before these threads have
+      // produced its P, i.e. after these loads have completed.
       PROF_WAIT(3 + t, 3, wait_or_abort(bar(B_SFULL + t), sph & 1u, abort_flag));
       ++sph;
       PROF_MARK(prof_t_o);
       tc_fence_after();
-      if (row == 0) mbar_arrive(bar(B_VEMPTY + (int)((kv0 + (uint32_t)n_mine - 1u) % KV_STAGES)));
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __half* orow;
-      if (p.dense) orow = p.out + (long long)it.seq * p.o_batch_stride + (long long)it.head[t] * p.o_head_stride +
-                          (long long)grow * p.o_tok_stride;
-      else orow = p.out + (it.tok0 + grow) * p.o_tok_stride + (long long)it.head[t] * p.o_head_stride;
+      if (fwd == 1) mbar_arrive(bar(B_VEMPTY + (int)((kv0 + (uint32_t)n_mine - 1u) % KV_STAGES)));
+      float* slot_l = xch + 2 * (2 * 128);     // a slot of its own: the steps' slots may be rewritten at once
+      slot_l[h * 128 + row] = l;
+      pair_sync();
+      PROF_MARK(pe1);
+      const float l_row = l + slot_l[(h ^ 1) * 128 + row];
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+      // My half of the row, scaled and packed: NU units of 16 bytes (8 columns each).
+      constexpr int NU = D / 16;
+      uint32_t u[NU][4];
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
-        float o[32];
-        tc_ld32(tO + c * 32, o);
+        float o[16];
+        tc_ld16(tO + c * 16, o);
         tc_wait_ld();
-        if (grow < len) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = pack_half2(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
-            w.y = pack_half2(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-            w.z = pack_half2(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
-            w.w = pack_half2(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
-            if (c * 32 + i * 8 < p.D_real) *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
+        for (int i = 0; i < 8; ++i) u[2 * c + (i >> 2)][i & 3] = pack_half2(o[2 * i] * inv, o[2 * i + 1] * inv);
+      }
+      // A thread-per-row store would touch 32 different 128-byte lines per instruction (the rows of a warp lie
+      // a whole row apart in memory), and the load/store unit handles one line per cycle.  Transpose the
+      // units within groups of NU lanes instead (lane i of a group ends up with unit i of every row of the
+      // group), so that NU consecutive lanes write NU * 16 contiguous bytes of one row.
+      PROF_MARK(pe2);
+      const int gi = lane & (NU - 1);
+#pragma unroll
+      for (int sft = NU / 2; sft >= 1; sft >>= 1) {
+#pragma unroll
+        for (int k = 0; k < NU; ++k) {
+          if (k & sft) continue;
+          const bool up = (gi & sft) != 0;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const uint32_t send = up ? u[k][w] : u[k | sft][w];
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, send, sft);
+            if (up) u[k][w] = got; else u[k | sft][w] = got;
           }
         }
       }
+      // u[k] now holds unit gi of the row (lane - gi + k) of this warp's quadrant
+      PROF_MARK(pe3);
+      const int row_g = wq * 32 + (lane - gi);            // first row of my lane group within the tile
+      const int col = h * (D / 2) + gi * 8;               // first column of the unit I store
+      __half* obase;
+      if (p.dense) obase = p.out + (long long)it.seq * p.o_batch_stride + (long long)it.head[t] * p.o_head_stride;
+      else obase = p.out + it.tok0 * p.o_tok_stride + (long long)it.head[t] * p.o_head_stride;
+#pragma unroll
+      for (int k = 0; k < NU; ++k) {
+        const int r = it.row0[t] + row_g + k;             // row within the sequence
+        if (r < len && col < p.D_real)
+          *reinterpret_cast<uint4*>(obase + (long long)r * p.o_tok_stride + col) = make_uint4(u[k][0], u[k][1], u[k][2], u[k][3]);
+      }
       tc_fence_before();
+      // the partner must have read my row sum before the next epilogue overwrites the slot: it did so right
+      // behind the barrier above, and the next epilogue lies at least one KV step (with barriers that both
+      // warps take part in) ahead
       PROF_MARK(prof_t_x);
       PROF_SPAN(3 + t, 5, prof_t_o, prof_t_x);
+      if (t == 0) {   // epilogue pieces, kept in unused slots of the copy lane's row of counters
+        PROF_SPAN(0, 5, prof_t_o, pe1);     // pair barrier
+        PROF_SPAN(0, 6, pe1, pe2);          // tensor-memory reads, scaling, packing
+        PROF_SPAN(0, 7, pe2, pe3);          // transpose
+        PROF_SPAN(0, 8, pe3, prof_t_x);     // stores
+      }
     }
   }
 
   // ---- tear-down ------------------------------------------------------------------
 #ifdef FA_TC5_PROF
   if (prof_on) {
-    const int role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 3 ? 2 : 3 + ((warp - 4) >> 2);
+    const int role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 3 ? 2 : 3 + ((warp - 4) >> 3);
     prof_smem[role * 16 + 15] += (unsigned long long)(clock64() - prof_start);
   }
 #endif
@@ -841,6 +988,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   if (threadIdx.x < 5 * 16) atomicAdd(&g_tc5_prof[threadIdx.x], prof_smem[threadIdx.x]);
 #endif
   if (warp == 2) {
+    __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
@@ -901,16 +1049,18 @@ int g_tc5_variant = 0;
 template <int D>
 Tc5Kernel sweep_kernel(int v) {
   switch (v) {
-    case 1: return prefill_tc5_kernel<D, 0, 2, 1>;
-    case 2: return prefill_tc5_kernel<D, 0, 2, 1, 1>;         // no exp2
-    case 3: return prefill_tc5_kernel<D, 0, 1, 1>;
-    case 4: return prefill_tc5_kernel<D, 0, 2, 1, 16>;        // no softmax at all
-    case 5: return prefill_tc5_kernel<D, 0, 2, 1, 16 | 2>;    // no softmax, QK only
-    case 6: return prefill_tc5_kernel<D, 0, 2, 1, 16 | 4>;    // no softmax, PV only
-    case 7: return prefill_tc5_kernel<D, 0, 3, 1>;
-    case 8: return prefill_tc5_kernel<D, 2, 2, 1>;
-    case 9: return prefill_tc5_kernel<D, 4, 2, 1>;
-    default: return prefill_tc5_kernel<D, 0, 2, 0>;
+    case 1: return prefill_tc5_kernel<D, 0, 1>;
+    case 2: return prefill_tc5_kernel<D, 0, 1, 1>;         // no exp2
+    case 4: return prefill_tc5_kernel<D, 0, 1, 16>;        // no softmax at all
+    case 5: return prefill_tc5_kernel<D, 0, 1, 16 | 2>;    // no softmax, QK only
+    case 6: return prefill_tc5_kernel<D, 0, 1, 16 | 4>;    // no softmax, PV only
+    case 8: return prefill_tc5_kernel<D, 2, 1>;
+    case 9: return prefill_tc5_kernel<D, 4, 1>;
+    case 10: return prefill_tc5_kernel<D, 3, 1>;
+    case 12: return prefill_tc5_kernel<D, 0, 1, 32>;       // no turn taking between the tiles
+    case 13: return prefill_tc5_kernel<D, 2, 1, 32>;
+    case 11: return prefill_tc5_kernel<D, 1, 1>;
+    default: return prefill_tc5_kernel<D, 0, 0>;
   }
 }
 #endif
@@ -920,7 +1070,7 @@ Tc5Kernel pick_kernel() {
 #ifdef FA_TC5_SWEEP
   return sweep_kernel<D>(g_tc5_variant);
 #else
-  return g_tc5_poly ? prefill_tc5_kernel<D, 2, 2, 1> : prefill_tc5_kernel<D, 0, 2, 1>;
+  return g_tc5_poly ? prefill_tc5_kernel<D, 2, 1> : prefill_tc5_kernel<D, 0, 1>;
 #endif
 }
 
@@ -955,7 +1105,8 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   p.scale_log2 = pp.scale_log2;
   constexpr int KV_STAGES = (D == 128) ? 2 : 4;
   constexpr size_t TILE = (size_t)(D / 64) * 128 * 128;
-  size_t smem = 1024 + (2 + 2 * KV_STAGES) * TILE + 64 * 8 + 16;  // tiles + barriers, item queue, flags
+  // tiles + barriers, item queue, flags + the softmax role's exchange area
+  size_t smem = 1024 + (2 + 2 * KV_STAGES) * TILE + 64 * 8 + 2 * 3 * 2 * 128 * 4 + 8 * 4;
 #ifdef FA_TC5_PROF
   smem += (5 * 16 + 8) * 8;
 #endif
@@ -973,7 +1124,7 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   grid = dim3((unsigned)(n_items < sms ? n_items : sms));
   e = next_item_counter(&p.item_counter, stream);
   if (e != cudaSuccess) return e;
-  kern<<<grid, 384, smem, stream>>>(qmap, kmap, vmap, p);
+  kern<<<grid, 640, smem, stream>>>(qmap, kmap, vmap, p);
   return cudaGetLastError();
 }
 
