@@ -41,6 +41,7 @@ SIGNATURES = {
     "fa_peer_allreduce_sum_bf16": (_i, [_c.POINTER(_vp), _c.POINTER(_vp), _vp, _i, _i, _i64, _i64, _vp]),
     "fa_peer_allgather": (_i, [_c.POINTER(_vp), _c.POINTER(_vp), _vp, _i, _i, _vp, _i64, _i64, _vp]),
     "fa_peer_status": (_i, [_vp, _vp, _c.POINTER(_i)]),
+    "fa_peer_reset": (_i, [_vp, _vp, _vp]),
     "fa_peer_set_max_polls": (_i, [_c.c_uint]),
     "fa_prefill_set_impl": (_i, [_i]),
     "fa_prefill_status": (_i, [_vp, _c.POINTER(_i), _i]),

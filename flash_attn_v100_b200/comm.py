@@ -117,6 +117,16 @@ class PeerCollectives:
         with torch.cuda.device(self.device):
             _lib.check(self.lib.fa_peer_status(self._state, self._stream(), ctypes.byref(st)))
 
+    def reset(self) -> None:
+        """Recover after a collective gave up waiting (`check()` raised): every rank clears its flags,
+        epoch and status between two host barriers.  All ranks must call it, with no collective in flight."""
+        import torch.distributed as dist
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)          # nobody launches a collective any more
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.fa_peer_reset(ctypes.c_void_p(self._own[1]), self._state, self._stream()))
+        dist.barrier(group=self.group)          # every rank's flags are clean before anyone stamps them again
+
     def close(self) -> None:
         """Unmap the other ranks' buffers and free this rank's (all ranks, after a barrier)."""
         import torch.distributed as dist

@@ -789,6 +789,15 @@ int fa_peer_allgather(void* const* data_ptrs, void* const* flag_ptrs, void* stat
   return FA_OK;
 }
 
+int fa_peer_reset(void* flags, void* state, void* stream) {
+  FA_REQUIRE(flags && state, "null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  FA_CUDA(cudaMemsetAsync(flags, 0, fa::kPeerFlagBytes, s));
+  FA_CUDA(cudaMemsetAsync(state, 0, 256, s));
+  FA_CUDA(cudaStreamSynchronize(s));
+  return FA_OK;
+}
+
 int fa_peer_set_max_polls(unsigned int max_polls) {
   FA_REQUIRE(max_polls > 0, "max_polls must be positive");
   g_peer_max_polls = max_polls;

@@ -50,8 +50,24 @@ class GenerationRunner:
         B, P = prompts.shape
         assert B <= self.max_batch and P + max_new_tokens <= self.max_seq_len
         ids = [f"r{i}" for i in range(B)]
-        for r in ids:
-            kv.allocate(r, P + max_new_tokens)          # blocks for the whole generation: the table is static
+        allocated = []
+        try:
+            rows = []
+            for r in ids:
+                rows.append(kv.allocate(r, P + max_new_tokens))   # blocks for the whole generation: the table is static
+                allocated.append(r)
+            # the captured decode graphs address rows 0..B-1 of the resident table: anything else (another user
+            # of the cache holding rows, rows leaked by an earlier failure) must not go unnoticed
+            if rows != list(range(B)):
+                raise RuntimeError(f"generate() needs table rows 0..{B - 1} of the KV cache, got {rows}")
+            return self._generate(prompts, max_new_tokens, prefill_chunk, logits_out, ids)
+        finally:
+            for r in reversed(allocated):       # rows and blocks return in the order the next call takes them
+                kv.release(r)
+
+    def _generate(self, prompts, max_new_tokens, prefill_chunk, logits_out, ids):
+        m, kv, dev = self.model, self.kv, self.model.device
+        B, P = prompts.shape
         table = kv.block_table[:B]
         out = torch.empty((B, max_new_tokens), dtype=torch.int64, device=dev)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
@@ -159,9 +175,16 @@ class GenerationRunner:
         torch.cuda.current_stream(dev).wait_stream(side)
         ev[2].record()
         self._events = ev
-        for r in reversed(ids):         # rows and blocks return in the order the next call takes them
+        for r in ids:
             kv.commit(r, max_new_tokens - 1)
-            kv.release(r)
+        # device-side conditions recorded by the kernels of this call (a block-table entry outside the pool, a
+        # bounded wait that ran out, a collective that gave up on a rank) surface here, not as wrong tokens
+        from .. import ops
+        torch.cuda.synchronize(dev)
+        ops.check_async_errors(dev)
+        ops.check_prefill_errors(dev)
+        if m.comm is not None:
+            m.comm.check()
         return out
 
     def close(self):

@@ -553,7 +553,8 @@ def rope_append_paged_fp16(q, k, v, cos, sin, k_cache, v_cache, block_table, pos
         _chk(positions is not None, "positions is required for a decode step")
     R = cos.shape[-1]
     _chk(cos.numel() == T * R and sin.shape == cos.shape, "cos and sin must hold one row of rot_dim values per token")
-    _same_device(q, k, "q", "k"); _same_device(q, cos, "q", "cos")
+    _same_device(q, k, "q", "k"); _same_device(q, v, "q", "v")
+    _same_device(q, cos, "q", "cos"); _same_device(q, sin, "q", "sin")
     has_cache = k_cache is not None
     _chk((k_cache is None) == (v_cache is None), "k_cache and v_cache must be given together")
     if has_cache:
@@ -565,6 +566,11 @@ def rope_append_paged_fp16(q, k, v, cos, sin, k_cache, v_cache, block_table, pos
              k_cache.size(2) == PAGE_BLOCK_SIZE and k_cache.size(3) == D, "cache must be [pages, H_KV, 16, D]")
         _chk(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.size(0) >= batch,
              "block_table must be int32 [batch, *]")
+        # the kernel reads block_table[seq * stride + blk] for blk < stride: every such entry must exist
+        max_num_blocks = int(max_num_blocks)
+        _chk(max_num_blocks > 0, "max_num_blocks must be positive")
+        _chk(batch * max_num_blocks <= block_table.numel(),
+             "max_num_blocks (row stride) is larger than block_table allows")
     if positions is not None:
         _check_input(positions, "positions")
         _chk(positions.dtype == torch.int32 and positions.numel() == batch, "positions must be int32 [batch]")

@@ -11,10 +11,13 @@
  *  - All tensors are dense/contiguous in the layouts given per function.
  *  - Calls are asynchronous on `stream` (a cudaStream_t passed as void*; NULL is
  *    the legacy default stream).  Nothing here synchronises the device.
- *  - No function allocates device memory.  Split-KV decode needs scratch
+ *  - No OPERATOR allocates device memory.  Split-KV decode needs scratch
  *    ("workspace"); the caller owns it, sizes it with fa_decode_workspace_bytes()
  *    and may reuse it for calls that are ordered on one stream.  Calls that can
- *    overlap on the GPU need distinct workspaces.
+ *    overlap on the GPU need distinct workspaces.  The one exception is the set-up
+ *    of the peer-memory collectives: fa_peer_alloc calls cudaMalloc three times and
+ *    synchronises the device (memory that other processes map through CUDA IPC has
+ *    to come from cudaMalloc); fa_peer_free releases it.
  *  - Return value: FA_OK or a negative fa_status; fa_last_error() gives the text
  *    for the calling thread.  Invalid arguments are rejected before any launch.
  *  - fp16 tensors are IEEE binary16; softmax scale is always 1/sqrt(D)
@@ -75,7 +78,9 @@ int fa_decode_status(const void* workspace, void* stream, int* host_status_out);
 
 /* Tuning hook for the decode kernels: consumer warps per CTA, copy-ring depth per
  * warp and persistent CTAs per SM.  0 keeps the built-in choice for that field.
- * Process-wide; values that do not fit in shared memory are reduced. */
+ * Process-wide; values that do not fit in shared memory are reduced.  The setting is a
+ * plain global read by every decode call: change it only while no other thread is inside a
+ * decode entry point (it is a measurement hook, not a per-call option). */
 int fa_decode_set_tuning(int warps, int stages, int ctas_per_sm);
 
 /*
@@ -298,7 +303,8 @@ int fa_half_to_bf16(const void* in, void* out, int64_t n, void* stream);
 /* Kernel choice for the prefill entry points: 0 = automatic (tcgen05 kernel for
  * D = 64/128, mma.sync kernel otherwise), 1 = always the mma.sync kernel, 2 = require
  * the tcgen05 kernel, 3 = tcgen05 kernel with every fourth pair of exp2 evaluated as a
- * polynomial on the FMA pipes.  Process-wide; meant for tests and measurements. */
+ * polynomial on the FMA pipes.  Process-wide, a plain global like fa_decode_set_tuning: meant
+ * for tests and measurements, not to be changed while another thread launches a prefill. */
 int fa_prefill_set_impl(int impl);
 
 /* Read back (synchronously on `stream`) the sticky status word of the prefill kernels
@@ -341,6 +347,13 @@ int fa_peer_allgather(void* const* data_ptrs, void* const* flag_ptrs, void* stat
                       int rank, int world, const void* src, int64_t offset_bytes,
                       int64_t chunk_bytes, void* stream);
 int fa_peer_status(const void* state, void* stream, int* host_status_out);
+/* Way back from a wait that ran out.  The status word is sticky, and a rank that ran a collective
+ * without its peers has advanced its epoch and stamped the peers' flags, so later collectives on the
+ * same buffers would keep mismatching.  fa_peer_reset zeroes this rank's flag array and local state
+ * (epoch, ticket, status) and waits for that on `stream`.  ALL ranks must call it, with no collective
+ * in flight, between two host-side barriers (after the first nobody launches, after the second
+ * everybody may again).  The alternative is to free the buffers and allocate new ones. */
+int fa_peer_reset(void* flags, void* state, void* stream);
 /* Bound of every wait for another rank, in polls of at least 100 ns (default 2^26;
  * applies to launches made after the call). */
 int fa_peer_set_max_polls(unsigned int max_polls);

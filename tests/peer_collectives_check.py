@@ -112,6 +112,23 @@ def main():
             print(f"bounded wait reported: {e}", flush=True)
     ok &= timed_out
     torch.cuda.synchronize()
+    # ---- the way back: every rank resets its flags / epoch / status, then collectives work again ----
+    pc.reset()
+    _lib.check(_lib.load().fa_peer_set_max_polls(1 << 26))
+    x = torch.randn(64, 8 * world, generator=g, device=dev).bfloat16()
+    want = expected_sum(x)
+    v = pc.view(0, (64, 8 * world), torch.bfloat16)
+    v.copy_(x)
+    pc.all_reduce_(v)
+    torch.cuda.synchronize()
+    recovered = torch.equal(v, want)
+    try:
+        pc.check()
+    except RuntimeError:
+        recovered = False
+    ok &= recovered
+    if rank == 0:
+        print(f"all-reduce after reset: {recovered}", flush=True)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     pc.close()
