@@ -162,15 +162,6 @@ fa::DecodeLaunchConfig pick_decode_config(int D, int G, int slot_rows, int B, in
   return c;
 }
 
-// Arrival counters in a workspace are tagged with the launch's epoch; epoch 0 is never used, so
-// zero-filled or stale memory reads as "no arrivals".
-unsigned int next_epoch() {
-  static std::atomic<unsigned int> e{0};
-  unsigned int v = ++e;
-  if (v == 0) v = ++e;
-  return v;
-}
-
 using fa::kMaxDecodeCtas;
 
 struct DecodeCall {
@@ -228,7 +219,6 @@ int run_decode(const DecodeCall& c) {
   const size_t prefix_bytes = (((size_t)(c.B + 1) * 4 + 255) & ~(size_t)255);
   p.counters = reinterpret_cast<unsigned long long*>(ws + fa::kWsCountersOffset);
   p.partials = reinterpret_cast<float*>(ws + fa::kWsPrefixOffset + prefix_bytes);
-  p.epoch = next_epoch();
   p.B = c.B; p.H_Q = c.H_Q; p.H_KV = c.H_KV; p.G = G;
   p.D_real = c.D;
   p.n_gblk = (G + 15) / 16;

@@ -12,10 +12,11 @@
 // whatever the length spread, and a segment is split across CTAs only at range
 // boundaries: at most two partial results per CTA.  The CTA that delivers the
 // last partial of a split segment (an arrival counter per split segment, named
-// by the first CTA that works on it, tagged with a per-launch epoch and left at
-// "no arrivals" by the last arriver, so that it never needs clearing after the
-// workspace's one-time initialisation) merges them by log-sum-exp.  The page prefix sums that define the unit numbering are
-// recomputed by every CTA in shared memory: the whole decode is one launch.
+// by the first CTA that works on it, bumped with one atomic add per arrival and
+// put back to zero by the last arriver, so that it never needs clearing after the
+// workspace's one-time initialisation unless a launch recorded a device status)
+// merges them by log-sum-exp.  The page prefix sums that define the unit numbering
+// are recomputed by every CTA in shared memory: the whole decode is one launch.
 //
 // Data path.  Inside a CTA each warp streams its own pages (page i of a piece
 // goes to warp i mod W) through a private ring of shared-memory stages filled
@@ -950,21 +951,15 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       if (threadIdx.x == 0) {
         // At most one split segment starts in a CTA's range (segments that start and end inside it are
         // complete), so the first CTA of the segment names its counter.
-        unsigned long long* cnt = p.counters + first;
-        unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(cnt);
-        unsigned int arrivals;
-        while (true) {
-          const unsigned int have = ((unsigned int)(seen >> 32) == p.epoch) ? (unsigned int)seen : 0u;
-          arrivals = have + 1u;
-          const unsigned long long want = ((unsigned long long)p.epoch << 32) | arrivals;
-          const unsigned long long prev = atomicCAS(cnt, seen, want);
-          if (prev == seen) break;
-          seen = prev;
-        }
+        // One atomic add per arrival (a compare-and-swap loop on a tagged counter serialised the CTAs of a
+        // segment: with a few long sequences spread over the whole grid that took longer than the
+        // attention itself).  The counter is self-cleaning: the last arriver puts it back to zero, so a
+        // workspace needs clearing only once - and again after a launch that recorded a device status,
+        // whose counters may be left mid-count.
+        unsigned int* cnt = reinterpret_cast<unsigned int*>(p.counters + first);
+        const unsigned int arrivals = atomicAdd(cnt, 1u) + 1u;
         s_last_flag = (arrivals == n_parts) ? 1 : 0;
-        // everyone has arrived: leave the counter at zero arrivals, so that a CUDA-graph replay of
-        // this launch (same epoch) starts clean
-        if (arrivals == n_parts) *reinterpret_cast<volatile unsigned long long*>(cnt) = (unsigned long long)p.epoch << 32;
+        if (arrivals == n_parts) *reinterpret_cast<volatile unsigned int*>(cnt) = 0u;
       }
       __syncthreads();
       if (s_last_flag) {
@@ -973,19 +968,40 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         for (int e = threadIdx.x; e < Gb * D; e += blockDim.x) {
           const int row = e / D, d = e - row * D;
           if (d >= p.D_real) continue;
-          float M = -INFINITY;
-          for (int c = first; c <= last; ++c) {
+          // The partials sit in L2 (other CTAs wrote them): every read costs an L2 round trip, so the reads
+          // of eight partials are issued together before any of them is used.  (A segment is split over
+          // up to hundreds of CTAs when few sequences fill the grid; one dependent read per partial made the
+          // merge the longest part of such launches.)
+          constexpr int MB = 8;
+          auto part_row = [&](int c) -> const float* {
             const int slot = ((long long)c * per >= seg_start) ? 0 : 1;
-            const float* part = p.partials + ((size_t)c * 2 + slot) * p.slot_rows * ROWLEN;
-            M = fmaxf(M, __ldcg(part + row * ROWLEN + D));
+            return p.partials + ((size_t)c * 2 + slot) * p.slot_rows * ROWLEN + row * ROWLEN;
+          };
+          float M = -INFINITY;
+          for (int c0 = first; c0 <= last; c0 += MB) {
+            float mv[MB];
+#pragma unroll
+            for (int k = 0; k < MB; ++k) mv[k] = (c0 + k <= last) ? __ldcg(part_row(c0 + k) + D) : -INFINITY;
+#pragma unroll
+            for (int k = 0; k < MB; ++k) M = fmaxf(M, mv[k]);
           }
           float L = 0.f, O = 0.f;
-          for (int c = first; c <= last; ++c) {
-            const int slot = ((long long)c * per >= seg_start) ? 0 : 1;
-            const float* part = p.partials + ((size_t)c * 2 + slot) * p.slot_rows * ROWLEN;
-            const float f = fast_exp2(__ldcg(part + row * ROWLEN + D) - M);
-            L += __ldcg(part + row * ROWLEN + D + 1) * f;
-            O += __ldcg(part + row * ROWLEN + d) * f;
+          for (int c0 = first; c0 <= last; c0 += MB) {
+            float mv[MB], lv[MB], ov[MB];
+#pragma unroll
+            for (int k = 0; k < MB; ++k) {
+              const bool in = c0 + k <= last;
+              const float* pr = part_row(in ? c0 + k : last);
+              mv[k] = in ? __ldcg(pr + D) : -INFINITY;
+              lv[k] = in ? __ldcg(pr + D + 1) : 0.f;
+              ov[k] = in ? __ldcg(pr + d) : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < MB; ++k) {
+              const float f = (mv[k] == -INFINITY) ? 0.f : fast_exp2(mv[k] - M);
+              L += lv[k] * f;
+              O += ov[k] * f;
+            }
           }
           outp[(size_t)row * p.D_real + d] = __float2half_rn(O / L);
         }

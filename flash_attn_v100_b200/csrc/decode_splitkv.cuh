@@ -31,9 +31,8 @@ struct DecodeParams {
   const __half* v_scale_h;     // int8 cache only: [B, H_KV, N] fp16
   int32_t* prefix;             // workspace: [B + 1] running page counts
   float* partials;             // workspace: [n_cta][2][slot_rows][D + 2]
-  unsigned long long* counters;  // workspace: [kMaxDecodeCtas] (epoch << 32 | arrivals), one per split
-                                 // segment, indexed by the first CTA that works on the segment
-  unsigned int epoch;          // unique per launch; counters of other epochs read as zero
+  unsigned long long* counters;  // workspace: [kMaxDecodeCtas] arrivals (low word), one per split segment,
+                                 // indexed by the first CTA that works on the segment; zero between launches
   int32_t* status;             // workspace: sticky status word
   int B, H_Q, H_KV, G;         // G = H_Q / H_KV
   int D_real;                  // head dimension of the tensors (<= the padded one the kernel is built for)

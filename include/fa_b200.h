@@ -63,7 +63,9 @@ size_t fa_decode_workspace_bytes(int B, int H_Q, int H_KV, int D);
 
 /* Zero the status word and the arrival counters at the head of a workspace.  REQUIRED once
  * after allocating it, before its first use (the counters must not start from arbitrary
- * bytes); afterwards the kernels keep them consistent, whatever shapes the workspace serves.
+ * bytes); afterwards the kernels keep them consistent (every launch leaves the counters at
+ * zero), whatever shapes the workspace serves.  REQUIRED again after a launch that recorded a
+ * device status (fa_decode_status != 0): such a launch may have left counters mid-count.
  * workspace == NULL (workspace_bytes ignored) re-initialises the built-in scratch of
  * fa_paged_decode_gqa_f16_static_scratch, i.e. clears its status word. */
 int fa_decode_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
