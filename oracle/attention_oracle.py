@@ -273,7 +273,8 @@ def paged_decode(q, k_cache, v_cache, block_table, seq_lens, final_cast=True):
 # --------------------------------------------------------------------------
 def round_half_away(x: torch.Tensor) -> torch.Tensor:
     """C `roundf` (flash_attn_kernel.cu:2837, :2856); torch.round is half-even."""
-    return torch.sign(x) * torch.floor(x.abs() + 0.5)
+    # |x| + 0.5 in double: exact, so that 0.49999997f does not round up to 1 on the way
+    return (torch.sign(x).double() * torch.floor(x.abs().double() + 0.5)).to(x.dtype)
 
 
 def quantize_int8(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:

@@ -56,3 +56,28 @@ def test_int8_rounding_ties_and_clamp():
     _, scores = fa.forward_decode_int8_gqa(q.cuda(), k.cuda(), v.cuda(), qs.cuda(), ks.cuda(), N - 1, return_scores=True)
     ref = orc.int8_scores(q, k, qs, ks)
     assert torch.equal(scores.cpu(), ref)
+
+
+def test_int8_benchmark_shape_scores_bit_exact_on_sampled_rows():
+    """The INT8 benchmark configuration at full size (B=32, 32/8 heads, D=128, N=4096, cache_len 4095):
+    the int32 accumulators of sampled (batch, head) rows against the CPU restatement, bit for bit, and the
+    outputs of those rows within 2e-3."""
+    import flash_attn_v100 as fa
+    import flash_attn_v100_b200
+    B, H_Q, H_KV, D, N = 32, 32, 8, 128, 4096
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(4)
+    q = torch.randn(B, H_Q, 1, D, generator=g, device=dev, dtype=torch.float16)
+    k = torch.randn(B, H_KV, N, D, generator=g, device=dev, dtype=torch.float16)
+    v = torch.randn(B, H_KV, N, D, generator=g, device=dev, dtype=torch.float16)
+    qs = (q.abs().amax(-1).float().squeeze(-1) / 127).contiguous()
+    ks = (k.abs().amax(-1).float() / 127).contiguous()
+    out, scores = fa.forward_decode_int8_gqa(q, k, v, qs, ks, N - 1, return_scores=True)
+    torch.cuda.synchronize()
+    flash_attn_v100_b200.check_async_errors()
+    for b in (0, 13, 31):
+        sl = slice(b, b + 1)
+        ref_out, ref_dots = orc.decode_int8_gqa(q[sl].cpu(), k[sl].cpu(), v[sl].cpu(), qs[sl].cpu(), ks[sl].cpu(), N - 1,
+                                                final_cast=False)
+        assert torch.equal(scores[sl].cpu(), ref_dots), b
+        assert (out[sl].float().cpu() - ref_out).abs().max().item() < 2e-3, b
