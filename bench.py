@@ -585,6 +585,9 @@ def roofline_of(wl, ms_per_step, peaks, peak_src):
             "duration": "CUDA-event time of one step on the launching stream (median block of `steps` steps)"}
 
 
+MIN_SECONDS = 0.5   # device time covered by the repeated blocks of one measurement (--min-seconds)
+
+
 def timed_record(wl, fa, steps, warmup, world, device, rank, local, peaks, peak_src):
     """Warm up, then time `wl.step` in blocks of `steps` with the clocks sampled across the timed blocks."""
     import flash_attn_v100_b200
@@ -596,7 +599,7 @@ def timed_record(wl, fa, steps, warmup, world, device, rank, local, peaks, peak_
     if rank == 0:
         sampler.start()
         time.sleep(0.15)
-    m = measure(lambda: wl.step(fa), steps, world, device, getattr(wl, "flush", None))
+    m = measure(lambda: wl.step(fa), steps, world, device, getattr(wl, "flush", None), min_seconds=MIN_SECONDS)
     clocks = sampler.stop() if rank == 0 else None
     flash_attn_v100_b200.check_async_errors()
     ms_per_step = m["ms_block"] / steps
@@ -671,7 +674,7 @@ def run_b200(args):
     if wl.step_e2e is not None:
         for _ in range(3):
             wl.step_e2e(fa)
-        m = measure(lambda: wl.step_e2e(fa), args.steps, world, device)
+        m = measure(lambda: wl.step_e2e(fa), args.steps, world, device, min_seconds=MIN_SECONDS)
         ms_e2e = m["ms_block"] / args.steps
         h2d, d2h = wl.e2e_bytes()
         e2e = {"value": wl.units_per_step * world / (ms_e2e * 1e-3), "unit": wl.unit,
@@ -822,7 +825,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true",
                     help="skip the head-sharded, secondary (prefill, INT8) and multi-GPU records of the default run")
+    ap.add_argument("--min-seconds", type=float, default=0.5,
+                    help="repeat the block of --steps timed steps until this much device time is covered "
+                         "(0: one block; used for the profiler's launch list)")
     args = ap.parse_args()
+    global MIN_SECONDS
+    MIN_SECONDS = args.min_seconds
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "engine":
