@@ -23,6 +23,7 @@ SIGNATURES = {
     "fa_decode_status": (_i, [_vp, _vp, _c.POINTER(_i)]),
     "fa_decode_set_tuning": (_i, [_i, _i, _i]),
     "fa_paged_decode_gqa_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i, _i64, _vp, _sz, _vp]),
+    "fa_paged_decode_gqa_f16_out_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i, _i64, _vp, _sz, _vp]),
     "fa_paged_decode_gqa_f16_static_scratch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i, _i64, _vp]),
     "fa_decode_gqa_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "fa_decode_sliding_window_gqa_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
@@ -32,6 +33,7 @@ SIGNATURES = {
     "fa_rope_append_paged_f16": (_i, [_vp] * 12 + [_i, _i, _i, _i, _i, _i, _i64, _i, _vp]),
     "fa_add_rmsnorm_bf16": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _c.c_float, _vp]),
     "fa_qk_norm_split_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _c.c_float, _vp]),
+    "fa_qkv_rope_append_f16": (_i, [_vp] * 13 + [_i, _i, _i, _i, _i, _c.c_float, _i64, _i, _vp]),
     "fa_silu_mul_bf16": (_i, [_vp, _vp, _i64, _i, _vp]),
     "fa_half_to_bf16": (_i, [_vp, _vp, _i64, _vp]),
     "fa_peer_alloc": (_i, [_sz, _c.POINTER(_vp), _c.POINTER(_vp), _c.POINTER(_vp), _vp, _vp]),
@@ -47,6 +49,7 @@ SIGNATURES = {
     "fa_prefill_status": (_i, [_vp, _c.POINTER(_i), _i]),
     "fa_prefill_dense_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "fa_prefill_varlen_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _i, _vp]),
+    "fa_prefill_varlen_f16_out_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _i, _vp]),
 }
 
 _lib = None

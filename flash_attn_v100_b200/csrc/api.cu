@@ -174,6 +174,7 @@ struct DecodeCall {
   int B, H_Q, H_KV, D, mode, fixed_len, N, bt_stride;
   long long num_pages, rows_total, max_units;
   bool int8;
+  bool out_bf16;                     // output stored as bfloat16 instead of fp16
   bool kv8;                          // int8 cache with fp16 per-token scales
   const void *k_scale_h, *v_scale_h;
   // sliding window + sink (contiguous fixed mode): see DecodeParams.  has_window = false: identity page map
@@ -206,6 +207,7 @@ int run_decode(const DecodeCall& c) {
   memset(&p, 0, sizeof(p));
   p.q = static_cast<const __half*>(c.q);
   p.out = static_cast<__half*>(c.out);
+  p.out_bf16 = c.out_bf16 ? 1 : 0;
   p.block_table = c.block_table;
   p.lens = c.lens;
   p.q_scale = c.q_scale;
@@ -357,10 +359,10 @@ int fa_decode_set_tuning(int warps, int stages, int ctas_per_sm) {
   return FA_OK;
 }
 
-int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_cache, void* out,
-                            const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q, int H_KV, int D,
-                            int64_t num_pages, int block_table_stride, int64_t max_seq_len, void* workspace,
-                            size_t workspace_bytes, void* stream) {
+static int paged_decode_impl(const void* q, const void* k_cache, const void* v_cache, void* out,
+                             const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q, int H_KV, int D,
+                             int64_t num_pages, int block_table_stride, int64_t max_seq_len, void* workspace,
+                             size_t workspace_bytes, void* stream, bool out_bf16) {
   int rc = check_paged_args(q, k_cache, v_cache, out, block_table, seq_lens, B, H_Q, H_KV, D, num_pages,
                             block_table_stride);
   if (rc != FA_OK) return rc;
@@ -375,8 +377,25 @@ int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_ca
   if (max_seq_len > 0 && (max_seq_len + 15) / 16 < max_pages) max_pages = (max_seq_len + 15) / 16;
   c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * max_pages;
   c.int8 = false;
+  c.out_bf16 = out_bf16;
   c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
   return run_decode(c);
+}
+
+int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                            const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q, int H_KV, int D,
+                            int64_t num_pages, int block_table_stride, int64_t max_seq_len, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  return paged_decode_impl(q, k_cache, v_cache, out, block_table, seq_lens, B, H_Q, H_KV, D, num_pages,
+                           block_table_stride, max_seq_len, workspace, workspace_bytes, stream, false);
+}
+
+int fa_paged_decode_gqa_f16_out_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                     const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q, int H_KV,
+                                     int D, int64_t num_pages, int block_table_stride, int64_t max_seq_len,
+                                     void* workspace, size_t workspace_bytes, void* stream) {
+  return paged_decode_impl(q, k_cache, v_cache, out, block_table, seq_lens, B, H_Q, H_KV, D, num_pages,
+                           block_table_stride, max_seq_len, workspace, workspace_bytes, stream, true);
 }
 
 int fa_decode_gqa_f16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N, int D,
@@ -588,9 +607,9 @@ int fa_prefill_dense_f16(const void* q, const void* k, const void* v, void* out,
   return run_prefill(p, D, static_cast<cudaStream_t>(stream));
 }
 
-int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
-                          int batch, int64_t total, int H_Q, int H_KV, int D, int max_seqlen, int causal,
-                          void* stream) {
+static int prefill_varlen_impl(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
+                               int batch, int64_t total, int H_Q, int H_KV, int D, int max_seqlen, int causal,
+                               void* stream, bool out_bf16) {
   int rc = check_decode_common(q, k, v, out, batch, H_Q, H_KV, D);
   if (rc != FA_OK) return rc;
   FA_REQUIRE(cu_seqlens != nullptr, "null cu_seqlens");
@@ -606,7 +625,20 @@ int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out
   p.q_batch_stride = 0; p.q_head_stride = D; p.q_tok_stride = (long long)H_Q * D;
   p.kv_batch_stride = 0; p.kv_head_stride = D; p.kv_tok_stride = (long long)H_KV * D;
   p.causal = causal ? 1 : 0;
+  p.out_bf16 = out_bf16 ? 1 : 0;
   return run_prefill(p, D, static_cast<cudaStream_t>(stream));
+}
+
+int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
+                          int batch, int64_t total, int H_Q, int H_KV, int D, int max_seqlen, int causal,
+                          void* stream) {
+  return prefill_varlen_impl(q, k, v, out, cu_seqlens, batch, total, H_Q, H_KV, D, max_seqlen, causal, stream, false);
+}
+
+int fa_prefill_varlen_f16_out_bf16(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
+                                   int batch, int64_t total, int H_Q, int H_KV, int D, int max_seqlen, int causal,
+                                   void* stream) {
+  return prefill_varlen_impl(q, k, v, out, cu_seqlens, batch, total, H_Q, H_KV, D, max_seqlen, causal, stream, true);
 }
 
 int fa_rope_append_paged_f16(const void* q, const void* k, const void* v, const float* cos, const float* sin,
@@ -642,6 +674,37 @@ int fa_rope_append_paged_f16(const void* q, const void* k, const void* v, const 
   FA_CUDA(fa::prefill_status_ptr(&p.status));
   cudaError_t e = fa::launch_rope_append(p, di.sm_count, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, "rope/append launch failed: %s", cudaGetErrorString(e));
+  return FA_OK;
+}
+
+int fa_qkv_rope_append_f16(const void* qkv, const void* q_weight, const void* k_weight, const float* cos,
+                           const float* sin, void* q_out, void* k_out, void* v_out, void* k_cache, void* v_cache,
+                           const int32_t* block_table, const int32_t* positions, const int32_t* cu_seqlens, int T,
+                           int batch, int H_Q, int H_KV, int D, float eps, int64_t num_pages, int block_table_stride,
+                           void* stream) {
+  FA_REQUIRE(qkv && cos && sin && q_out, "null tensor pointer");
+  FA_REQUIRE(T >= 0 && batch > 0 && H_Q > 0 && H_KV > 0, "T must be >= 0; batch, H_Q, H_KV positive");
+  if (!supported_d(D)) return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (supported: 64, 128, 256)", D);
+  FA_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "k_cache and v_cache must be given together");
+  if (k_cache != nullptr) {
+    FA_REQUIRE(block_table != nullptr && block_table_stride > 0 && num_pages > 0,
+               "block_table, its stride and num_pages are required with a cache");
+  }
+  FA_REQUIRE(cu_seqlens != nullptr || (positions != nullptr && T == batch),
+             "without cu_seqlens there is one token per sequence (T == batch) and positions is required");
+  fa::QkvRopeAppendParams p;
+  memset(&p, 0, sizeof(p));
+  p.qkv = qkv; p.q_weight = q_weight; p.k_weight = k_weight; p.eps = eps;
+  p.v_out = static_cast<__half*>(v_out);
+  p.r.cos = cos; p.r.sin = sin;
+  p.r.q_out = static_cast<__half*>(q_out); p.r.k_out = static_cast<__half*>(k_out);
+  p.r.k_cache = static_cast<__half*>(k_cache); p.r.v_cache = static_cast<__half*>(v_cache);
+  p.r.block_table = block_table; p.r.positions = positions; p.r.cu_seqlens = cu_seqlens;
+  p.r.T = T; p.r.batch = batch; p.r.H_Q = H_Q; p.r.H_KV = H_KV; p.r.D = D; p.r.rot_dim = D;
+  p.r.bt_stride = block_table_stride; p.r.num_pages = num_pages;
+  FA_CUDA(fa::prefill_status_ptr(&p.r.status));
+  cudaError_t e = fa::launch_qkv_rope_append(p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(FA_ERR_CUDA, "qkv norm/rope/append launch failed: %s", cudaGetErrorString(e));
   return FA_OK;
 }
 

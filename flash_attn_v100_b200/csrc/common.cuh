@@ -1,6 +1,7 @@
 // Shared device helpers (sm_100a): mbarrier, TMA, ldmatrix, mma.sync, packing.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -129,6 +130,23 @@ __device__ __forceinline__ void mma_s8_16832(int (&c)[4], const uint32_t (&a)[4]
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// 16-bit result of an operator: IEEE binary16 (the reference's output type) or bfloat16 (for callers whose
+// activations are bfloat16; the bits are stored through the same __half-typed pointer).
+__device__ __forceinline__ __half to_out16(float x, bool bf16) {
+  if (bf16) {
+    const __nv_bfloat16 b = __float2bfloat16_rn(x);
+    return *reinterpret_cast<const __half*>(&b);
+  }
+  return __float2half_rn(x);
+}
+__device__ __forceinline__ uint32_t pack_out16x2(float lo, float hi, bool bf16) {
+  if (bf16) {
+    const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&b);
+  }
+  return pack_half2(lo, hi);
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

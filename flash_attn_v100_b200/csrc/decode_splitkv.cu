@@ -930,7 +930,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           O += rp[d] * f;
         }
         if (complete) {
-          p.out[((size_t)b * p.H_Q + head0 + row) * p.D_real + d] = __float2half_rn(O / L);
+          p.out[((size_t)b * p.H_Q + head0 + row) * p.D_real + d] = to_out16(O / L, p.out_bf16 != 0);
         } else {
           part[row * ROWLEN + d] = O;
           if (d == 0) {
@@ -1003,7 +1003,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
               O += ov[k] * f;
             }
           }
-          outp[(size_t)row * p.D_real + d] = __float2half_rn(O / L);
+          outp[(size_t)row * p.D_real + d] = to_out16(O / L, p.out_bf16 != 0);
         }
       }
     }

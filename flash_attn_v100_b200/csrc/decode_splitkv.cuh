@@ -21,7 +21,8 @@ enum DecodeKind : int {
 
 struct DecodeParams {
   const __half* q;             // [B, H_Q, 1, D]
-  __half* out;                 // [B, H_Q, 1, D]
+  __half* out;                 // [B, H_Q, 1, D]: fp16, or bfloat16 bits when out_bf16 is set
+  int out_bf16;
   const int32_t* block_table;  // paged only
   const int32_t* lens;         // seq_lens / cache_lens, null in fixed mode
   const float* q_scale;        // int8 only: [B, H_Q]

@@ -11,7 +11,8 @@ struct PrefillParams {
   const __half* q;
   const __half* k;
   const __half* v;
-  __half* out;
+  __half* out;                // fp16, or bfloat16 bits when out_bf16 is set
+  int out_bf16;
   const int32_t* cu_seqlens;  // null => dense [B,H,N,D]; else packed [total,H,D]
   int batch;                  // sequences (dense: B)
   int H_Q, H_KV;

@@ -205,14 +205,14 @@ __global__ void __launch_bounds__(BM * 2) prefill_mma_kernel(const PrefillParams
 #pragma unroll
     for (int i = 0; i < NT_O; ++i)
       if (i * 8 < p.D_real)
-        *reinterpret_cast<__half2*>(o + i * 8 + cq) = __floats2half2_rn(acc[i][0] * inv0, acc[i][1] * inv0);
+        *reinterpret_cast<uint32_t*>(o + i * 8 + cq) = pack_out16x2(acc[i][0] * inv0, acc[i][1] * inv0, p.out_bf16 != 0);
   }
   if (qrow0 + 8 < len) {
     __half* o = og + (long long)(qrow0 + 8) * p.q_tok_stride;
 #pragma unroll
     for (int i = 0; i < NT_O; ++i)
       if (i * 8 < p.D_real)
-        *reinterpret_cast<__half2*>(o + i * 8 + cq) = __floats2half2_rn(acc[i][2] * inv1, acc[i][3] * inv1);
+        *reinterpret_cast<uint32_t*>(o + i * 8 + cq) = pack_out16x2(acc[i][2] * inv1, acc[i][3] * inv1, p.out_bf16 != 0);
   }
 }
 

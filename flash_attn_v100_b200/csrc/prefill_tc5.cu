@@ -82,6 +82,7 @@ struct Tc5Params {
   int D_real;      // head dimension of the tensors (columns [D_real, D) read as zeros through the tensor maps)
   int pair_heads;  // 1: two heads x same rows; 0: one head x two row blocks
   int dense;
+  int out_bf16;    // store O as bfloat16 instead of fp16
   int n_hg, n_rb;  // head groups and row blocks of the item grid (items = n_rb * batch * n_hg)
   unsigned long long* item_counter;  // next unclaimed item of this launch (zeroed in-stream before it)
   float scale_log2;
@@ -925,7 +926,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         tc_ld16(tO + c * 16, o);
         tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 8; ++i) u[2 * c + (i >> 2)][i & 3] = pack_half2(o[2 * i] * inv, o[2 * i + 1] * inv);
+        for (int i = 0; i < 8; ++i) u[2 * c + (i >> 2)][i & 3] = pack_out16x2(o[2 * i] * inv, o[2 * i + 1] * inv, p.out_bf16 != 0);
       }
       // A thread-per-row store would touch 32 different 128-byte lines per instruction (the rows of a warp lie
       // a whole row apart in memory), and the load/store unit handles one line per cycle.  Transpose the
@@ -1102,6 +1103,7 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   p.D_real = pp.D_real;
   p.pair_heads = ((pp.H_Q / pp.H_KV) % 2 == 0) ? 1 : 0;
   p.dense = dense ? 1 : 0;
+  p.out_bf16 = pp.out_bf16;
   p.scale_log2 = pp.scale_log2;
   constexpr int KV_STAGES = (D == 128) ? 2 : 4;
   constexpr size_t TILE = (size_t)(D / 64) * 128 * 128;

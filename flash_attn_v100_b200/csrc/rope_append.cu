@@ -19,6 +19,8 @@
 #include "common.cuh"
 #include "rope_append.cuh"
 
+#include <cuda_bf16.h>
+
 namespace fa {
 namespace {
 
@@ -144,7 +146,115 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
   }
 }
 
+// qkv projection output -> attention inputs.  One warp per (token, head); lane L holds D/32 consecutive
+// elements, its rotary partner (the element half a head away) lives in lane L ^ 16.  The arithmetic is that
+// of the per-head norm kernel followed by the rotary kernel above, value for value, so the fused launch is
+// bit-identical to the two it replaces.
+template <int PER>
+__global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeAppendParams p) {
+  const RopeAppendParams& r = p.r;
+  const int D = r.D, heads = r.H_Q + 2 * r.H_KV;
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)r.T * heads) return;
+  const int tok = (int)(wid / heads);
+  const int hh = (int)(wid - (long long)tok * heads);
+  int kind, h;   // 0 = q, 1 = k, 2 = v
+  if (hh < r.H_Q) { kind = 0; h = hh; }
+  else if (hh < r.H_Q + r.H_KV) { kind = 1; h = hh - r.H_Q; }
+  else { kind = 2; h = hh - r.H_Q - r.H_KV; }
+  const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.qkv) + ((long long)tok * heads + hh) * D + lane * PER;
+  float f[PER];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    f[i] = __bfloat162float(src[i]);
+    ss += f[i] * f[i];
+  }
+  const __nv_bfloat16* w = kind == 0 ? static_cast<const __nv_bfloat16*>(p.q_weight)
+                         : kind == 1 ? static_cast<const __nv_bfloat16*>(p.k_weight) : nullptr;
+  if (w != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = rsqrtf(ss / (float)D + p.eps);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const __nv_bfloat16 nb = __float2bfloat16(f[i] * inv);
+      f[i] = __bfloat162float(__float2bfloat16(__bfloat162float(w[lane * PER + i]) * __bfloat162float(nb)));
+    }
+  }
+  __half x[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) x[i] = __float2half_rn(f[i]);
+
+  // sequence and cache slot of this token
+  int seq, pos;
+  if (r.cu_seqlens != nullptr) {
+    int lo = 0, hi = r.batch;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (__ldg(r.cu_seqlens + mid) <= tok) lo = mid; else hi = mid;
+    }
+    seq = lo;
+    pos = tok - __ldg(r.cu_seqlens + seq) + (r.positions ? __ldg(r.positions + seq) : 0);
+  } else {
+    seq = tok;
+    pos = __ldg(r.positions + seq);
+  }
+  __half* dst_page = nullptr;
+  if (kind != 0 && r.k_cache != nullptr) {
+    const int blk = pos >> 4;
+    int page = -1;
+    if (pos >= 0 && blk < r.bt_stride) page = __ldg(r.block_table + (long long)seq * r.bt_stride + blk);
+    if (page >= 0 && (long long)page < r.num_pages) {
+      __half* base = (kind == 1) ? r.k_cache : r.v_cache;
+      dst_page = base + (((long long)page * r.H_KV + h) * 16 + (pos & 15)) * D + lane * PER;
+    } else if (lane == 0) {
+      atomicOr(r.status, kStatusBadPageId);   // no slot for this token: reported, nothing written
+    }
+  }
+  __half o[PER];
+  if (kind == 2) {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) o[i] = x[i];
+  } else {
+    // rotary: first half (lanes 0-15) x1 * cos - x2 * sin, second half x2 * cos + x1 * sin, with the partner
+    // element from lane ^ 16 and cos / sin at the element's own index (the tables hold cat(freqs, freqs))
+    const float* cs = r.cos + (long long)tok * D + lane * PER;
+    const float* sn = r.sin + (long long)tok * D + lane * PER;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const unsigned short mine = __half_as_ushort(x[i]);
+      const __half other = __ushort_as_half((unsigned short)__shfl_xor_sync(0xffffffffu, (unsigned int)mine, 16));
+      const __half c = __float2half_rn(__ldg(cs + i)), s = __float2half_rn(__ldg(sn + i));
+      o[i] = lane < 16 ? rope_lo(x[i], other, c, s) : rope_hi(other, x[i], c, s);
+    }
+  }
+  __half* dst_lin = nullptr;
+  if (kind == 0) dst_lin = r.q_out + ((long long)tok * r.H_Q + h) * D + lane * PER;
+  else if (kind == 1 && r.k_out != nullptr) dst_lin = r.k_out + ((long long)tok * r.H_KV + h) * D + lane * PER;
+  else if (kind == 2 && p.v_out != nullptr) dst_lin = p.v_out + ((long long)tok * r.H_KV + h) * D + lane * PER;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    if (dst_lin) dst_lin[i] = o[i];
+    if (dst_page) dst_page[i] = o[i];
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_qkv_rope_append(const QkvRopeAppendParams& p, cudaStream_t stream) {
+  const long long warps = (long long)p.r.T * (p.r.H_Q + 2 * p.r.H_KV);
+  if (warps == 0) return cudaSuccess;
+  const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  switch (p.r.D) {
+    case 64: qkv_rope_append_kernel<2><<<blocks, 256, 0, stream>>>(p); break;
+    case 128: qkv_rope_append_kernel<4><<<blocks, 256, 0, stream>>>(p); break;
+    case 256: qkv_rope_append_kernel<8><<<blocks, 256, 0, stream>>>(p); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
 
 cudaError_t launch_rope_append(const RopeAppendParams& p, int sm_count, cudaStream_t stream) {
   const int per_head = (p.rot_dim / 2) / 8 + (p.D - p.rot_dim) / 8;

@@ -26,4 +26,16 @@ struct RopeAppendParams {
 
 cudaError_t launch_rope_append(const RopeAppendParams& p, int sm_count, cudaStream_t stream);
 
+// The decoder block's projection output to attention inputs in one launch: per-head RMSNorm of q and k
+// (weights may be null), cast to fp16, full rotary embedding, k / v appended to the pages.
+struct QkvRopeAppendParams {
+  const void* qkv;            // [T, (H_Q + 2 H_KV) * D] bf16: q heads, then k heads, then v heads
+  const void* q_weight;       // [D] bf16 or null
+  const void* k_weight;       // [D] bf16 or null
+  float eps;
+  __half* v_out;              // optional [T, H_KV, D] fp16 copy of v (prefill attention reads it)
+  RopeAppendParams r;         // cos, sin, q_out, k_out, caches, tables, sizes (q / k / v unused; rot_dim == D)
+};
+cudaError_t launch_qkv_rope_append(const QkvRopeAppendParams& p, cudaStream_t stream);
+
 }  // namespace fa

@@ -34,6 +34,9 @@ class TPDecoder:
         # the greedy candidates with the library's peer-memory kernels (capturable into the step's CUDA graph)
         # instead of NCCL calls.  Prefill keeps NCCL (large messages, not replayed from a graph).
         self.comm = None
+        # one launch for QK-norm + cast + rotary + cache append (False: the norm kernel and the rotary/append
+        # kernel one after the other; same values, kept for the parity test of the fused kernel)
+        self.fused_qkv = True
         self.device = torch.device(device)
         self.ql = cfg.num_heads // world
         self.kl = cfg.num_kv_heads // world
@@ -62,6 +65,26 @@ class TPDecoder:
         kn = _p(lw["kn"]) if self.cfg.qk_norm else None
         _lib.check(self.lib.fa_qk_norm_split_f16(_p(qkv), qn, kn, _p(q), _p(k), _p(v), T, self.ql, self.kl, D,
                                                  self.cfg.rms_norm_eps, self._stream()))
+        return q, k, v
+
+    def _qkv_rope_append(self, qkv, lw, cos, sin, k_pool, v_pool, block_table, slots, max_blocks, cu_seqlens):
+        """Per-head QK-norm, cast to fp16, rotary embedding and the append of k / v to the pages in ONE launch
+        (the two-kernel path is `_qk_norm_split` + `ops.rope_append_paged_fp16`; same values).  Returns q_rot
+        and, for packed prompts, the rotated k and v the prefill attention reads."""
+        T, D = qkv.size(0), self.cfg.head_dim
+        prefill = cu_seqlens is not None
+        q = torch.empty((T, self.ql, D), dtype=torch.float16, device=self.device)
+        k = torch.empty((T, self.kl, D), dtype=torch.float16, device=self.device) if prefill else None
+        v = torch.empty((T, self.kl, D), dtype=torch.float16, device=self.device) if prefill else None
+        batch = cu_seqlens.numel() - 1 if prefill else T
+        if block_table.stride(1) != 1 or block_table.stride(0) != max_blocks or batch * max_blocks > block_table.numel():
+            raise RuntimeError("block_table rows must be contiguous with stride max_blocks")
+        qn = _p(lw["qn"]) if self.cfg.qk_norm else None
+        kn = _p(lw["kn"]) if self.cfg.qk_norm else None
+        _lib.check(self.lib.fa_qkv_rope_append_f16(
+            _p(qkv), qn, kn, _p(cos), _p(sin), _p(q), _p(k) if prefill else None, _p(v) if prefill else None,
+            _p(k_pool), _p(v_pool), _p(block_table), _p(slots), _p(cu_seqlens) if prefill else None, T, batch,
+            self.ql, self.kl, D, self.cfg.rms_norm_eps, k_pool.size(0), max_blocks, self._stream()))
         return q, k, v
 
     def _silu_mul(self, gu):
@@ -122,18 +145,28 @@ class TPDecoder:
                 x = st["x"]
                 h = self._add_rmsnorm(x, st["delta"], lw["ln1"])         # x += delta (previous MLP); h = ln1(x)
                 qkv = h @ lw["wqkv"].t()
-                q, k, v = self._qk_norm_split(qkv, lw)
-                if prefill:
-                    q_rot, k_rot = ops.rope_append_paged_fp16(q, k, v, st["cos"], st["sin"], kv.k_pools[l], kv.v_pools[l],
-                                                              block_table, slots, max_blocks, cu_seqlens=cu_seqlens,
-                                                              return_k=True)
-                    attn = ops.forward_varlen_prefill_fp16(q_rot, k_rot, v, cu_seqlens, max_seqlen, True)
+                if self.fused_qkv:
+                    q_rot, k_rot, v = self._qkv_rope_append(qkv, lw, st["cos"], st["sin"], kv.k_pools[l], kv.v_pools[l],
+                                                            block_table, slots, max_blocks, cu_seqlens)
+                    if not prefill:
+                        q_rot = q_rot.unsqueeze(2)
                 else:
-                    q_rot = ops.rope_append_paged_fp16(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2), st["cos"], st["sin"],
-                                                       kv.k_pools[l], kv.v_pools[l], block_table, slots, max_blocks)
+                    q, k, v = self._qk_norm_split(qkv, lw)
+                    if prefill:
+                        q_rot, k_rot = ops.rope_append_paged_fp16(q, k, v, st["cos"], st["sin"], kv.k_pools[l],
+                                                                  kv.v_pools[l], block_table, slots, max_blocks,
+                                                                  cu_seqlens=cu_seqlens, return_k=True)
+                    else:
+                        q_rot = ops.rope_append_paged_fp16(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2), st["cos"],
+                                                           st["sin"], kv.k_pools[l], kv.v_pools[l], block_table, slots,
+                                                           max_blocks)
+                if prefill:
+                    attn = ops.forward_varlen_prefill_fp16(q_rot, k_rot, v, cu_seqlens, max_seqlen, True,
+                                                           out_dtype=torch.bfloat16)
+                else:
                     attn = ops.forward_paged_decode_gqa_fp16(q_rot, kv.k_pools[l], kv.v_pools[l], block_table,
-                                                             st["lens"], max_blocks)
-                a = self._to_bf16(attn.reshape(x.size(0), self.ql * cfg.head_dim))
+                                                             st["lens"], max_blocks, out_dtype=torch.bfloat16)
+                a = attn.reshape(x.size(0), self.ql * cfg.head_dim)   # bf16 straight from the attention epilogue
                 if peer is None:
                     st["o"] = a @ lw["wo"].t()
                 else:                      # GEMM straight into the peer buffer, summed in place over the ranks

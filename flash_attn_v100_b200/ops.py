@@ -327,10 +327,13 @@ def forward_continuous_batching_fp16(q, k, v, cache_lens, causal):
     return out
 
 
-def forward_paged_decode_gqa_fp16(q, k_cache, v_cache, block_table, seq_lens, max_num_blocks):
+def forward_paged_decode_gqa_fp16(q, k_cache, v_cache, block_table, seq_lens, max_num_blocks, out_dtype=None):
     """flash_attn_forward_paged_decode_gqa_fp16 (flash_attn_kernel.cu:3516-3584).
     q [B,H_Q,1,D]; k_cache/v_cache [pages,H_KV,16,D] fp16; block_table [B,*] int32 with
-    row stride `max_num_blocks` (:3438); seq_lens [B] int32.  seq_len 0 gives zeros."""
+    row stride `max_num_blocks` (:3438); seq_lens [B] int32.  seq_len 0 gives zeros.
+    `out_dtype=torch.bfloat16` (an addition) returns the result rounded to bfloat16 instead of fp16."""
+    _chk(out_dtype in (None, torch.float16, torch.bfloat16), "out_dtype must be float16 or bfloat16")
+    bf16_out = out_dtype == torch.bfloat16
     for t, n in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache"), (block_table, "block_table"),
                  (seq_lens, "seq_lens")):
         _check_input(t, n)
@@ -360,11 +363,12 @@ def forward_paged_decode_gqa_fp16(q, k_cache, v_cache, block_table, seq_lens, ma
          "max_num_blocks (row stride) is larger than block_table allows")
     lib = _lib.load()
     with torch.cuda.device(q.device):
-        out = torch.empty((B, H_Q, 1, D), dtype=q.dtype, device=q.device)
+        out = torch.empty((B, H_Q, 1, D), dtype=torch.bfloat16 if bf16_out else q.dtype, device=q.device)
         s = _stream_ptr(q.device)
         ws = _workspace(q.device, s, B, H_Q, H_KV, D)
         max_len = min(max_num_blocks, block_table.size(1)) * PAGE_BLOCK_SIZE
-        _lib.check(lib.fa_paged_decode_gqa_f16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table),
+        entry = lib.fa_paged_decode_gqa_f16_out_bf16 if bf16_out else lib.fa_paged_decode_gqa_f16
+        _lib.check(entry(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table),
                                                _ptr(seq_lens), B, H_Q, H_KV, D, k_cache.size(0), max_num_blocks,
                                                max_len, _ptr(ws), ws.numel(), ctypes.c_void_p(s)))
     return out
@@ -463,7 +467,7 @@ def forward_prefill_gqa_fp16_out(out, q, k, v, causal):
     return _prefill_gqa(out, q, k, v, causal)
 
 
-def _varlen(q, k, v, cu_seqlens, max_seqlen, causal, stream_int=None):
+def _varlen(q, k, v, cu_seqlens, max_seqlen, causal, stream_int=None, bf16_out=False):
     for t, n in ((q, "q"), (k, "k"), (v, "v"), (cu_seqlens, "cu_seqlens")):
         _check_input(t, n)
     # check_varlen_prefill_input_shapes (flash_attn_kernel.cu:195-219); the head-count
@@ -486,22 +490,26 @@ def _varlen(q, k, v, cu_seqlens, max_seqlen, causal, stream_int=None):
     _chk(batch > 0, "cu_seqlens must contain at least one sequence")
     lib = _lib.load()
     with torch.cuda.device(q.device):
-        out = torch.zeros_like(q)  # rows outside every sequence stay zero, as in the reference (:3373)
+        # rows outside every sequence stay zero, as in the reference (:3373)
+        out = torch.zeros(q.shape, dtype=torch.bfloat16 if bf16_out else q.dtype, device=q.device)
         s = _stream_ptr(q.device, stream_int)
         if stream_int is not None and stream_int != torch.cuda.current_stream(q.device).cuda_stream:
             # zeros_like ran on the current stream; order the foreign stream after it
             ev = torch.cuda.Event()
             ev.record()
             torch.cuda.ExternalStream(stream_int, device=q.device).wait_event(ev)
-        _lib.check(lib.fa_prefill_varlen_f16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens), batch, total,
-                                             H_Q, H_KV, D, max_seqlen, 1 if causal else 0, ctypes.c_void_p(s)))
+        entry = lib.fa_prefill_varlen_f16_out_bf16 if bf16_out else lib.fa_prefill_varlen_f16
+        _lib.check(entry(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens), batch, total,
+                         H_Q, H_KV, D, max_seqlen, 1 if causal else 0, ctypes.c_void_p(s)))
     return out
 
 
-def forward_varlen_prefill_fp16(q, k, v, cu_seqlens, max_seqlen, causal):
+def forward_varlen_prefill_fp16(q, k, v, cu_seqlens, max_seqlen, causal, out_dtype=None):
     """flash_attn_forward_varlen_prefill_fp16 (flash_attn_kernel.cu:3354-3387).
-    q [total,H_Q,D], k/v [total,H_KV,D] fp16 packed; cu_seqlens [batch+1] int32."""
-    return _varlen(q, k, v, cu_seqlens, max_seqlen, causal)
+    q [total,H_Q,D], k/v [total,H_KV,D] fp16 packed; cu_seqlens [batch+1] int32.
+    `out_dtype=torch.bfloat16` (an addition) returns the result rounded to bfloat16 instead of fp16."""
+    _chk(out_dtype in (None, torch.float16, torch.bfloat16), "out_dtype must be float16 or bfloat16")
+    return _varlen(q, k, v, cu_seqlens, max_seqlen, causal, bf16_out=out_dtype == torch.bfloat16)
 
 
 def forward_varlen_prefill_fp16_stream(q, k, v, cu_seqlens, max_seqlen, causal, stream_int):

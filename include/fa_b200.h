@@ -108,6 +108,18 @@ int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_ca
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * fa_paged_decode_gqa_f16 with the output stored as bfloat16 (same shape, 2 bytes per element): for
+ * callers whose activations are bfloat16, such as the decoder slice of this library, which would
+ * otherwise convert the fp16 result in a kernel of its own.  q and the caches stay fp16; the result is the
+ * same fp32 value rounded once to bfloat16.  No counterpart in the reference (its operators return fp16).
+ */
+int fa_paged_decode_gqa_f16_out_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                     const int32_t* block_table, const int32_t* seq_lens,
+                                     int B, int H_Q, int H_KV, int D,
+                                     int64_t num_pages, int block_table_stride, int64_t max_seq_len,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Paged GQA decode without any caller-provided scratch.  This entry point has no
  * counterpart in the reference project.
  *
@@ -254,6 +266,10 @@ int fa_prefill_dense_f16(const void* q, const void* k, const void* v, void* out,
 int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out,
                           const int32_t* cu_seqlens, int batch, int64_t total,
                           int H_Q, int H_KV, int D, int max_seqlen, int causal, void* stream);
+/* fa_prefill_varlen_f16 with the output stored as bfloat16 (see fa_paged_decode_gqa_f16_out_bf16). */
+int fa_prefill_varlen_f16_out_bf16(const void* q, const void* k, const void* v, void* out,
+                          const int32_t* cu_seqlens, int batch, int64_t total,
+                          int H_Q, int H_KV, int D, int max_seqlen, int causal, void* stream);
 
 /*
  * Fused rotary embedding + KV append into pages: the write side of the paged cache for one
@@ -299,6 +315,16 @@ int fa_add_rmsnorm_bf16(void* x, const void* delta, const void* weight, void* ou
 int fa_qk_norm_split_f16(const void* qkv, const void* q_weight, const void* k_weight, void* q,
                          void* k, void* v, int64_t T, int H_Q, int H_KV, int D, float eps,
                          void* stream);
+/* fa_qk_norm_split_f16 and fa_rope_append_paged_f16 (full rotary, rot_dim == D) in one launch, value
+ * for value the same arithmetic: qkv [T, (H_Q + 2 H_KV) * D] bf16 -> per-head RMSNorm of q and k (weights may
+ * be NULL) -> fp16 -> rotary embedding -> q_out [T,H_Q,D]; k and v go to the paged cache (when given) and,
+ * optionally, to k_out / v_out [T,H_KV,D] (the packed prefill attention reads those).  cos / sin [T, D] fp32;
+ * positions / cu_seqlens / block_table as in fa_rope_append_paged_f16. */
+int fa_qkv_rope_append_f16(const void* qkv, const void* q_weight, const void* k_weight, const float* cos,
+                           const float* sin, void* q_out, void* k_out, void* v_out, void* k_cache,
+                           void* v_cache, const int32_t* block_table, const int32_t* positions,
+                           const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV, int D, float eps,
+                           int64_t num_pages, int block_table_stride, void* stream);
 int fa_silu_mul_bf16(const void* gate_up, void* out, int64_t T, int I, void* stream);
 int fa_half_to_bf16(const void* in, void* out, int64_t n, void* stream);
 

@@ -314,3 +314,38 @@ def test_head_dimensions_between_the_builds(fa, D):
     assert torch.equal(scores.cpu()[:, :, :71], ref_dots[:, :, :71])
     assert _err(out, ref_out) < TOL
     _finish(fa)
+
+
+def test_bf16_output_variants_round_the_same_fp32_result(fa):
+    """`out_dtype=torch.bfloat16` (paged decode, varlen prefill): the same fp32 result rounded once to
+    bfloat16 - within one bfloat16 rounding (2^-9 relative) of the oracle's fp32 value plus the usual 2e-3."""
+    w = orc.make_paged_workload(B=5, H_Q=32, H_KV=8, D=128, min_len=1, max_len=500, seed=3)
+    args = (w["q"].cuda(), w["k_cache"].cuda(), w["v_cache"].cuda(), w["block_table"].cuda(), w["seq_lens"].cuda(),
+            w["max_num_blocks"])
+    out16 = fa.forward_paged_decode_gqa_fp16(*args)
+    outb = fa.forward_paged_decode_gqa_fp16(*args, out_dtype=torch.bfloat16)
+    assert outb.dtype == torch.bfloat16 and outb.shape == out16.shape
+    ref = orc.paged_decode(w["q"], w["k_cache"], w["v_cache"], w["block_table"], w["seq_lens"], final_cast=False)
+    tol = TOL + ref.abs() * 2.0 ** -8
+    assert ((outb.float().cpu() - ref).abs() <= tol).all()
+    assert (outb.float() - out16.float()).abs().max().item() < 2.0 ** -7      # two roundings of values below 2
+    lens = [70, 1, 200, 33]
+    cu = torch.tensor([0, 70, 71, 271, 304], dtype=torch.int32)
+    g = torch.Generator().manual_seed(8)
+    q = torch.randn(304, 8, 128, generator=g).half()
+    k = torch.randn(304, 2, 128, generator=g).half()
+    v = torch.randn(304, 2, 128, generator=g).half()
+    for impl in (0, 1):                     # tcgen05 kernel and mma.sync kernel
+        flash_attn_v100_b200_set_impl(impl)
+        outb = fa.forward_varlen_prefill_fp16(q.cuda(), k.cuda(), v.cuda(), cu.cuda(), max(lens), True,
+                                              out_dtype=torch.bfloat16)
+        ref = orc.varlen_prefill(q, k, v, cu, True, final_cast=False)
+        assert outb.dtype == torch.bfloat16
+        assert ((outb.float().cpu() - ref).abs() <= TOL + ref.abs() * 2.0 ** -8).all(), impl
+    flash_attn_v100_b200_set_impl(0)
+    _finish(fa)
+
+
+def flash_attn_v100_b200_set_impl(impl):
+    import flash_attn_v100_b200
+    flash_attn_v100_b200.set_prefill_impl(impl)

@@ -45,6 +45,32 @@ def test_engine_matches_oracle_logits_and_tokens():
     pkg.check_async_errors(); pkg.check_prefill_errors()
 
 
+def test_fused_qkv_kernel_is_bit_identical_to_the_two_kernels_it_replaces():
+    """QK-norm + cast + rotary + append in one launch against the norm kernel followed by the rotary/append
+    kernel: the same tokens and bit-identical logits, prompts (packed) and decode steps, and bit-identical
+    cache pages."""
+    cfg, model, Runner = _setup(seed=11)
+    g = torch.Generator().manual_seed(6)
+    prompts = torch.randint(0, cfg.vocab_size, (3, 37), generator=g)
+    out = {}
+    for fused in (True, False):
+        model.fused_qkv = fused
+        logs = []
+        r = Runner(model, max_batch=4, max_seq_len=64, use_cuda_graph=False)
+        toks = r.generate(prompts, 9, prefill_chunk=2, logits_out=logs)
+        torch.cuda.synchronize()
+        out[fused] = (toks.clone(), [lg.clone() for _, _, lg in logs], [kp.clone() for kp in r.kv.k_pools],
+                      [vp.clone() for vp in r.kv.v_pools])
+    model.fused_qkv = True
+    assert torch.equal(out[True][0], out[False][0])
+    for a, b in zip(out[True][1], out[False][1]):
+        assert torch.equal(a, b)
+    for a, b in zip(out[True][2] + out[True][3], out[False][2] + out[False][3]):
+        assert torch.equal(a, b)
+    import flash_attn_v100_b200 as pkg
+    pkg.check_async_errors(); pkg.check_prefill_errors()
+
+
 def test_cuda_graph_replay_reproduces_eager_tokens():
     cfg, model, Runner = _setup(seed=7)
     g = torch.Generator().manual_seed(4)
