@@ -48,14 +48,15 @@ __device__ __forceinline__ void peer_barrier(const PeerPointers& pp, int rank, i
   __syncthreads();
   const int tid = threadIdx.x;
   if (tid < world) {
-    __threadfence_system();   // this CTA's stores (ordered before by the CTA barrier) precede the flag
+    // The release store at system scope orders this CTA's earlier stores before the flag: the other threads'
+    // stores were made visible to this thread by the CTA barrier above, and a release is cumulative over them.
     st_release_sys(pp.flags[tid] + flag_index(phase, blockIdx.x, rank), e);
     const uint32_t* mine = pp.flags[rank] + flag_index(phase, blockIdx.x, tid);
     bool ok = false;
     if (*reinterpret_cast<volatile int32_t*>(status) == 0) {
       for (unsigned int i = 0; i < max_polls; ++i) {
         if (ld_acquire_sys(mine) == e) { ok = true; break; }
-        __nanosleep(100);
+        if (i >= 64u) __nanosleep(100);   // the peers are usually within a few microseconds: spin first
       }
     }
     if (!ok) atomicOr(status, kPeerStatusTimeout);
@@ -89,6 +90,8 @@ peer_allreduce_bf16_kernel(const PeerPointers pp, const PeerState st, int rank, 
   peer_barrier(pp, rank, world, 0, e, st.status, st.max_polls);
   // slice `rank`: n_vec_per_slice 16-byte vectors, strided over the CTAs
   const long long v0 = (long long)rank * n_vec_per_slice;
+  // (the host picks the grid so that a thread has one or two vectors: every remote load of the slice is in
+  // flight at once and the pass costs one NVLink round trip)
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec_per_slice;
        v += (long long)gridDim.x * blockDim.x) {
     float acc[8];

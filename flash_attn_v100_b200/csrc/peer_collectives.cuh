@@ -6,7 +6,7 @@
 namespace fa {
 
 constexpr int kPeerMaxWorld = 8;    // ranks of one NVLink domain served by these kernels
-constexpr int kPeerMaxCtas = 32;    // CTAs of one collective launch (each has its own flags)
+constexpr int kPeerMaxCtas = 128;   // CTAs of one collective launch (each has its own flags)
 constexpr size_t kPeerFlagBytes = 2 * kPeerMaxCtas * kPeerMaxWorld * sizeof(uint32_t);
 constexpr int kPeerStatusTimeout = 1;
 
