@@ -99,6 +99,22 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   return false;
 }
 
+// The same wait as a plain polling loop (mbarrier.test_wait never suspends the thread): tuning builds only.
+template <bool SPIN>
+__device__ __forceinline__ bool wait_sel(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if constexpr (!SPIN) {
+    return wait_or_abort(bar, parity, abort_flag);
+  } else {
+    for (uint32_t i = 0; i < (kTc5MaxPolls << 2); ++i) {
+      if (mbar_test_wait(bar, parity)) return true;
+      if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicOr(&g_prefill_status, kStatusWaitTimeout);
+    return false;
+  }
+}
+
 // Bounded wait that does not look at the abort flag: used on the way out, to let asynchronous copies and
 // MMAs that are still in flight finish before shared and tensor memory are given up.
 __device__ __forceinline__ void drain_wait(uint32_t bar, uint32_t parity) {
@@ -544,7 +560,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
         const int n_mine = it.n_kv[t];
         auto take_token = [&]() {
           if (!other_active) return;
-          PROF_WAIT(1 + t, 6, wait_or_abort(bar(B_TOKEN + t), tok_waits & 1u, abort_flag));
+          PROF_WAIT(1 + t, 6, wait_sel<(DBG & 64) != 0>(bar(B_TOKEN + t), tok_waits & 1u, abort_flag));
           ++tok_waits;
         };
         auto pass_token = [&]() {
@@ -571,9 +587,9 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
             const int st1 = (g + 1) % KV_STAGES;
             const uint32_t ph1 = ((g + 1) / KV_STAGES) & 1u;
             PROF_COUNT(1 + t, 14);
-            PROF_WAIT(1 + t, 3, wait_or_abort(bar(B_VFULL + st), ph, abort_flag));
-            if (more) PROF_WAIT(1 + t, 4, wait_or_abort(bar(B_KFULL + st1), ph1, abort_flag));
-            PROF_WAIT(1 + t, 5, wait_or_abort(bar(B_PFULL + t), blk & 1u, abort_flag));
+            PROF_WAIT(1 + t, 3, wait_sel<(DBG & 64) != 0>(bar(B_VFULL + st), ph, abort_flag));
+            if (more) PROF_WAIT(1 + t, 4, wait_sel<(DBG & 64) != 0>(bar(B_KFULL + st1), ph1, abort_flag));
+            PROF_WAIT(1 + t, 5, wait_sel<(DBG & 64) != 0>(bar(B_PFULL + t), blk & 1u, abort_flag));
             PROF_SINCE(1 + t, 9, 2 + t);      // P arrival (row 0's warp) -> seen by the MMA lane
             // tile 1's block j+1 follows tile 0's block j+1; tile 0's block j+1 follows tile 1's
             // block j, which exists unless tile 1 has already run out of KV tiles
@@ -613,7 +629,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           const uint32_t ph = (g / KV_STAGES) & 1u;
           PROF_WAIT(1 + t, 8, wait_or_abort(bar(B_KFULL + st), ph, abort_flag));
           if (lane == 0) mbar_arrive(bar(B_KEMPTY + st));
-          PROF_WAIT(1 + t, 8, wait_or_abort(bar(B_VFULL + st), ph, abort_flag));
+          PROF_WAIT(1 + t, 8, wait_sel<(DBG & 64) != 0>(bar(B_VFULL + st), ph, abort_flag));
           if (lane == 0) mbar_arrive(bar(B_VEMPTY + st));
         }
         kv_it += (uint32_t)it.n_max;
@@ -749,7 +765,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
       float m = 0.f, l = 0.f;
       for (int j = 0; j < n_mine; ++j, ++pph) {
         PROF_COUNT(3 + t, 14);
-        PROF_WAIT(3 + t, 1, wait_or_abort(bar(B_SFULL + t), sph & 1u, abort_flag));
+        PROF_WAIT(3 + t, 1, wait_sel<(DBG & 128) != 0>(bar(B_SFULL + t), sph & 1u, abort_flag));
         ++sph;
         if (j > 0) PROF_SINCE(3 + t, 8, t);   // commit issued by the MMA lane -> batch seen complete here
         PROF_MARK(prof_t_s);
@@ -1061,6 +1077,9 @@ Tc5Kernel sweep_kernel(int v) {
     case 12: return prefill_tc5_kernel<D, 0, 1, 32>;       // no turn taking between the tiles
     case 13: return prefill_tc5_kernel<D, 2, 1, 32>;
     case 11: return prefill_tc5_kernel<D, 1, 1>;
+    case 14: return prefill_tc5_kernel<D, 0, 1, 64>;       // the MMA lanes poll without suspending
+    case 15: return prefill_tc5_kernel<D, 0, 1, 128>;      // the softmax threads poll the score barrier without suspending
+    case 16: return prefill_tc5_kernel<D, 0, 1, 192>;
     default: return prefill_tc5_kernel<D, 0, 0>;
   }
 }
