@@ -101,6 +101,26 @@ class PeerCollectives:
                                                        self._offset_of(t), t.numel(), self._stream()))
         return t
 
+    def all_reduce_add_rmsnorm_(self, part: torch.Tensor, x: torch.Tensor, h: torch.Tensor, weight: torch.Tensor,
+                                eps: float) -> torch.Tensor:
+        """x += sum over the ranks of `part`; h = rmsnorm(x) * weight — one kernel, x and h identical on every
+        rank afterwards.  part, x, h: [rows, cols] bf16 views of the buffer (same views on every rank, rows a
+        multiple of the world size); weight [cols] bf16 anywhere on this device.  Bit-identical to
+        `all_reduce_(part)` followed by the add + RMS norm kernel."""
+        if not (part.dtype == x.dtype == h.dtype == weight.dtype == torch.bfloat16):
+            raise TypeError("all_reduce_add_rmsnorm_ takes bfloat16")
+        if part.dim() != 2 or part.shape != x.shape or part.shape != h.shape or weight.numel() != part.size(1):
+            raise ValueError("part, x and h must be [rows, cols] of one shape and weight [cols]")
+        if part.size(0) % self.world != 0:
+            raise ValueError("rows must be a multiple of the world size")
+        if not weight.is_contiguous() or weight.device != self.device:
+            raise ValueError("weight must be contiguous on this rank's device")
+        _lib.check(self.lib.fa_peer_allreduce_add_rmsnorm_bf16(
+            self._data, self._flags, self._state, self.rank, self.world, self._offset_of(part), self._offset_of(x),
+            self._offset_of(h), part.size(0), part.size(1), ctypes.c_void_p(weight.data_ptr()), float(eps),
+            self._stream()))
+        return h
+
     def all_gather_into(self, out: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
         """`out` [world, ...] (a view of the buffer) receives `src` of every rank at index rank."""
         nbytes = src.numel() * src.element_size()

@@ -828,6 +828,30 @@ int fa_peer_allreduce_sum_bf16(void* const* data_ptrs, void* const* flag_ptrs, v
   return FA_OK;
 }
 
+int fa_peer_allreduce_add_rmsnorm_bf16(void* const* data_ptrs, void* const* flag_ptrs, void* state, int rank, int world,
+                                       int64_t part_offset_bytes, int64_t x_offset_bytes, int64_t h_offset_bytes,
+                                       int64_t rows, int cols, const void* weight, float eps, void* stream) {
+  fa::PeerPointers pp;
+  fa::PeerState st;
+  int rc = fill_peer_args(data_ptrs, flag_ptrs, state, rank, world, &pp, &st);
+  if (rc != FA_OK) return rc;
+  FA_REQUIRE(weight, "null weight pointer");
+  FA_REQUIRE(part_offset_bytes >= 0 && x_offset_bytes >= 0 && h_offset_bytes >= 0 && part_offset_bytes % 16 == 0 &&
+                 x_offset_bytes % 16 == 0 && h_offset_bytes % 16 == 0,
+             "region offsets must be non-negative multiples of 16");
+  FA_REQUIRE(rows > 0 && rows % world == 0 && rows <= (1 << 24), "rows must be a positive multiple of world");
+  FA_REQUIRE(cols > 0 && cols % 8 == 0 && cols <= 16384, "cols must be a multiple of 8, at most 16384");
+  const int64_t bytes = rows * (int64_t)cols * 2;
+  auto apart = [bytes](int64_t a, int64_t b) { return a + bytes <= b || b + bytes <= a; };
+  FA_REQUIRE(apart(part_offset_bytes, x_offset_bytes) && apart(part_offset_bytes, h_offset_bytes) &&
+                 apart(x_offset_bytes, h_offset_bytes),
+             "the three regions must not overlap");
+  FA_CUDA(fa::launch_peer_allreduce_add_rmsnorm(pp, st, rank, world, part_offset_bytes, x_offset_bytes,
+                                                h_offset_bytes, (int)rows, cols, weight, eps,
+                                                static_cast<cudaStream_t>(stream)));
+  return FA_OK;
+}
+
 int fa_peer_allgather(void* const* data_ptrs, void* const* flag_ptrs, void* state, int rank, int world, const void* src,
                       int64_t offset_bytes, int64_t chunk_bytes, void* stream) {
   fa::PeerPointers pp;

@@ -125,6 +125,96 @@ peer_allreduce_bf16_kernel(const PeerPointers pp, const PeerState st, int rank, 
   end_epoch(st, e);
 }
 
+// All-reduce of a row-parallel GEMM output fused with the residual add and the RMS norm that follow it in a
+// decoder block:   delta = bf16(sum over ranks of part[rank]);  x = bf16(x + delta);  h = rmsnorm(x) * w.
+// part, x and h are [rows, cols] bf16 regions of the peer buffers.  The slices of the all-reduce are whole
+// rows (rows is a multiple of world): the rank that reduces a row holds all of it, so it also owns the
+// row's sum of squares, and it stores the new x and h rows into every rank's buffer.  One CTA of 256
+// threads per row (in turn), a thread keeps up to eight 16-byte chunks.  Thread layout, accumulation order
+// and roundings repeat the separate all-reduce and add + norm kernels operation by operation (the sum is
+// rounded to bf16 before it is added), so the results are bit-identical to theirs.
+__global__ void __launch_bounds__(256)
+peer_allreduce_add_rmsnorm_kernel(const PeerPointers pp, const PeerState st, int rank, int world,
+                                  long long part_off, long long x_off, long long h_off, int rows_per_rank, int cols,
+                                  const __nv_bfloat16* __restrict__ w, float eps) {
+  __shared__ float red[8];
+  const uint32_t e = begin_epoch(st);
+  peer_barrier(pp, rank, world, 0, e, st.status, st.max_polls);
+  const int nchunk = cols >> 3;
+  for (int r = blockIdx.x; r < rows_per_rank; r += gridDim.x) {
+    const long long row_bytes = ((long long)rank * rows_per_rank + r) * (long long)cols * 2;
+    uint4 keep[8];
+    float ss = 0.f;
+    int n = 0;
+    for (int c = threadIdx.x; c < nchunk; c += blockDim.x, ++n) {
+      const long long off = row_bytes + (long long)c * 16;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      uint4 in[kPeerMaxWorld];
+#pragma unroll
+      for (int p = 0; p < kPeerMaxWorld; ++p)
+        if (p < world) in[p] = __ldcg(reinterpret_cast<const uint4*>(pp.data[p] + part_off + off));
+      uint4 xv = __ldcg(reinterpret_cast<const uint4*>(pp.data[rank] + x_off + off));
+#pragma unroll
+      for (int p = 0; p < kPeerMaxWorld; ++p) {
+        if (p < world) {
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&in[p]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h2[i]);
+            acc[2 * i] += f.x;
+            acc[2 * i + 1] += f.y;
+          }
+        }
+      }
+      __nv_bfloat16* xh = reinterpret_cast<__nv_bfloat16*>(&xv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float d = __bfloat162float(__float2bfloat16(acc[i]));      // the all-reduce's bf16 result
+        xh[i] = __float2bfloat16(__bfloat162float(xh[i]) + d);           // residual add, rounded to bf16
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float f = __bfloat162float(xh[i]);
+        ss += f * f;
+      }
+      keep[n] = xv;
+#pragma unroll
+      for (int p = 0; p < kPeerMaxWorld; ++p)
+        if (p < world) *reinterpret_cast<uint4*>(pp.data[p] + x_off + off) = xv;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __syncthreads();                      // the previous row's readers of `red` are done
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+    const float inv = rsqrtf(tot / (float)cols + eps);
+    n = 0;
+    for (int c = threadIdx.x; c < nchunk; c += blockDim.x, ++n) {
+      const long long off = row_bytes + (long long)c * 16;
+      const uint4 wv = *reinterpret_cast<const uint4*>(w + (long long)c * 8);
+      const __nv_bfloat16* wh = reinterpret_cast<const __nv_bfloat16*>(&wv);
+      const __nv_bfloat16* xh = reinterpret_cast<const __nv_bfloat16*>(&keep[n]);
+      uint4 ov;
+      __nv_bfloat16* oh = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        // normalise in fp32, cast to bf16, then multiply by the weight (as the separate norm kernel does)
+        const __nv_bfloat16 nb = __float2bfloat16(__bfloat162float(xh[i]) * inv);
+        oh[i] = __float2bfloat16(__bfloat162float(wh[i]) * __bfloat162float(nb));
+      }
+#pragma unroll
+      for (int p = 0; p < kPeerMaxWorld; ++p)
+        if (p < world) *reinterpret_cast<uint4*>(pp.data[p] + h_off + off) = ov;
+    }
+  }
+  peer_barrier(pp, rank, world, 1, e, st.status, st.max_polls);
+  end_epoch(st, e);
+}
+
 __global__ void __launch_bounds__(256)
 peer_allgather_kernel(const PeerPointers pp, const PeerState st, int rank, int world, const uint8_t* src,
                       long long offset_bytes, long long chunk_bytes) {
@@ -148,6 +238,18 @@ cudaError_t launch_peer_allreduce_bf16(const PeerPointers& pp, const PeerState& 
   if (ctas < 1) ctas = 1;
   if (ctas > kPeerMaxCtas) ctas = kPeerMaxCtas;
   peer_allreduce_bf16_kernel<<<ctas, 512, 0, stream>>>(pp, st, rank, world, offset_bytes, n_vec_per_slice);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_allreduce_add_rmsnorm(const PeerPointers& pp, const PeerState& st, int rank, int world,
+                                              long long part_off, long long x_off, long long h_off, int rows, int cols,
+                                              const void* w, float eps, cudaStream_t stream) {
+  const int rows_per_rank = rows / world;
+  int ctas = rows_per_rank < kPeerMaxCtas ? rows_per_rank : kPeerMaxCtas;
+  if (ctas < 1) ctas = 1;
+  peer_allreduce_add_rmsnorm_kernel<<<ctas, 256, 0, stream>>>(pp, st, rank, world, part_off, x_off, h_off,
+                                                              rows_per_rank, cols,
+                                                              static_cast<const __nv_bfloat16*>(w), eps);
   return cudaGetLastError();
 }
 

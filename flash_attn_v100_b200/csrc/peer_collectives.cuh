@@ -27,6 +27,12 @@ struct PeerState {                  // local device memory of this rank
 cudaError_t launch_peer_allreduce_bf16(const PeerPointers& pp, const PeerState& st, int rank, int world,
                                        long long offset_bytes, long long n_elems, int ctas, cudaStream_t stream);
 
+// delta = sum over ranks of the [rows, cols] bf16 region at part_off; x (region at x_off) += delta;
+// h (region at h_off) = rmsnorm(x) * w, in every rank's buffer.  rows % world == 0, cols % 8 == 0, cols <= 16384.
+cudaError_t launch_peer_allreduce_add_rmsnorm(const PeerPointers& pp, const PeerState& st, int rank, int world,
+                                              long long part_off, long long x_off, long long h_off, int rows, int cols,
+                                              const void* w, float eps, cudaStream_t stream);
+
 // Rank r's `chunk_bytes` at `src` (local memory) end up at offset_bytes + r * chunk_bytes of every
 // rank's data buffer.  chunk_bytes must be a multiple of 4.
 cudaError_t launch_peer_allgather(const PeerPointers& pp, const PeerState& st, int rank, int world, const void* src,

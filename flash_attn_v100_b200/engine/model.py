@@ -37,6 +37,9 @@ class TPDecoder:
         # one launch for QK-norm + cast + rotary + cache append (False: the norm kernel and the rotary/append
         # kernel one after the other; same values, kept for the parity test of the fused kernel)
         self.fused_qkv = True
+        # the decode step's all-reduces take the residual add and the RMS norm that follow them into the same
+        # kernel (False: all-reduce, then the add + norm kernel; same values, kept for the parity test)
+        self.fused_norm = True
         self.device = torch.device(device)
         self.ql = cfg.num_heads // world
         self.kl = cfg.num_kv_heads // world
@@ -111,8 +114,12 @@ class TPDecoder:
         nbytes = (T * self.cfg.hidden_size * 2 + 255) // 256 * 256
         if 2 * nbytes > c.data_bytes or (T * self.cfg.hidden_size) % (8 * self.world) != 0:
             return None
-        return (c.view(0, (T, self.cfg.hidden_size), torch.bfloat16),
-                c.view(nbytes, (T, self.cfg.hidden_size), torch.bfloat16))
+        views = [c.view(i * nbytes, (T, self.cfg.hidden_size), torch.bfloat16) for i in range(2)]
+        # with room for two more regions (residual stream and normed activations) and whole rows per rank, the
+        # all-reduces also do the residual add and the norm
+        if self.fused_norm and 4 * nbytes <= c.data_bytes and T % self.world == 0 and self.cfg.hidden_size <= 16384:
+            views += [c.view(i * nbytes, (T, self.cfg.hidden_size), torch.bfloat16) for i in (2, 3)]
+        return tuple(views)
 
     def rope_tables(self, positions):
         """fp32 cos/sin [T, D] exactly as the reference computes them (rope.py:228-266)."""
@@ -132,9 +139,15 @@ class TPDecoder:
         st = {"delta": None}
         peer = None if prefill else self._peer_rows(token_ids.numel())
         st["peer"] = peer
+        fused = peer is not None and len(peer) == 4    # peer[2]: residual stream x, peer[3]: normed activations h
+        n_layers = len(self.w["layers"])
 
         def first():
-            st["x"] = self.w["embed"][token_ids]                          # [T, hidden] bf16
+            if fused:
+                st["x"] = torch.index_select(self.w["embed"], 0, token_ids, out=peer[2])
+                st["h"] = self._add_rmsnorm(st["x"], None, self.w["layers"][0]["ln1"])
+            else:
+                st["x"] = self.w["embed"][token_ids]                      # [T, hidden] bf16
             st["cos"], st["sin"] = self.rope_tables(positions)
             # decode: lengths including the new token (derived here so that a replayed step recomputes them)
             st["lens"] = seq_lens_after if (prefill or seq_lens_after is not None) else slots + 1
@@ -143,7 +156,8 @@ class TPDecoder:
         for l, lw in enumerate(self.w["layers"]):
             def attention_half(l=l, lw=lw):
                 x = st["x"]
-                h = self._add_rmsnorm(x, st["delta"], lw["ln1"])         # x += delta (previous MLP); h = ln1(x)
+                # x += delta (previous MLP); h = ln1(x) — done by the previous all-reduce on the fused path
+                h = st["h"] if fused else self._add_rmsnorm(x, st["delta"], lw["ln1"])
                 qkv = h @ lw["wqkv"].t()
                 if self.fused_qkv:
                     q_rot, k_rot, v = self._qkv_rope_append(qkv, lw, st["cos"], st["sin"], kv.k_pools[l], kv.v_pools[l],
@@ -169,20 +183,31 @@ class TPDecoder:
                 a = attn.reshape(x.size(0), self.ql * cfg.head_dim)   # bf16 straight from the attention epilogue
                 if peer is None:
                     st["o"] = a @ lw["wo"].t()
+                elif fused:                # GEMM into the peer buffer; sum over the ranks, x += sum, h = ln2(x)
+                    st["h"] = self.comm.all_reduce_add_rmsnorm_(torch.mm(a, lw["wo"].t(), out=peer[0]), peer[2],
+                                                                peer[3], lw["ln2"], cfg.rms_norm_eps)
                 else:                      # GEMM straight into the peer buffer, summed in place over the ranks
                     st["o"] = self.comm.all_reduce_(torch.mm(a, lw["wo"].t(), out=peer[0]))
 
-            def mlp_half(lw=lw):
-                h = self._add_rmsnorm(st["x"], st["o"], lw["ln2"])       # x += attention; h = ln2(x)
+            def mlp_half(l=l, lw=lw):
+                # x += attention; h = ln2(x) — done by the attention half's all-reduce on the fused path
+                h = st["h"] if fused else self._add_rmsnorm(st["x"], st["o"], lw["ln2"])
                 gu = h @ lw["wgu"].t()
                 if peer is None:
                     st["delta"] = self._silu_mul(gu) @ lw["wd"].t()
+                elif fused:                # ... x += sum, h = the next layer's ln1(x), or the final norm
+                    w_next = self.w["layers"][l + 1]["ln1"] if l + 1 < n_layers else self.w["final_ln"]
+                    st["h"] = self.comm.all_reduce_add_rmsnorm_(torch.mm(self._silu_mul(gu), lw["wd"].t(), out=peer[1]),
+                                                                peer[2], peer[3], w_next, cfg.rms_norm_eps)
                 else:
                     st["delta"] = self.comm.all_reduce_(torch.mm(self._silu_mul(gu), lw["wd"].t(), out=peer[1]))
 
             layers.append((attention_half, mlp_half))
 
         def last():
+            if fused:                      # the last all-reduce has applied the final norm
+                st["hidden"] = st["h"]
+                return
             if prefill:
                 idx = (cu_seqlens[1:] - 1).long()
                 x_last, d_last = st["x"][idx].contiguous(), st["delta"][idx].contiguous()

@@ -32,9 +32,11 @@ class GenerationRunner:
             from ..comm import PeerCollectives
             import torch.distributed as dist
             rows = (max_batch * cfg.hidden_size * 2 + 255) // 256 * 256
-            self._gather_off = 2 * rows
+            # four [max_batch, hidden] regions (the two row-parallel GEMM outputs, the residual stream and the
+            # normed activations of the fused all-reduce + norm) and the greedy candidates behind them
+            self._gather_off = 4 * rows
             model.comm = PeerCollectives(model.group if model.group is not None else dist.group.WORLD, model.device,
-                                         2 * rows + model.world * max_batch * 8)
+                                         4 * rows + model.world * max_batch * 8)
         self._side_stream = torch.cuda.Stream(device=model.device)   # decode runs here (one scratch workspace)
         # Under tensor parallelism prompt chunks are prefilled two at a time, each on its own stream and
         # advanced in turn from one all-reduce to the next, so that one chunk's NCCL all-reduce (134 MB per

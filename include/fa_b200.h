@@ -357,6 +357,16 @@ int fa_prefill_status(void* stream, int* host_status_out, int clear);
  *   offset_bytes of every rank's data buffer (n_elems a multiple of 8 * world);
  *   each element is reduced in fp32, in rank order, by one rank and stored to
  *   all: the result is bit-identical on every rank.
+ * fa_peer_allreduce_add_rmsnorm_bf16: the all-reduce of a row-parallel GEMM
+ *   output together with the residual add and the RMS norm that follow it in a
+ *   decoder block (decoder_layer.py:69-85, norm.py:7-34 of the reference's model
+ *   code).  Three [rows, cols] bf16 regions of the data buffers, at the same
+ *   offsets on every rank:  delta = bf16(sum over ranks of part);
+ *   x = bf16(x + delta);  h = rmsnorm(x, eps) * weight.  x and h end up
+ *   identical on every rank; part is left as it was.  rows a multiple of world,
+ *   cols a multiple of 8 (<= 16384), weight [cols] bf16 in local memory.  The
+ *   results are bit-identical to fa_peer_allreduce_sum_bf16 followed by
+ *   fa_add_rmsnorm_bf16.
  * fa_peer_allgather: rank r's chunk_bytes at `src` (local memory) are stored
  *   at offset_bytes + r * chunk_bytes of every rank's data buffer.
  * data_ptrs / flag_ptrs: host arrays of `world` device pointers in rank order
@@ -371,6 +381,10 @@ int fa_peer_free(void* data, void* flags, void* state);
 int fa_peer_allreduce_sum_bf16(void* const* data_ptrs, void* const* flag_ptrs, void* state,
                                int rank, int world, int64_t offset_bytes, int64_t n_elems,
                                void* stream);
+int fa_peer_allreduce_add_rmsnorm_bf16(void* const* data_ptrs, void* const* flag_ptrs, void* state,
+                                       int rank, int world, int64_t part_offset_bytes,
+                                       int64_t x_offset_bytes, int64_t h_offset_bytes, int64_t rows,
+                                       int cols, const void* weight, float eps, void* stream);
 int fa_peer_allgather(void* const* data_ptrs, void* const* flag_ptrs, void* state,
                       int rank, int world, const void* src, int64_t offset_bytes,
                       int64_t chunk_bytes, void* stream);

@@ -45,6 +45,39 @@ def main():
         if rank == 0:
             print(f"all-reduce {rows}x{cols}: exact {same}, identical across ranks {ident}", flush=True)
 
+    # ---- all-reduce + residual add + RMS norm in one kernel: bit-identical to the separate kernels ----
+    lib = _lib.load()
+    for rows, cols in [(world, 8), (8 * world, 4096), (4 * world, 1032), (32 * world, 2048 + 64)]:
+        n = rows * cols * 2
+        reg = (n + 255) // 256 * 256
+        part = pc.view(0, (rows, cols), torch.bfloat16)
+        xr = pc.view(reg, (rows, cols), torch.bfloat16)
+        hr = pc.view(2 * reg, (rows, cols), torch.bfloat16)
+        gs = torch.Generator(device=dev).manual_seed(7)          # the residual stream is the same on every rank
+        x0 = torch.randn(rows, cols, generator=gs, device=dev).bfloat16()
+        wn = (1.0 + 0.1 * torch.randn(cols, generator=gs, device=dev)).bfloat16()
+        p0 = torch.randn(rows, cols, generator=g, device=dev).bfloat16()
+        # separate kernels
+        part.copy_(p0)
+        pc.all_reduce_(part)
+        x_ref = x0.clone()
+        h_ref = torch.empty_like(x_ref)
+        _lib.check(lib.fa_add_rmsnorm_bf16(x_ref.data_ptr(), part.data_ptr(), wn.data_ptr(), h_ref.data_ptr(), rows, cols,
+                                           1e-6, torch.cuda.current_stream(dev).cuda_stream))
+        torch.cuda.synchronize()
+        dist.barrier()
+        # one kernel
+        part.copy_(p0)
+        xr.copy_(x0)
+        hr.zero_()
+        pc.all_reduce_add_rmsnorm_(part, xr, hr, wn, 1e-6)
+        torch.cuda.synchronize()
+        okf = torch.equal(xr, x_ref) and torch.equal(hr, h_ref) and torch.equal(part, p0)
+        ok &= okf
+        if rank == 0:
+            print(f"all-reduce + add + rmsnorm {rows}x{cols}: bit-identical to the separate kernels {okf}", flush=True)
+        dist.barrier()
+
     # ---- all-gather ----
     src = torch.randn(64, 2, generator=g, device=dev)
     out = pc.view(4 << 20, (world, 64, 2), torch.float32)

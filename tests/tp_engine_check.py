@@ -45,6 +45,17 @@ def main():
     print(f"[rank {rank}] peer-collective decode: graph equal to eager {peer_equal}, logit err vs NCCL run "
           f"{err_peer:.4f} / {err_peer_dec:.4f}", flush=True)
     graphs_equal = graphs_equal and peer_equal and err_peer < 3e-2 and err_peer_dec < 3e-2
+    # the same with the all-reduce, the residual add and the norm as separate kernels: bit-identical
+    m_sep = TPDecoder(cfg, w_tp, rank, world, None, f"cuda:{local}")
+    m_sep.fused_norm = False
+    ps = GenerationRunner(m_sep, 4, 64, peer_collectives=True)
+    logs_ps = []
+    toks_ps = ps.generate(prompts, 16, logits_out=logs_ps)
+    torch.cuda.synchronize()
+    ps.close()
+    fused_equal = torch.equal(toks_ps, toks_pr) and all(torch.equal(a[2], b[2]) for a, b in zip(logs_ps, logs_pr))
+    print(f"[rank {rank}] fused all-reduce + norm equal to the separate kernels: {fused_equal}", flush=True)
+    graphs_equal = graphs_equal and fused_equal
     # prompt chunks prefilled two at a time on two streams (one chunk's all-reduce overlaps the other's compute):
     # the same tokens as the same chunks prefilled one after the other
     toks_seq = tp.generate(prompts, 16, prefill_chunk=2, logits_out=[])
