@@ -52,6 +52,12 @@ SIGNATURES = {
     "fa_prefill_dense_f16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "fa_prefill_varlen_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _i, _vp]),
     "fa_prefill_varlen_f16_out_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _i, _vp]),
+    "fa_paged_decode_gqa_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i64, _i, _i64, _vp, _sz, _vp]),
+    "fa_decode_gqa_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "fa_prefill_dense_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "fa_prefill_varlen_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _i, _vp]),
+    "fa_rope_append_paged_bf16": (_i, [_vp] * 12 + [_i, _i, _i, _i, _i, _i, _i64, _i, _vp]),
+    "fa_qkv_rope_append_bf16": (_i, [_vp] * 13 + [_i, _i, _i, _i, _i, _c.c_float, _i64, _i, _vp]),
 }
 
 _lib = None

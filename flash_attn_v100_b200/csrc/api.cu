@@ -175,6 +175,7 @@ struct DecodeCall {
   long long num_pages, rows_total, max_units;
   bool int8;
   bool out_bf16;                     // output stored as bfloat16 instead of fp16
+  bool bf16;                         // q and the cache are bfloat16 (bfloat16 MMAs); implies out_bf16
   bool kv8;                          // int8 cache with fp16 per-token scales
   const void *k_scale_h, *v_scale_h;
   // sliding window + sink (contiguous fixed mode): see DecodeParams.  has_window = false: identity page map
@@ -207,7 +208,7 @@ int run_decode(const DecodeCall& c) {
   memset(&p, 0, sizeof(p));
   p.q = static_cast<const __half*>(c.q);
   p.out = static_cast<__half*>(c.out);
-  p.out_bf16 = c.out_bf16 ? 1 : 0;
+  p.out_bf16 = (c.out_bf16 || c.bf16) ? 1 : 0;
   p.block_table = c.block_table;
   p.lens = c.lens;
   p.q_scale = c.q_scale;
@@ -249,7 +250,7 @@ int run_decode(const DecodeCall& c) {
   rc = c.kv8 ? make_rows_map_u8(&vmap, c.v, c.rows_total, c.D) : make_rows_map(&vmap, c.v, c.rows_total, c.D, 16);
   if (rc != FA_OK) return rc;
   const size_t smem = fa::decode_smem_bytes(Dp, cfg.warps, cfg.stages, slot_rows, c.B, kv_elem_bytes);
-  const int kind = c.kv8 ? fa::kKindInt8KV : (c.int8 ? fa::kKindInt8QK : fa::kKindF16);
+  const int kind = c.kv8 ? fa::kKindInt8KV : (c.int8 ? fa::kKindInt8QK : (c.bf16 ? fa::kKindBF16 : fa::kKindF16));
   cudaError_t e = fa::launch_decode(kmap, vmap, p, Dp, kind, cfg.warps, smem, c.stream);
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, "decode launch failed: %s", cudaGetErrorString(e));
   return FA_OK;
@@ -362,7 +363,7 @@ int fa_decode_set_tuning(int warps, int stages, int ctas_per_sm) {
 static int paged_decode_impl(const void* q, const void* k_cache, const void* v_cache, void* out,
                              const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q, int H_KV, int D,
                              int64_t num_pages, int block_table_stride, int64_t max_seq_len, void* workspace,
-                             size_t workspace_bytes, void* stream, bool out_bf16) {
+                             size_t workspace_bytes, void* stream, bool out_bf16, bool bf16 = false) {
   int rc = check_paged_args(q, k_cache, v_cache, out, block_table, seq_lens, B, H_Q, H_KV, D, num_pages,
                             block_table_stride);
   if (rc != FA_OK) return rc;
@@ -378,8 +379,17 @@ static int paged_decode_impl(const void* q, const void* k_cache, const void* v_c
   c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * max_pages;
   c.int8 = false;
   c.out_bf16 = out_bf16;
+  c.bf16 = bf16;
   c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
   return run_decode(c);
+}
+
+int fa_paged_decode_gqa_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                             const int32_t* block_table, const int32_t* seq_lens, int B, int H_Q, int H_KV, int D,
+                             int64_t num_pages, int block_table_stride, int64_t max_seq_len, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  return paged_decode_impl(q, k_cache, v_cache, out, block_table, seq_lens, B, H_Q, H_KV, D, num_pages,
+                           block_table_stride, max_seq_len, workspace, workspace_bytes, stream, true, true);
 }
 
 int fa_paged_decode_gqa_f16(const void* q, const void* k_cache, const void* v_cache, void* out,
@@ -398,8 +408,9 @@ int fa_paged_decode_gqa_f16_out_bf16(const void* q, const void* k_cache, const v
                            block_table_stride, max_seq_len, workspace, workspace_bytes, stream, true);
 }
 
-int fa_decode_gqa_f16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N, int D,
-                      int causal, int cache_len, void* workspace, size_t workspace_bytes, void* stream) {
+static int decode_gqa_impl(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N,
+                           int D, int causal, int cache_len, void* workspace, size_t workspace_bytes, void* stream,
+                           bool bf16) {
   int rc = check_decode_common(q, k, v, out, B, H_Q, H_KV, D);
   if (rc != FA_OK) return rc;
   FA_REQUIRE(N > 0, "N must be positive");
@@ -413,8 +424,19 @@ int fa_decode_gqa_f16(const void* q, const void* k, const void* v, void* out, in
   c.bt_stride = 0; c.num_pages = 0;
   c.rows_total = (long long)B * H_KV * N;
   c.max_units = (long long)B * H_KV * ((H_Q / H_KV + 15) / 16) * ((c.fixed_len + 15) / 16);
+  c.bf16 = bf16;
   c.ws = workspace; c.ws_bytes = workspace_bytes; c.stream = static_cast<cudaStream_t>(stream);
   return run_decode(c);
+}
+
+int fa_decode_gqa_f16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N, int D,
+                      int causal, int cache_len, void* workspace, size_t workspace_bytes, void* stream) {
+  return decode_gqa_impl(q, k, v, out, B, H_Q, H_KV, N, D, causal, cache_len, workspace, workspace_bytes, stream, false);
+}
+
+int fa_decode_gqa_bf16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N, int D,
+                       int causal, int cache_len, void* workspace, size_t workspace_bytes, void* stream) {
+  return decode_gqa_impl(q, k, v, out, B, H_Q, H_KV, N, D, causal, cache_len, workspace, workspace_bytes, stream, true);
 }
 
 int fa_decode_sliding_window_gqa_f16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV,
@@ -577,7 +599,9 @@ static int run_prefill(fa::PrefillParams& p, int D, cudaStream_t stream) {
   const bool tc5_ok = fa::prefill_tc5_supported(p, D);
   if (g_prefill_impl == 2 && !tc5_ok)
     return fail(FA_ERR_UNSUPPORTED, "the tcgen05 prefill kernel supports D = 64 and 128 only");
-  if (tc5_ok && g_prefill_impl != 1) {
+  if (p.in_bf16 && !tc5_ok)
+    return fail(FA_ERR_UNSUPPORTED, "bfloat16 prefill is served by the tcgen05 kernel: head dimension up to 128");
+  if (tc5_ok && (g_prefill_impl != 1 || p.in_bf16)) {
     EncodeTiledFn enc;
     rc = get_encode(&enc);
     if (rc != FA_OK) return rc;
@@ -589,8 +613,8 @@ static int run_prefill(fa::PrefillParams& p, int D, cudaStream_t stream) {
   return FA_OK;
 }
 
-int fa_prefill_dense_f16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N,
-                         int D, int causal, void* stream) {
+static int prefill_dense_impl(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N,
+                              int D, int causal, void* stream, bool in_bf16) {
   int rc = check_decode_common(q, k, v, out, B, H_Q, H_KV, D);
   if (rc != FA_OK) return rc;
   FA_REQUIRE(N > 0, "N must be positive");
@@ -604,12 +628,23 @@ int fa_prefill_dense_f16(const void* q, const void* k, const void* v, void* out,
   p.q_batch_stride = (long long)H_Q * N * D; p.q_head_stride = (long long)N * D; p.q_tok_stride = D;
   p.kv_batch_stride = (long long)H_KV * N * D; p.kv_head_stride = (long long)N * D; p.kv_tok_stride = D;
   p.causal = causal ? 1 : 0;
+  p.in_bf16 = in_bf16 ? 1 : 0;
   return run_prefill(p, D, static_cast<cudaStream_t>(stream));
+}
+
+int fa_prefill_dense_f16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N,
+                         int D, int causal, void* stream) {
+  return prefill_dense_impl(q, k, v, out, B, H_Q, H_KV, N, D, causal, stream, false);
+}
+
+int fa_prefill_dense_bf16(const void* q, const void* k, const void* v, void* out, int B, int H_Q, int H_KV, int N,
+                          int D, int causal, void* stream) {
+  return prefill_dense_impl(q, k, v, out, B, H_Q, H_KV, N, D, causal, stream, true);
 }
 
 static int prefill_varlen_impl(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
                                int batch, int64_t total, int H_Q, int H_KV, int D, int max_seqlen, int causal,
-                               void* stream, bool out_bf16) {
+                               void* stream, bool out_bf16, bool in_bf16 = false) {
   int rc = check_decode_common(q, k, v, out, batch, H_Q, H_KV, D);
   if (rc != FA_OK) return rc;
   FA_REQUIRE(cu_seqlens != nullptr, "null cu_seqlens");
@@ -626,7 +661,15 @@ static int prefill_varlen_impl(const void* q, const void* k, const void* v, void
   p.kv_batch_stride = 0; p.kv_head_stride = D; p.kv_tok_stride = (long long)H_KV * D;
   p.causal = causal ? 1 : 0;
   p.out_bf16 = out_bf16 ? 1 : 0;
+  p.in_bf16 = in_bf16 ? 1 : 0;
   return run_prefill(p, D, static_cast<cudaStream_t>(stream));
+}
+
+int fa_prefill_varlen_bf16(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
+                           int batch, int64_t total, int H_Q, int H_KV, int D, int max_seqlen, int causal,
+                           void* stream) {
+  return prefill_varlen_impl(q, k, v, out, cu_seqlens, batch, total, H_Q, H_KV, D, max_seqlen, causal, stream, true,
+                             true);
 }
 
 int fa_prefill_varlen_f16(const void* q, const void* k, const void* v, void* out, const int32_t* cu_seqlens,
@@ -641,10 +684,10 @@ int fa_prefill_varlen_f16_out_bf16(const void* q, const void* k, const void* v, 
   return prefill_varlen_impl(q, k, v, out, cu_seqlens, batch, total, H_Q, H_KV, D, max_seqlen, causal, stream, true);
 }
 
-int fa_rope_append_paged_f16(const void* q, const void* k, const void* v, const float* cos, const float* sin,
-                             void* q_out, void* k_out, void* k_cache, void* v_cache, const int32_t* block_table,
-                             const int32_t* positions, const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV,
-                             int D, int rot_dim, int64_t num_pages, int block_table_stride, void* stream) {
+static int rope_append_impl(const void* q, const void* k, const void* v, const float* cos, const float* sin,
+                            void* q_out, void* k_out, void* k_cache, void* v_cache, const int32_t* block_table,
+                            const int32_t* positions, const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV,
+                            int D, int rot_dim, int64_t num_pages, int block_table_stride, void* stream, bool bf16) {
   FA_REQUIRE(q && k && v && cos && sin && q_out, "null tensor pointer");
   FA_REQUIRE(T >= 0 && batch > 0 && H_Q > 0 && H_KV > 0, "T must be >= 0; batch, H_Q, H_KV positive");
   FA_REQUIRE(D > 0 && D <= 256 && D % 8 == 0, "D must be a multiple of 8, at most 256");
@@ -671,17 +714,34 @@ int fa_rope_append_paged_f16(const void* q, const void* k, const void* v, const 
   p.block_table = block_table; p.positions = positions; p.cu_seqlens = cu_seqlens;
   p.T = T; p.batch = batch; p.H_Q = H_Q; p.H_KV = H_KV; p.D = D; p.rot_dim = rot_dim;
   p.bt_stride = block_table_stride; p.num_pages = num_pages;
+  p.bf16 = bf16 ? 1 : 0;
   FA_CUDA(fa::prefill_status_ptr(&p.status));
   cudaError_t e = fa::launch_rope_append(p, di.sm_count, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, "rope/append launch failed: %s", cudaGetErrorString(e));
   return FA_OK;
 }
 
-int fa_qkv_rope_append_f16(const void* qkv, const void* q_weight, const void* k_weight, const float* cos,
-                           const float* sin, void* q_out, void* k_out, void* v_out, void* k_cache, void* v_cache,
-                           const int32_t* block_table, const int32_t* positions, const int32_t* cu_seqlens, int T,
-                           int batch, int H_Q, int H_KV, int D, float eps, int64_t num_pages, int block_table_stride,
-                           void* stream) {
+int fa_rope_append_paged_f16(const void* q, const void* k, const void* v, const float* cos, const float* sin,
+                             void* q_out, void* k_out, void* k_cache, void* v_cache, const int32_t* block_table,
+                             const int32_t* positions, const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV,
+                             int D, int rot_dim, int64_t num_pages, int block_table_stride, void* stream) {
+  return rope_append_impl(q, k, v, cos, sin, q_out, k_out, k_cache, v_cache, block_table, positions, cu_seqlens, T,
+                          batch, H_Q, H_KV, D, rot_dim, num_pages, block_table_stride, stream, false);
+}
+
+int fa_rope_append_paged_bf16(const void* q, const void* k, const void* v, const float* cos, const float* sin,
+                              void* q_out, void* k_out, void* k_cache, void* v_cache, const int32_t* block_table,
+                              const int32_t* positions, const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV,
+                              int D, int rot_dim, int64_t num_pages, int block_table_stride, void* stream) {
+  return rope_append_impl(q, k, v, cos, sin, q_out, k_out, k_cache, v_cache, block_table, positions, cu_seqlens, T,
+                          batch, H_Q, H_KV, D, rot_dim, num_pages, block_table_stride, stream, true);
+}
+
+static int qkv_rope_append_impl(const void* qkv, const void* q_weight, const void* k_weight, const float* cos,
+                                const float* sin, void* q_out, void* k_out, void* v_out, void* k_cache, void* v_cache,
+                                const int32_t* block_table, const int32_t* positions, const int32_t* cu_seqlens, int T,
+                                int batch, int H_Q, int H_KV, int D, float eps, int64_t num_pages,
+                                int block_table_stride, void* stream, bool bf16) {
   FA_REQUIRE(qkv && cos && sin && q_out, "null tensor pointer");
   FA_REQUIRE(T >= 0 && batch > 0 && H_Q > 0 && H_KV > 0, "T must be >= 0; batch, H_Q, H_KV positive");
   if (!supported_d(D)) return fail(FA_ERR_UNSUPPORTED, "head dimension %d is not built (supported: 64, 128, 256)", D);
@@ -702,10 +762,31 @@ int fa_qkv_rope_append_f16(const void* qkv, const void* q_weight, const void* k_
   p.r.block_table = block_table; p.r.positions = positions; p.r.cu_seqlens = cu_seqlens;
   p.r.T = T; p.r.batch = batch; p.r.H_Q = H_Q; p.r.H_KV = H_KV; p.r.D = D; p.r.rot_dim = D;
   p.r.bt_stride = block_table_stride; p.r.num_pages = num_pages;
+  p.r.bf16 = bf16 ? 1 : 0;
   FA_CUDA(fa::prefill_status_ptr(&p.r.status));
   cudaError_t e = fa::launch_qkv_rope_append(p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(FA_ERR_CUDA, "qkv norm/rope/append launch failed: %s", cudaGetErrorString(e));
   return FA_OK;
+}
+
+int fa_qkv_rope_append_f16(const void* qkv, const void* q_weight, const void* k_weight, const float* cos,
+                           const float* sin, void* q_out, void* k_out, void* v_out, void* k_cache, void* v_cache,
+                           const int32_t* block_table, const int32_t* positions, const int32_t* cu_seqlens, int T,
+                           int batch, int H_Q, int H_KV, int D, float eps, int64_t num_pages, int block_table_stride,
+                           void* stream) {
+  return qkv_rope_append_impl(qkv, q_weight, k_weight, cos, sin, q_out, k_out, v_out, k_cache, v_cache, block_table,
+                              positions, cu_seqlens, T, batch, H_Q, H_KV, D, eps, num_pages, block_table_stride,
+                              stream, false);
+}
+
+int fa_qkv_rope_append_bf16(const void* qkv, const void* q_weight, const void* k_weight, const float* cos,
+                            const float* sin, void* q_out, void* k_out, void* v_out, void* k_cache, void* v_cache,
+                            const int32_t* block_table, const int32_t* positions, const int32_t* cu_seqlens, int T,
+                            int batch, int H_Q, int H_KV, int D, float eps, int64_t num_pages, int block_table_stride,
+                            void* stream) {
+  return qkv_rope_append_impl(qkv, q_weight, k_weight, cos, sin, q_out, k_out, v_out, k_cache, v_cache, block_table,
+                              positions, cu_seqlens, T, batch, H_Q, H_KV, D, eps, num_pages, block_table_stride,
+                              stream, true);
 }
 
 int fa_add_rmsnorm_bf16(void* x, const void* delta, const void* weight, void* out, int64_t rows, int cols, float eps,

@@ -115,15 +115,24 @@ __device__ __forceinline__ int seq_len_of(const DecodeParams& p, int b) {
 
 // MMA on the query-head block.  HM ("half M"): the block has at most 8 heads, so fragment rows 8-15 are
 // all-zero padding: their A registers are passed as zero and their accumulators are not kept.
-template <bool HM>
+template <bool HM, bool BF = false>
 __device__ __forceinline__ void mma_rows(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  if constexpr (HM) {
+  if constexpr (HM && BF) {
+    float d2, d3;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, "
+        "{%0,%1,%9,%9};"
+        : "+f"(c[0]), "+f"(c[1]), "=f"(d2), "=f"(d3)
+        : "r"(a[0]), "r"(0u), "r"(a[2]), "r"(b0), "r"(b1), "f"(0.f));
+  } else if constexpr (HM) {
     float d2, d3;
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, "
         "{%0,%1,%9,%9};"
         : "+f"(c[0]), "+f"(c[1]), "=f"(d2), "=f"(d3)
         : "r"(a[0]), "r"(0u), "r"(a[2]), "r"(b0), "r"(b1), "f"(0.f));
+  } else if constexpr (BF) {
+    mma_bf16_16816(c, a, b0, b1);
   } else {
     mma_f16_16816(c, a, b0, b1);
   }
@@ -269,7 +278,7 @@ template <int D, int KIND, bool HM>
 struct DecodeOccupancy {
   static constexpr int kThreads = HM ? 128 : 256;
   static constexpr int kMinBlocks =
-      !HM ? 1 : (D == 64 ? 4 : (D == 256 ? 2 : (KIND == kKindF16 ? FA_F16_MINB : (KIND == kKindInt8KV ? FA_KV8_MINB : FA_I8QK_MINB))));
+      !HM ? 1 : (D == 64 ? 4 : (D == 256 ? 2 : ((KIND == kKindF16 || KIND == kKindBF16) ? FA_F16_MINB : (KIND == kKindInt8KV ? FA_KV8_MINB : FA_I8QK_MINB))));
 };
 
 template <int D, int KIND, bool HM>
@@ -278,6 +287,7 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
                       const __grid_constant__ CUtensorMap vmap, const DecodeParams p) {
   constexpr bool INT8 = KIND == kKindInt8QK;   // fp16 cache, K and Q quantised on the fly for the scores
   constexpr bool KV8 = KIND == kKindInt8KV;    // int8 cache with per-token fp16 scales
+  constexpr bool BF = KIND == kKindBF16;       // bfloat16 q / cache: the fp16 path with bfloat16 MMAs and P
   constexpr int NR = HM ? 2 : 4;               // live accumulator registers per fragment (rows g | g, g + 8)
   constexpr int PAGE_BYTES = 16 * D * (KV8 ? 1 : 2);
   // One TMA box: 16 rows x 128 bytes (64 fp16 or 128 int8 columns), 128-byte swizzle;
@@ -645,8 +655,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           const uint32_t addr = kbase + (chunk >> 3) * SLAB_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
           uint32_t kb[4];
           ldmatrix_x4(kb, addr);
-          mma_rows<HM>(s[0], qa[kk], kb[0], kb[1]);
-          mma_rows<HM>(s[1], qa[kk], kb[2], kb[3]);
+          mma_rows<HM, BF>(s[0], qa[kk], kb[0], kb[1]);
+          mma_rows<HM, BF>(s[1], qa[kk], kb[2], kb[3]);
         }
 #pragma unroll
         for (int j = 0; j < 2; ++j)
@@ -779,8 +789,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
       l0 = l0 * a0 + (pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1]);
       float a1 = 1.f;
       uint32_t pa[4];
-      pa[0] = pack_half2(pr[0][0], pr[0][1]);
-      pa[2] = pack_half2(pr[1][0], pr[1][1]);
+      pa[0] = BF ? pack_bf162(pr[0][0], pr[0][1]) : pack_half2(pr[0][0], pr[0][1]);
+      pa[2] = BF ? pack_bf162(pr[1][0], pr[1][1]) : pack_half2(pr[1][0], pr[1][1]);
       pa[1] = pa[3] = 0u;
       if constexpr (!HM) {
         float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
@@ -795,8 +805,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           pr[j][3] = fast_exp2(s[j][3] - mn1);
         }
         l1 = l1 * a1 + (pr[0][2] + pr[0][3] + pr[1][2] + pr[1][3]);
-        pa[1] = pack_half2(pr[0][2], pr[0][3]);
-        pa[3] = pack_half2(pr[1][2], pr[1][3]);
+        pa[1] = BF ? pack_bf162(pr[0][2], pr[0][3]) : pack_half2(pr[0][2], pr[0][3]);
+        pa[3] = BF ? pack_bf162(pr[1][2], pr[1][3]) : pack_half2(pr[1][2], pr[1][3]);
       }
       if (__any_sync(0xffffffffu, (a0 != 1.f) || (a1 != 1.f))) {
 #pragma unroll
@@ -854,8 +864,8 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
           const uint32_t addr = vbase + (chunk >> 3) * SLAB_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
           uint32_t vb[4];
           ldmatrix_x4_trans(vb, addr);
-          mma_rows<HM>(acc[2 * c2], pa, vb[0], vb[1]);
-          mma_rows<HM>(acc[2 * c2 + 1], pa, vb[2], vb[3]);
+          mma_rows<HM, BF>(acc[2 * c2], pa, vb[0], vb[1]);
+          mma_rows<HM, BF>(acc[2 * c2 + 1], pa, vb[2], vb[3]);
         }
       }
 
@@ -1057,6 +1067,7 @@ cudaError_t launch_decode(const CUtensorMap& kmap, const CUtensorMap& vmap, cons
   case DD:                                               \
     if (kind == kKindInt8QK) { FA_DECODE_KIND(DD, kKindInt8QK) } \
     if (kind == kKindInt8KV) { FA_DECODE_KIND(DD, kKindInt8KV) } \
+    if (kind == kKindBF16) { FA_DECODE_KIND(DD, kKindBF16) } \
     FA_DECODE_KIND(DD, kKindF16)
   switch (D) {
     FA_DECODE_CASE(64)

@@ -17,10 +17,11 @@ enum DecodeKind : int {
   kKindF16 = 0,     // fp16 cache, fp16 arithmetic
   kKindInt8QK = 1,  // fp16 cache; Q and K quantised in the kernel, integer score dot products
   kKindInt8KV = 2,  // int8 cache with one fp16 scale per token, dequantised in the kernel
+  kKindBF16 = 3,    // bfloat16 q and cache, bfloat16 MMAs (P rounded to bfloat16), bfloat16 output
 };
 
 struct DecodeParams {
-  const __half* q;             // [B, H_Q, 1, D]
+  const __half* q;             // [B, H_Q, 1, D] (bfloat16 bits for kKindBF16, like the cache behind the tensor maps)
   __half* out;                 // [B, H_Q, 1, D]: fp16, or bfloat16 bits when out_bf16 is set
   int out_bf16;
   const int32_t* block_table;  // paged only

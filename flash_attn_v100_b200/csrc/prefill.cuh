@@ -13,6 +13,7 @@ struct PrefillParams {
   const __half* v;
   __half* out;                // fp16, or bfloat16 bits when out_bf16 is set
   int out_bf16;
+  int in_bf16;                // q, k, v are bfloat16 (tcgen05 kernel only: bfloat16 MMAs, P rounded to bfloat16)
   const int32_t* cu_seqlens;  // null => dense [B,H,N,D]; else packed [total,H,D]
   int batch;                  // sequences (dense: B)
   int H_Q, H_KV;

@@ -250,7 +250,7 @@ __device__ __forceinline__ constexpr bool pair_uses_poly(int i) {
 
 // One 32-column chunk of a score row: P = exp2(s * scale - m) as fp16 pairs, written to tensor memory at
 // `taddr` (16 columns); the fp32 sum of the chunk is added to `rs`.
-template <int NPOLY, int DBG = 0>
+template <int NPOLY, int DBG = 0, bool BF = false>
 __device__ __forceinline__ void exp_chunk_store(const float (&s)[32], float2 sc2, float2 nm2, float2& rs,
                                                 uint32_t taddr) {
   uint32_t pk[16];
@@ -267,7 +267,7 @@ __device__ __forceinline__ void exp_chunk_store(const float (&s)[32], float2 sc2
       e.y = fast_exp2(x.y);
     }
     rs = fadd2(rs, e);
-    pk[i] = (DBG & 8) ? __float_as_uint(e.x) : pack_half2(e.x, e.y);   // DBG 8: no conversion
+    pk[i] = (DBG & 8) ? __float_as_uint(e.x) : (BF ? pack_bf162(e.x, e.y) : pack_half2(e.x, e.y));   // DBG 8: no conversion
   }
   tc_st16(taddr, pk);
 }
@@ -350,7 +350,8 @@ __device__ __forceinline__ bool tc5_decode_item(const Tc5Params& p, long long it
 // masking take the fast path described in the softmax role.
 // DBG (tuning builds only, results are wrong): 1 no exp2, 2 no PV MMAs, 4 no QK MMAs, 8 no fp16 conversion,
 // 16 the softmax hands over at once without computing anything, 32 no turn taking between the tiles (valid results).
-template <int D, int NPOLY, int SM, int DBG = 0>
+// BF: q, k, v are bfloat16: the same kernel with bfloat16 MMA operands and P rounded to bfloat16.
+template <int D, int NPOLY, int SM, int DBG = 0, bool BF = false>
 __global__ void __launch_bounds__(640, 1)
 prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                    const __grid_constant__ CUtensorMap vmap, const Tc5Params p) {
@@ -359,8 +360,12 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
   constexpr int SLAB = 128 * 128;            // bytes of a [128 rows][64 cols] fp16 slab
   constexpr int NSLAB = D / 64;
   constexpr int TILE_BYTES = NSLAB * SLAB;   // one Q / K / V tile
-  constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-  constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  // instruction descriptor of kind::f16: fp32 accumulators (bit 4), operand formats (bits 7 and 10: 1 = bfloat16),
+  // B taken MN-major for PV (bit 16), N / 8 at bit 17, M / 16 at bit 24
+  constexpr uint32_t IDESC_FMT = BF ? ((1u << 7) | (1u << 10)) : 0u;
+  constexpr uint32_t IDESC_QK = (1u << 4) | IDESC_FMT | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  constexpr uint32_t IDESC_PV =
+      (1u << 4) | IDESC_FMT | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t O_COL0 = 256;
   // P (fp16, 64 columns = four quarters of 16) lies over columns [16, 80) of its S, and the quarters hold the
@@ -809,7 +814,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           lo_loaded = true;
           turn_wait(pph);
           const float2 nm2 = make_float2(-m, -m);
-          exp_chunk_store<NPOLY, DBG>(sv, sc2, nm2, rs_lo, tP + q_lo * 16);
+          exp_chunk_store<NPOLY, DBG, BF>(sv, sc2, nm2, rs_lo, tP + q_lo * 16);
           const bool inside = (rs_lo.x + rs_lo.y <= 32768.f) && (fmaxf(a0, a1) * p.scale_log2 <= m + 15.f);   // false for NaN
           const uint32_t tag = pph + 1u;
           if (__any_sync(0xffffffffu, !inside) && lane == 0) *my_tag = tag;
@@ -825,7 +830,7 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           } else {
             tc_wait_ld();
             PROF_MARK(pf6);
-            exp_chunk_store<NPOLY, DBG>(sw, sc2, nm2, rs_hi, tP + q_hi * 16);
+            exp_chunk_store<NPOLY, DBG, BF>(sw, sc2, nm2, rs_hi, tP + q_hi * 16);
             turn_pass();
             PROF_MARK(pf7);
             PROF_STAMP(2 + t);
@@ -904,12 +909,12 @@ prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_consta
           const float neg_m = (m == -INFINITY) ? 0.f : -m;
           const float2 nm2 = make_float2(neg_m, neg_m);
           if (!lo_loaded) turn_wait(pph);     // (a redone step has taken its turn already)
-          if (c_lo * 32 < lim_max) exp_chunk_store<NPOLY, DBG>(sv, sc2, nm2, rs_lo, tP + q_lo * 16);
+          if (c_lo * 32 < lim_max) exp_chunk_store<NPOLY, DBG, BF>(sv, sc2, nm2, rs_lo, tP + q_lo * 16);
           else zero_chunk_store(tP + q_lo * 16);
           tc_ld32(tS + c_hi * 32, sw);        // chunk c_hi again (its columns are written by nobody but me)
           tc_wait_ld();
           mask_chunk(sw, c_hi);
-          if (c_hi * 32 < lim_max) exp_chunk_store<NPOLY, DBG>(sw, sc2, nm2, rs_hi, tP + q_hi * 16);
+          if (c_hi * 32 < lim_max) exp_chunk_store<NPOLY, DBG, BF>(sw, sc2, nm2, rs_hi, tP + q_hi * 16);
           else zero_chunk_store(tP + q_hi * 16);
           turn_pass();
           PROF_STAMP(2 + t);
@@ -1093,6 +1098,10 @@ Tc5Kernel pick_kernel() {
   return g_tc5_poly ? prefill_tc5_kernel<D, 2, 1> : prefill_tc5_kernel<D, 0, 1>;
 #endif
 }
+template <int D>
+Tc5Kernel pick_kernel_bf16() {
+  return g_tc5_poly ? prefill_tc5_kernel<D, 2, 1, 0, true> : prefill_tc5_kernel<D, 0, 1, 0, true>;
+}
 
 template <int D>
 cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t stream) {
@@ -1122,7 +1131,7 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
   p.D_real = pp.D_real;
   p.pair_heads = ((pp.H_Q / pp.H_KV) % 2 == 0) ? 1 : 0;
   p.dense = dense ? 1 : 0;
-  p.out_bf16 = pp.out_bf16;
+  p.out_bf16 = (pp.out_bf16 || pp.in_bf16) ? 1 : 0;
   p.scale_log2 = pp.scale_log2;
   constexpr int KV_STAGES = (D == 128) ? 2 : 4;
   constexpr size_t TILE = (size_t)(D / 64) * 128 * 128;
@@ -1131,7 +1140,7 @@ cudaError_t launch_tc5_t(const PrefillParams& pp, void* encode_fn, cudaStream_t 
 #ifdef FA_TC5_PROF
   smem += (5 * 16 + 8) * 8;
 #endif
-  Tc5Kernel kern = pick_kernel<D>();
+  Tc5Kernel kern = pp.in_bf16 ? pick_kernel_bf16<D>() : pick_kernel<D>();
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int max_len = dense ? pp.N : pp.max_seqlen;

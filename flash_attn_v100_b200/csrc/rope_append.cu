@@ -24,24 +24,37 @@
 namespace fa {
 namespace {
 
-__device__ __forceinline__ __half rope_lo(__half x1, __half x2, __half c, __half s) {
+// The element type of q / k / v and of the cache: fp16, or bfloat16 for the bfloat16 twins (the same
+// operation-by-operation rounding, which is what PyTorch does on bfloat16 tensors as well).
+__device__ __forceinline__ float el_f(__half x) { return __half2float(x); }
+__device__ __forceinline__ float el_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T el_from(float x);
+template <> __device__ __forceinline__ __half el_from<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 el_from<__nv_bfloat16>(float x) { return __float2bfloat16(x); }
+
+template <typename T>
+__device__ __forceinline__ T rope_lo(T x1, T x2, T c, T s) {
   // first half:  x1 * cos + (-x2) * sin
-  const __half a = __float2half_rn(__half2float(x1) * __half2float(c));
-  const __half b = __float2half_rn(-__half2float(x2) * __half2float(s));
-  return __float2half_rn(__half2float(a) + __half2float(b));
+  const T a = el_from<T>(el_f(x1) * el_f(c));
+  const T b = el_from<T>(-el_f(x2) * el_f(s));
+  return el_from<T>(el_f(a) + el_f(b));
 }
-__device__ __forceinline__ __half rope_hi(__half x1, __half x2, __half c, __half s) {
+template <typename T>
+__device__ __forceinline__ T rope_hi(T x1, T x2, T c, T s) {
   // second half: x2 * cos + x1 * sin
-  const __half a = __float2half_rn(__half2float(x2) * __half2float(c));
-  const __half b = __float2half_rn(__half2float(x1) * __half2float(s));
-  return __float2half_rn(__half2float(a) + __half2float(b));
+  const T a = el_from<T>(el_f(x2) * el_f(c));
+  const T b = el_from<T>(el_f(x1) * el_f(s));
+  return el_from<T>(el_f(a) + el_f(b));
 }
 
+template <typename T>
 union Chunk {
   uint4 v;
-  __half h[8];
+  T h[8];
+  __device__ Chunk() {}
 };
 
+template <typename T>
 __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams p) {
   const int D = p.D, R = p.rot_dim, half_r = R / 2;
   const int chunks_rot = half_r / 8;             // chunk pairs inside the rotary span
@@ -77,23 +90,23 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
       pos = __ldg(p.positions + seq);
     }
 
-    const __half* src;
-    if (kind == 0) src = p.q + ((long long)tok * p.H_Q + h) * D;
-    else if (kind == 1) src = p.k + ((long long)tok * p.H_KV + h) * D;
-    else src = p.v + ((long long)tok * p.H_KV + h) * D;
+    const T* src;
+    if (kind == 0) src = reinterpret_cast<const T*>(p.q) + ((long long)tok * p.H_Q + h) * D;
+    else if (kind == 1) src = reinterpret_cast<const T*>(p.k) + ((long long)tok * p.H_KV + h) * D;
+    else src = reinterpret_cast<const T*>(p.v) + ((long long)tok * p.H_KV + h) * D;
 
     // destination(s)
-    __half* dst_lin = nullptr;     // q_out / k_out row
-    __half* dst_page = nullptr;    // cache row
-    if (kind == 0) dst_lin = p.q_out + ((long long)tok * p.H_Q + h) * D;
+    T* dst_lin = nullptr;     // q_out / k_out row
+    T* dst_page = nullptr;    // cache row
+    if (kind == 0) dst_lin = reinterpret_cast<T*>(p.q_out) + ((long long)tok * p.H_Q + h) * D;
     else {
-      if (kind == 1 && p.k_out != nullptr) dst_lin = p.k_out + ((long long)tok * p.H_KV + h) * D;
+      if (kind == 1 && p.k_out != nullptr) dst_lin = reinterpret_cast<T*>(p.k_out) + ((long long)tok * p.H_KV + h) * D;
       if (p.k_cache != nullptr) {
         const int blk = pos >> 4;
         int page = -1;
         if (pos >= 0 && blk < p.bt_stride) page = __ldg(p.block_table + (long long)seq * p.bt_stride + blk);
         if (page >= 0 && (long long)page < p.num_pages) {
-          __half* base = (kind == 1) ? p.k_cache : p.v_cache;
+          T* base = reinterpret_cast<T*>((kind == 1) ? p.k_cache : p.v_cache);
           dst_page = base + (((long long)page * p.H_KV + h) * 16 + (pos & 15)) * D;
         } else {
           atomicOr(p.status, kStatusBadPageId);   // no slot for this token: reported, nothing written
@@ -121,7 +134,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
     }
 
     // rotary chunk pair: elements [8c, 8c+8) of the first half and of the second half
-    Chunk x1, x2, o1, o2;
+    Chunk<T> x1, x2, o1, o2;
     x1.v = *reinterpret_cast<const uint4*>(src + c * 8);
     x2.v = *reinterpret_cast<const uint4*>(src + half_r + c * 8);
     const float* cs = p.cos + (long long)tok * R + c * 8;   // cos/sin repeat over the two halves
@@ -130,8 +143,8 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
     for (int i = 0; i < 8; ++i) {
       // the reference's tables hold cat(freqs, freqs): element i of the first half and element
       // half_r + i of the second half carry the same angle, but each is cast to fp16 on its own
-      const __half c1 = __float2half_rn(__ldg(cs + i)), s1 = __float2half_rn(__ldg(sn + i));
-      const __half c2 = __float2half_rn(__ldg(cs + half_r + i)), s2 = __float2half_rn(__ldg(sn + half_r + i));
+      const T c1 = el_from<T>(__ldg(cs + i)), s1 = el_from<T>(__ldg(sn + i));
+      const T c2 = el_from<T>(__ldg(cs + half_r + i)), s2 = el_from<T>(__ldg(sn + half_r + i));
       o1.h[i] = rope_lo(x1.h[i], x2.h[i], c1, s1);
       o2.h[i] = rope_hi(x1.h[i], x2.h[i], c2, s2);
     }
@@ -150,7 +163,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeAppendParams
 // elements, its rotary partner (the element half a head away) lives in lane L ^ 16.  The arithmetic is that
 // of the per-head norm kernel followed by the rotary kernel above, value for value, so the fused launch is
 // bit-identical to the two it replaces.
-template <int PER>
+template <int PER, typename T>
 __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeAppendParams p) {
   const RopeAppendParams& r = p.r;
   const int D = r.D, heads = r.H_Q + 2 * r.H_KV;
@@ -183,9 +196,9 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeAppen
       f[i] = __bfloat162float(__float2bfloat16(__bfloat162float(w[lane * PER + i]) * __bfloat162float(nb)));
     }
   }
-  __half x[PER];
+  T x[PER];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) x[i] = __float2half_rn(f[i]);
+  for (int i = 0; i < PER; ++i) x[i] = el_from<T>(f[i]);
 
   // sequence and cache slot of this token
   int seq, pos;
@@ -201,19 +214,19 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeAppen
     seq = tok;
     pos = __ldg(r.positions + seq);
   }
-  __half* dst_page = nullptr;
+  T* dst_page = nullptr;
   if (kind != 0 && r.k_cache != nullptr) {
     const int blk = pos >> 4;
     int page = -1;
     if (pos >= 0 && blk < r.bt_stride) page = __ldg(r.block_table + (long long)seq * r.bt_stride + blk);
     if (page >= 0 && (long long)page < r.num_pages) {
-      __half* base = (kind == 1) ? r.k_cache : r.v_cache;
+      T* base = reinterpret_cast<T*>((kind == 1) ? r.k_cache : r.v_cache);
       dst_page = base + (((long long)page * r.H_KV + h) * 16 + (pos & 15)) * D + lane * PER;
     } else if (lane == 0) {
       atomicOr(r.status, kStatusBadPageId);   // no slot for this token: reported, nothing written
     }
   }
-  __half o[PER];
+  T o[PER];
   if (kind == 2) {
 #pragma unroll
     for (int i = 0; i < PER; ++i) o[i] = x[i];
@@ -224,16 +237,17 @@ __global__ void __launch_bounds__(256) qkv_rope_append_kernel(const QkvRopeAppen
     const float* sn = r.sin + (long long)tok * D + lane * PER;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      const unsigned short mine = __half_as_ushort(x[i]);
-      const __half other = __ushort_as_half((unsigned short)__shfl_xor_sync(0xffffffffu, (unsigned int)mine, 16));
-      const __half c = __float2half_rn(__ldg(cs + i)), s = __float2half_rn(__ldg(sn + i));
+      const unsigned short mine = *reinterpret_cast<const unsigned short*>(&x[i]);
+      const unsigned short got = (unsigned short)__shfl_xor_sync(0xffffffffu, (unsigned int)mine, 16);
+      const T other = *reinterpret_cast<const T*>(&got);
+      const T c = el_from<T>(__ldg(cs + i)), s = el_from<T>(__ldg(sn + i));
       o[i] = lane < 16 ? rope_lo(x[i], other, c, s) : rope_hi(other, x[i], c, s);
     }
   }
-  __half* dst_lin = nullptr;
-  if (kind == 0) dst_lin = r.q_out + ((long long)tok * r.H_Q + h) * D + lane * PER;
-  else if (kind == 1 && r.k_out != nullptr) dst_lin = r.k_out + ((long long)tok * r.H_KV + h) * D + lane * PER;
-  else if (kind == 2 && p.v_out != nullptr) dst_lin = p.v_out + ((long long)tok * r.H_KV + h) * D + lane * PER;
+  T* dst_lin = nullptr;
+  if (kind == 0) dst_lin = reinterpret_cast<T*>(r.q_out) + ((long long)tok * r.H_Q + h) * D + lane * PER;
+  else if (kind == 1 && r.k_out != nullptr) dst_lin = reinterpret_cast<T*>(r.k_out) + ((long long)tok * r.H_KV + h) * D + lane * PER;
+  else if (kind == 2 && p.v_out != nullptr) dst_lin = reinterpret_cast<T*>(p.v_out) + ((long long)tok * r.H_KV + h) * D + lane * PER;
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     if (dst_lin) dst_lin[i] = o[i];
@@ -247,10 +261,19 @@ cudaError_t launch_qkv_rope_append(const QkvRopeAppendParams& p, cudaStream_t st
   const long long warps = (long long)p.r.T * (p.r.H_Q + 2 * p.r.H_KV);
   if (warps == 0) return cudaSuccess;
   const unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+  if (p.r.bf16) {
+    switch (p.r.D) {
+      case 64: qkv_rope_append_kernel<2, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p); break;
+      case 128: qkv_rope_append_kernel<4, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p); break;
+      case 256: qkv_rope_append_kernel<8, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p); break;
+      default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+  }
   switch (p.r.D) {
-    case 64: qkv_rope_append_kernel<2><<<blocks, 256, 0, stream>>>(p); break;
-    case 128: qkv_rope_append_kernel<4><<<blocks, 256, 0, stream>>>(p); break;
-    case 256: qkv_rope_append_kernel<8><<<blocks, 256, 0, stream>>>(p); break;
+    case 64: qkv_rope_append_kernel<2, __half><<<blocks, 256, 0, stream>>>(p); break;
+    case 128: qkv_rope_append_kernel<4, __half><<<blocks, 256, 0, stream>>>(p); break;
+    case 256: qkv_rope_append_kernel<8, __half><<<blocks, 256, 0, stream>>>(p); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();
@@ -263,7 +286,8 @@ cudaError_t launch_rope_append(const RopeAppendParams& p, int sm_count, cudaStre
   long long blocks = (total + 255) / 256;
   const long long cap = (long long)sm_count * 8;   // grid-stride loop beyond this
   if (blocks > cap) blocks = cap;
-  rope_append_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
+  if (p.bf16) rope_append_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  else rope_append_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -22,6 +22,7 @@ struct RopeAppendParams {
   int32_t* status;            // sticky status word (page id outside the pool / no slot)
   int T, batch, H_Q, H_KV, D, rot_dim, bt_stride;
   long long num_pages;
+  int bf16;                   // q / k / v, the outputs and the cache are bfloat16 instead of fp16
 };
 
 cudaError_t launch_rope_append(const RopeAppendParams& p, int sm_count, cudaStream_t stream);

@@ -40,6 +40,10 @@ class TPDecoder:
         # the decode step's all-reduces take the residual add and the RMS norm that follow them into the same
         # kernel (False: all-reduce, then the add + norm kernel; same values, kept for the parity test)
         self.fused_norm = True
+        # element type of q / k / v and of the KV pages: fp16 (the reference's operators) or bfloat16 (the
+        # library's *_bf16 twins: the activations' own type, no cast and no fp16 range limit); the KV cache
+        # handed to forward() must hold the same type
+        self.attn_dtype = torch.float16
         self.device = torch.device(device)
         self.ql = cfg.num_heads // world
         self.kl = cfg.num_kv_heads // world
@@ -76,15 +80,18 @@ class TPDecoder:
         and, for packed prompts, the rotated k and v the prefill attention reads."""
         T, D = qkv.size(0), self.cfg.head_dim
         prefill = cu_seqlens is not None
-        q = torch.empty((T, self.ql, D), dtype=torch.float16, device=self.device)
-        k = torch.empty((T, self.kl, D), dtype=torch.float16, device=self.device) if prefill else None
-        v = torch.empty((T, self.kl, D), dtype=torch.float16, device=self.device) if prefill else None
+        if k_pool.dtype != self.attn_dtype:
+            raise RuntimeError(f"the KV cache holds {k_pool.dtype}, the model's attn_dtype is {self.attn_dtype}")
+        q = torch.empty((T, self.ql, D), dtype=self.attn_dtype, device=self.device)
+        k = torch.empty((T, self.kl, D), dtype=self.attn_dtype, device=self.device) if prefill else None
+        v = torch.empty((T, self.kl, D), dtype=self.attn_dtype, device=self.device) if prefill else None
         batch = cu_seqlens.numel() - 1 if prefill else T
         if block_table.stride(1) != 1 or block_table.stride(0) != max_blocks or batch * max_blocks > block_table.numel():
             raise RuntimeError("block_table rows must be contiguous with stride max_blocks")
         qn = _p(lw["qn"]) if self.cfg.qk_norm else None
         kn = _p(lw["kn"]) if self.cfg.qk_norm else None
-        _lib.check(self.lib.fa_qkv_rope_append_f16(
+        entry = self.lib.fa_qkv_rope_append_bf16 if self.attn_dtype == torch.bfloat16 else self.lib.fa_qkv_rope_append_f16
+        _lib.check(entry(
             _p(qkv), qn, kn, _p(cos), _p(sin), _p(q), _p(k) if prefill else None, _p(v) if prefill else None,
             _p(k_pool), _p(v_pool), _p(block_table), _p(slots), _p(cu_seqlens) if prefill else None, T, batch,
             self.ql, self.kl, D, self.cfg.rms_norm_eps, k_pool.size(0), max_blocks, self._stream()))
@@ -174,7 +181,15 @@ class TPDecoder:
                         q_rot = ops.rope_append_paged_fp16(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2), st["cos"],
                                                            st["sin"], kv.k_pools[l], kv.v_pools[l], block_table, slots,
                                                            max_blocks)
-                if prefill:
+                if self.attn_dtype == torch.bfloat16:
+                    if not self.fused_qkv:
+                        raise RuntimeError("attn_dtype bfloat16 needs fused_qkv (the split kernels cast to fp16)")
+                    if prefill:
+                        attn = ops.forward_varlen_prefill_bf16(q_rot, k_rot, v, cu_seqlens, max_seqlen, True)
+                    else:
+                        attn = ops.forward_paged_decode_gqa_bf16(q_rot, kv.k_pools[l], kv.v_pools[l], block_table,
+                                                                 st["lens"], max_blocks)
+                elif prefill:
                     attn = ops.forward_varlen_prefill_fp16(q_rot, k_rot, v, cu_seqlens, max_seqlen, True,
                                                            out_dtype=torch.bfloat16)
                 else:

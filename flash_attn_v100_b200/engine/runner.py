@@ -21,7 +21,7 @@ class GenerationRunner:
         self.max_blocks = (max_seq_len + 15) // 16
         self.kv = PagedKVCache(num_blocks=max_batch * self.max_blocks, num_layers=cfg.num_layers,
                                num_kv_heads=model.kl, head_dim=cfg.head_dim, max_batch=max_batch,
-                               max_blocks_per_seq=self.max_blocks, device=model.device)
+                               max_blocks_per_seq=self.max_blocks, device=model.device, dtype=model.attn_dtype)
         # The decode step is replayed from one CUDA graph on a single rank.  Under tensor parallelism it is a
         # chain of graphs with the NCCL collectives issued eagerly in between (NCCL calls are not captured),
         # or - with peer_collectives - again one CUDA graph, the collectives being the library's peer-memory

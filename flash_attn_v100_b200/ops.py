@@ -13,7 +13,9 @@ surrounding PyTorch work and can be captured in CUDA graphs.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import threading
 from typing import Dict, Tuple
 
 import torch
@@ -23,6 +25,34 @@ from . import _lib
 PAGE_BLOCK_SIZE = 16  # flash_attn_kernel.cu:3389
 MAX_D_LARGE = 256     # flash_attn_kernel.cu:36
 SUPPORTED_D = (64, 128, 256)
+
+# Element type of q / k / v / caches that the wrappers below accept: float16, as in the reference, except inside
+# the bfloat16 twins at the end of this file (same checks and launches, the library's *_bf16 entry points).
+_elem_state = threading.local()
+
+
+def _elem():
+    return getattr(_elem_state, "dtype", torch.float16)
+
+
+def _elem_name():
+    return "bfloat16" if _elem() == torch.bfloat16 else "float16"
+
+
+def _entry(lib, f16_name):
+    """The C entry point for the current element type: fa_x_f16 or its twin fa_x_bf16."""
+    return getattr(lib, f16_name[:-3] + "bf16") if _elem() == torch.bfloat16 else getattr(lib, f16_name)
+
+
+@contextlib.contextmanager
+def _bf16_elements():
+    prev = _elem()
+    _elem_state.dtype = torch.bfloat16
+    try:
+        yield
+    finally:
+        _elem_state.dtype = prev
+
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 _retired_workspaces: list = []
@@ -180,7 +210,7 @@ def _decode_gqa(out, q, k, v, causal, cache_len, stream_int=None):
         _chk(out.size(1) == q.size(1), "out head count must match q")
         _chk(out.size(2) == 1, "out sequence length must be 1 for decode mode")
         _chk(out.size(3) == q.size(3), "out head dimension must match q")
-    _chk(q.dtype == torch.float16, "q, k, v must be float16")
+    _chk(q.dtype == _elem(), f"q, k, v must be {_elem_name()}")
     _chk(q.size(2) == 1, "q sequence length must be 1 for decode mode")
     B, H_Q, _, D = q.shape
     H_KV, N = k.size(1), k.size(2)
@@ -194,7 +224,7 @@ def _decode_gqa(out, q, k, v, causal, cache_len, stream_int=None):
             out = torch.empty((B, H_Q, 1, D), dtype=q.dtype, device=q.device)
         s = _stream_ptr(q.device, stream_int)
         ws = _workspace(q.device, s, B, H_Q, H_KV, D)
-        _lib.check(lib.fa_decode_gqa_f16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H_Q, H_KV, N, D,
+        _lib.check(_entry(lib, "fa_decode_gqa_f16")(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H_Q, H_KV, N, D,
                                          1 if causal else 0, cache_len, _ptr(ws), ws.numel(), ctypes.c_void_p(s)))
     return out
 
@@ -333,7 +363,7 @@ def forward_paged_decode_gqa_fp16(q, k_cache, v_cache, block_table, seq_lens, ma
     row stride `max_num_blocks` (:3438); seq_lens [B] int32.  seq_len 0 gives zeros.
     `out_dtype=torch.bfloat16` (an addition) returns the result rounded to bfloat16 instead of fp16."""
     _chk(out_dtype in (None, torch.float16, torch.bfloat16), "out_dtype must be float16 or bfloat16")
-    bf16_out = out_dtype == torch.bfloat16
+    bf16_out = out_dtype == torch.bfloat16 and _elem() == torch.float16
     for t, n in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache"), (block_table, "block_table"),
                  (seq_lens, "seq_lens")):
         _check_input(t, n)
@@ -341,9 +371,9 @@ def forward_paged_decode_gqa_fp16(q, k_cache, v_cache, block_table, seq_lens, ma
     _check_dim(block_table, 2, "block_table"); _check_dim(seq_lens, 1, "seq_lens")
     for t, n in ((k_cache, "k_cache"), (v_cache, "v_cache"), (block_table, "block_table"), (seq_lens, "seq_lens")):
         _same_device(q, t, "q", n)
-    _chk(q.dtype == torch.float16, "q must be float16")
-    _chk(k_cache.dtype == torch.float16, "k_cache must be float16")
-    _chk(v_cache.dtype == torch.float16, "v_cache must be float16")
+    _chk(q.dtype == _elem(), f"q must be {_elem_name()}")
+    _chk(k_cache.dtype == _elem(), f"k_cache must be {_elem_name()}")
+    _chk(v_cache.dtype == _elem(), f"v_cache must be {_elem_name()}")
     _chk(block_table.dtype == torch.int32, "block_table must be int32")
     _chk(seq_lens.dtype == torch.int32, "seq_lens must be int32")
     _chk(q.size(2) == 1, "q sequence length must be 1 for decode mode")
@@ -367,7 +397,7 @@ def forward_paged_decode_gqa_fp16(q, k_cache, v_cache, block_table, seq_lens, ma
         s = _stream_ptr(q.device)
         ws = _workspace(q.device, s, B, H_Q, H_KV, D)
         max_len = min(max_num_blocks, block_table.size(1)) * PAGE_BLOCK_SIZE
-        entry = lib.fa_paged_decode_gqa_f16_out_bf16 if bf16_out else lib.fa_paged_decode_gqa_f16
+        entry = lib.fa_paged_decode_gqa_f16_out_bf16 if bf16_out else _entry(lib, "fa_paged_decode_gqa_f16")
         _lib.check(entry(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table),
                                                _ptr(seq_lens), B, H_Q, H_KV, D, k_cache.size(0), max_num_blocks,
                                                max_len, _ptr(ws), ws.numel(), ctypes.c_void_p(s)))
@@ -420,7 +450,7 @@ def _prefill_dense(out, q, k, v, causal):
         if out is None:
             out = torch.empty((B, H_Q, N, D), dtype=q.dtype, device=q.device)
         s = _stream_ptr(q.device)
-        _lib.check(lib.fa_prefill_dense_f16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H_Q, H_KV, N, D,
+        _lib.check(_entry(lib, "fa_prefill_dense_f16")(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, H_Q, H_KV, N, D,
                                             1 if causal else 0, ctypes.c_void_p(s)))
     return out
 
@@ -436,7 +466,7 @@ def forward_fp16(q, k, v, causal):
     _same_dtype(q, k, "q", "k"); _same_dtype(q, v, "q", "v")
     _chk(q.shape == k.shape, "q and k must have the same shape")
     _chk(q.shape == v.shape, "q and v must have the same shape")
-    _chk(q.dtype == torch.float16, "q, k, v must be float16")
+    _chk(q.dtype == _elem(), f"q, k, v must be {_elem_name()}")
     _chk(q.size(3) <= MAX_D_LARGE, "D must be less than or equal to MAX_D_LARGE(256)")
     return _prefill_dense(None, q, k, v, causal)
 
@@ -451,7 +481,7 @@ def _prefill_gqa(out, q, k, v, causal):
         _check_dim(out, 4, "out")
         _same_device(out, q, "out", "q"); _same_dtype(out, q, "out", "q")
         _chk(out.shape == q.shape, "out shape must match q shape for prefill mode")
-    _chk(q.dtype == torch.float16, "q, k, v must be float16")
+    _chk(q.dtype == _elem(), f"q, k, v must be {_elem_name()}")
     _check_gqa_heads(q.size(1), k.size(1))
     _chk(q.size(3) <= MAX_D_LARGE, "D must be <= MAX_D_LARGE(256)")
     return _prefill_dense(out, q, k, v, causal)
@@ -478,8 +508,9 @@ def _varlen(q, k, v, cu_seqlens, max_seqlen, causal, stream_int=None, bf16_out=F
     _chk(k.size(0) == q.size(0) and v.size(0) == q.size(0), "k and v total length must match q")
     _chk(k.size(1) == v.size(1), "k and v must have the same number of heads")
     _chk(k.size(2) == q.size(2) and v.size(2) == q.size(2), "k and v head dimension must match q")
-    _chk(q.dtype == torch.float16, "q, k, v must be float16")
+    _chk(q.dtype == _elem(), f"q, k, v must be {_elem_name()}")
     _chk(cu_seqlens.dtype == torch.int32, "cu_seqlens must be int32")
+    bf16_out = bf16_out and _elem() == torch.float16
     total, H_Q, D = q.shape
     H_KV = k.size(1)
     _check_gqa_heads(H_Q, H_KV)
@@ -498,7 +529,7 @@ def _varlen(q, k, v, cu_seqlens, max_seqlen, causal, stream_int=None, bf16_out=F
             ev = torch.cuda.Event()
             ev.record()
             torch.cuda.ExternalStream(stream_int, device=q.device).wait_event(ev)
-        entry = lib.fa_prefill_varlen_f16_out_bf16 if bf16_out else lib.fa_prefill_varlen_f16
+        entry = lib.fa_prefill_varlen_f16_out_bf16 if bf16_out else _entry(lib, "fa_prefill_varlen_f16")
         _lib.check(entry(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens), batch, total,
                          H_Q, H_KV, D, max_seqlen, 1 if causal else 0, ctypes.c_void_p(s)))
     return out
@@ -539,7 +570,7 @@ def rope_append_paged_fp16(q, k, v, cos, sin, k_cache, v_cache, block_table, pos
     """
     for t, n in ((q, "q"), (k, "k"), (v, "v"), (cos, "cos"), (sin, "sin")):
         _check_input(t, n)
-    _chk(q.dtype == torch.float16 and k.dtype == torch.float16 and v.dtype == torch.float16, "q, k, v must be float16")
+    _chk(q.dtype == _elem() and k.dtype == _elem() and v.dtype == _elem(), f"q, k, v must be {_elem_name()}")
     _chk(cos.dtype == torch.float32 and sin.dtype == torch.float32, "cos and sin must be float32")
     _chk(k.shape == v.shape, "k and v must have the same shape")
     packed = cu_seqlens is not None
@@ -569,7 +600,7 @@ def rope_append_paged_fp16(q, k, v, cos, sin, k_cache, v_cache, block_table, pos
         for t, n in ((k_cache, "k_cache"), (v_cache, "v_cache"), (block_table, "block_table")):
             _check_input(t, n)
             _same_device(q, t, "q", n)
-        _chk(k_cache.dtype == torch.float16 and v_cache.dtype == torch.float16, "k_cache and v_cache must be float16")
+        _chk(k_cache.dtype == _elem() and v_cache.dtype == _elem(), f"k_cache and v_cache must be {_elem_name()}")
         _chk(k_cache.dim() == 4 and k_cache.shape == v_cache.shape and k_cache.size(1) == H_KV and
              k_cache.size(2) == PAGE_BLOCK_SIZE and k_cache.size(3) == D, "cache must be [pages, H_KV, 16, D]")
         _chk(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.size(0) >= batch,
@@ -587,13 +618,44 @@ def rope_append_paged_fp16(q, k, v, cos, sin, k_cache, v_cache, block_table, pos
         q_out = torch.empty_like(q)
         k_out = torch.empty_like(k) if return_k else None
         s = _stream_ptr(q.device)
-        _lib.check(lib.fa_rope_append_paged_f16(
+        _lib.check(_entry(lib, "fa_rope_append_paged_f16")(
             _ptr(q), _ptr(k), _ptr(v), _ptr(cos), _ptr(sin), _ptr(q_out), _ptr(k_out) if return_k else None,
             _ptr(k_cache) if has_cache else None, _ptr(v_cache) if has_cache else None,
             _ptr(block_table) if has_cache else None, _ptr(positions) if positions is not None else None,
             _ptr(cu_seqlens) if packed else None, T, batch, H_Q, H_KV, D, R,
             k_cache.size(0) if has_cache else 0, int(max_num_blocks) if has_cache else 0, ctypes.c_void_p(s)))
     return (q_out, k_out) if return_k else q_out
+
+
+# --------------------------------------------------------------------------
+# bfloat16 twins (additions: the reference's operators are fp16 only).  q / k / v, the caches and the result
+# are bfloat16; everything else — shapes, checks, errors — is that of the fp16 function named in the body.
+# --------------------------------------------------------------------------
+def forward_decode_gqa_bf16(q, k, v, causal, cache_len):
+    with _bf16_elements():
+        return forward_decode_gqa_fp16(q, k, v, causal, cache_len)
+
+
+def forward_paged_decode_gqa_bf16(q, k_cache, v_cache, block_table, seq_lens, max_num_blocks):
+    with _bf16_elements():
+        return forward_paged_decode_gqa_fp16(q, k_cache, v_cache, block_table, seq_lens, max_num_blocks)
+
+
+def forward_prefill_gqa_bf16(q, k, v, causal):
+    with _bf16_elements():
+        return forward_prefill_gqa_fp16(q, k, v, causal)
+
+
+def forward_varlen_prefill_bf16(q, k, v, cu_seqlens, max_seqlen, causal):
+    with _bf16_elements():
+        return forward_varlen_prefill_fp16(q, k, v, cu_seqlens, max_seqlen, causal)
+
+
+def rope_append_paged_bf16(q, k, v, cos, sin, k_cache, v_cache, block_table, positions, max_num_blocks,
+                           cu_seqlens=None, return_k=False):
+    with _bf16_elements():
+        return rope_append_paged_fp16(q, k, v, cos, sin, k_cache, v_cache, block_table, positions, max_num_blocks,
+                                      cu_seqlens=cu_seqlens, return_k=return_k)
 
 
 # --------------------------------------------------------------------------

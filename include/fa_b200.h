@@ -325,6 +325,43 @@ int fa_qkv_rope_append_f16(const void* qkv, const void* q_weight, const void* k_
                            void* v_cache, const int32_t* block_table, const int32_t* positions,
                            const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV, int D, float eps,
                            int64_t num_pages, int block_table_stride, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * bfloat16 twins: the same operators for q / k / v, caches and outputs that hold
+ * bfloat16 instead of fp16 (a model whose activations are bfloat16 keeps its
+ * range; the reference's operators are fp16 only).  Same arguments, shapes and
+ * error behaviour as the _f16 functions they are named after.  The score and
+ * output MMAs take bfloat16 operands (P is rounded to bfloat16 before P V), all
+ * accumulation, softmax and merging stay fp32.  fa_prefill_*_bf16 run on the
+ * tcgen05 kernel (head dimension up to 128; FA_ERR_UNSUPPORTED above).
+ * fa_rope_append_paged_bf16 / fa_qkv_rope_append_bf16 round cos / sin, each
+ * product and the sum to bfloat16, as PyTorch does for
+ * (x * cos) + (rotate_half(x) * sin) on bfloat16 tensors.
+ * -------------------------------------------------------------------------- */
+int fa_paged_decode_gqa_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                             const int32_t* block_table, const int32_t* seq_lens,
+                             int B, int H_Q, int H_KV, int D,
+                             int64_t num_pages, int block_table_stride, int64_t max_seq_len,
+                             void* workspace, size_t workspace_bytes, void* stream);
+int fa_decode_gqa_bf16(const void* q, const void* k, const void* v, void* out,
+                       int B, int H_Q, int H_KV, int N, int D, int causal, int cache_len,
+                       void* workspace, size_t workspace_bytes, void* stream);
+int fa_prefill_dense_bf16(const void* q, const void* k, const void* v, void* out,
+                          int B, int H_Q, int H_KV, int N, int D, int causal, void* stream);
+int fa_prefill_varlen_bf16(const void* q, const void* k, const void* v, void* out,
+                           const int32_t* cu_seqlens, int batch, int64_t total,
+                           int H_Q, int H_KV, int D, int max_seqlen, int causal, void* stream);
+int fa_rope_append_paged_bf16(const void* q, const void* k, const void* v, const float* cos,
+                              const float* sin, void* q_out, void* k_out, void* k_cache, void* v_cache,
+                              const int32_t* block_table, const int32_t* positions,
+                              const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV, int D,
+                              int rot_dim, int64_t num_pages, int block_table_stride, void* stream);
+int fa_qkv_rope_append_bf16(const void* qkv, const void* q_weight, const void* k_weight, const float* cos,
+                            const float* sin, void* q_out, void* k_out, void* v_out, void* k_cache,
+                            void* v_cache, const int32_t* block_table, const int32_t* positions,
+                            const int32_t* cu_seqlens, int T, int batch, int H_Q, int H_KV, int D, float eps,
+                            int64_t num_pages, int block_table_stride, void* stream);
+
 int fa_silu_mul_bf16(const void* gate_up, void* out, int64_t T, int I, void* stream);
 int fa_half_to_bf16(const void* in, void* out, int64_t n, void* stream);
 

@@ -3,7 +3,7 @@
     python tests/golden/make_golden_rope.py /path/to/reference
 
 Loads flash_attn_llm/models/rope.py of the reference by file path (no package import needed),
-runs RotaryEmbedding + apply_rotary_emb on seeded fp16 CPU tensors and stores inputs' SHA-256 and
+runs RotaryEmbedding + apply_rotary_emb on seeded fp16 (and bfloat16) CPU tensors and stores inputs' SHA-256 and
 the outputs in tests/golden/reference_rope_outputs.npz.
 """
 import hashlib
@@ -46,6 +46,14 @@ def main(ref_root):
         out[f"{name}/sin"] = sin.numpy()
         out[f"{name}/q"] = qe.numpy()
         out[f"{name}/k"] = ke.numpy()
+        # the same case on bfloat16 tensors (stored as their 16-bit patterns): the pin of the *_bf16 twins
+        torch.manual_seed(77)
+        qb = torch.randn(B, H_Q, 1, D).bfloat16()
+        kb = torch.randn(B, H_KV, 1, D).bfloat16()
+        qeb, keb = rope.apply_rotary_emb(qb, kb, cos, sin)
+        out[f"{name}/digest_bf16"] = digest(qb.view(torch.int16), kb.view(torch.int16))
+        out[f"{name}/q_bf16"] = qeb.view(torch.int16).numpy()
+        out[f"{name}/k_bf16"] = keb.view(torch.int16).numpy()
     np.savez_compressed(os.path.join(HERE, "reference_rope_outputs.npz"), **out)
     print("wrote", len(out), "arrays")
 

@@ -45,6 +45,37 @@ def test_engine_matches_oracle_logits_and_tokens():
     pkg.check_async_errors(); pkg.check_prefill_errors()
 
 
+def test_engine_with_bfloat16_attention_matches_oracle_logits():
+    """The same comparison with q / k / v and the KV pages in bfloat16 (the library's *_bf16 twins): no cast to
+    fp16 anywhere in the block."""
+    from oracle import model_oracle as mo
+    cfg, model, Runner = _setup()
+    model.attn_dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(3)
+    B, P, N = 3, 21, 12
+    prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g)
+    logs = []
+    runner = Runner(model, max_batch=4, max_seq_len=64, use_cuda_graph=False)
+    assert runner.kv.k_pools[0].dtype == torch.bfloat16
+    toks = runner.generate(prompts, N, prefill_chunk=2, logits_out=logs).cpu()
+    torch.cuda.synchronize()
+    pre = torch.cat([lg for kind, _, lg in logs if kind == "prefill"]).cpu()
+    dec = [lg.cpu() for kind, _, lg in logs if kind == "decode"]
+    eng = torch.stack([pre] + dec, dim=1)
+    full = torch.cat([prompts, toks[:, :-1]], dim=1)
+    ref = mo.forward_logits(cfg, 5, full)[:, P - 1:]
+    err = (eng - ref).abs().max().item()
+    assert err < TOL, err
+    top2 = ref.topk(2, dim=-1).values
+    confident = (top2[..., 0] - top2[..., 1]) > 2 * TOL
+    assert (toks[confident] == ref.argmax(-1)[confident]).all()
+    # graph replay reproduces the eager tokens in this mode too
+    r2 = Runner(model, max_batch=4, max_seq_len=64, use_cuda_graph=True)
+    assert torch.equal(r2.generate(prompts, N, prefill_chunk=2).cpu(), toks)
+    import flash_attn_v100_b200 as pkg
+    pkg.check_async_errors(); pkg.check_prefill_errors()
+
+
 def test_fused_qkv_kernel_is_bit_identical_to_the_two_kernels_it_replaces():
     """QK-norm + cast + rotary + append in one launch against the norm kernel followed by the rotary/append
     kernel: the same tokens and bit-identical logits, prompts (packed) and decode steps, and bit-identical

@@ -42,6 +42,21 @@ def test_rope_oracle_is_bit_identical_to_reference_module(rope_golden):
         assert torch.equal(ke, torch.from_numpy(rope_golden[f"{name}/k"]))
 
 
+def test_rope_oracle_on_bfloat16_is_bit_identical_to_reference_module(rope_golden):
+    """The pin of the *_bf16 twins: the reference module evaluated on bfloat16 tensors."""
+    for name, B, H_Q, H_KV, D, theta, prf, positions in ROPE_CASES:
+        torch.manual_seed(77)
+        q = torch.randn(B, H_Q, 1, D).bfloat16()
+        k = torch.randn(B, H_KV, 1, D).bfloat16()
+        assert gc.digest(q.view(torch.int16), k.view(torch.int16)) == str(rope_golden[f"{name}/digest_bf16"])
+        rot = int(D * prf)
+        cos, sin = orc.rope_cos_sin(torch.tensor(positions), rot, theta)
+        qe, ke = orc.apply_rotary_emb(q, k, cos.view(-1, 1, 1, rot), sin.view(-1, 1, 1, rot))
+        assert qe.dtype == torch.bfloat16
+        assert np.array_equal(qe.view(torch.int16).numpy(), rope_golden[f"{name}/q_bf16"])
+        assert np.array_equal(ke.view(torch.int16).numpy(), rope_golden[f"{name}/k_bf16"])
+
+
 def test_block_manager_alloc_reserve_release():
     kv = PagedKVCache(num_blocks=6, num_layers=2, num_kv_heads=2, head_dim=64, max_batch=3, max_blocks_per_seq=4,
                       device="cpu")
