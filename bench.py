@@ -638,12 +638,6 @@ def collectives_record(rank, world, device, iters=200):
     pc.all_reduce_(v)
     torch.cuda.synchronize()
     exact = bool(torch.equal(v, want))
-    pc.push = False                            # the barrier + remote-load kernel: the same sum
-    v.copy_(x)
-    pc.all_reduce_(v)
-    torch.cuda.synchronize()
-    exact = exact and bool(torch.equal(v, want))
-    pc.push = True
     y = torch.zeros(rows, cols, dtype=torch.bfloat16, device=device)
     v.zero_()                                  # zeros stay zeros however often they are summed
 
@@ -653,9 +647,6 @@ def collectives_record(rank, world, device, iters=200):
         return time_steps(fn, iters, world, device) / iters * 1e3   # microseconds, max over ranks
 
     us_peer = timed(lambda: pc.all_reduce_(v))
-    pc.push = False
-    us_pull = timed(lambda: pc.all_reduce_(v))
-    pc.push = True
     us_nccl = timed(lambda: dist.all_reduce(y))
     status_ok = True
     try:
@@ -667,8 +658,6 @@ def collectives_record(rank, world, device, iters=200):
     pc.close()
     link_bytes = 2.0 * (world - 1) / world * n * 2
     return {"message": "256 x 4096 bf16 (2 MB), sum all-reduce, in place", "peer_us": us_peer, "nccl_us": us_nccl,
-            "peer_kernel": "push (staging + flags behind the data); peer_pull_us: the barrier + remote-load kernel",
-            "peer_pull_us": us_pull,
             "nvlink_bytes_per_rank": link_bytes, "peer_gbs_per_rank": link_bytes / us_peer / 1e3,
             "nccl_gbs_per_rank": link_bytes / us_nccl / 1e3, "exact_vs_fp32_rank_order_sum_all_ranks": bool(flag.item()),
             "peer_status_clean": status_ok, "nvls": "off (NCCL_NVLS_ENABLE=0); peer kernel uses plain peer loads/stores",

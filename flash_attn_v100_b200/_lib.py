@@ -43,9 +43,6 @@ SIGNATURES = {
     "fa_peer_allreduce_sum_bf16": (_i, [_c.POINTER(_vp), _c.POINTER(_vp), _vp, _i, _i, _i64, _i64, _vp]),
     "fa_peer_allreduce_add_rmsnorm_bf16": (_i, [_c.POINTER(_vp), _c.POINTER(_vp), _vp, _i, _i, _i64, _i64, _i64, _i64,
                                                 _i, _vp, _c.c_float, _vp]),
-    "fa_peer_allreduce_push_sum_bf16": (_i, [_c.POINTER(_vp), _c.POINTER(_vp), _vp, _i, _i, _i64, _i64, _i64, _vp]),
-    "fa_peer_allreduce_push_add_rmsnorm_bf16": (_i, [_c.POINTER(_vp), _c.POINTER(_vp), _vp, _i, _i, _i64, _i64, _i64,
-                                                     _i64, _i, _vp, _c.c_float, _i64, _vp]),
     "fa_peer_allgather": (_i, [_c.POINTER(_vp), _c.POINTER(_vp), _vp, _i, _i, _vp, _i64, _i64, _vp]),
     "fa_peer_status": (_i, [_vp, _vp, _c.POINTER(_i)]),
     "fa_peer_reset": (_i, [_vp, _vp, _vp]),

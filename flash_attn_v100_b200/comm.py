@@ -43,15 +43,10 @@ class PeerCollectives:
             raise RuntimeError("peer collectives serve at most 8 ranks of one NVLink domain")
         self.lib = _lib.load()
         self.data_bytes = (int(data_bytes) + 255) // 256 * 256
-        # Behind the caller's data_bytes lies a staging area of the same size for the push variants of the
-        # all-reduces (`push = False`: the barrier + remote-load kernels, which need none; same results).
-        self.push = True
-        self._staging_off = self.data_bytes
-        self._alloc_bytes = 2 * self.data_bytes
         d, f, s = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
         hd, hf = ctypes.create_string_buffer(64), ctypes.create_string_buffer(64)
         with torch.cuda.device(self.device):
-            _lib.check(self.lib.fa_peer_alloc(self._alloc_bytes, ctypes.byref(d), ctypes.byref(f), ctypes.byref(s), hd, hf))
+            _lib.check(self.lib.fa_peer_alloc(self.data_bytes, ctypes.byref(d), ctypes.byref(f), ctypes.byref(s), hd, hf))
         self._own = (d.value, f.value, s.value)
         handles = [None] * self.world
         dist.all_gather_object(handles, (bytes(hd.raw), bytes(hf.raw), self.data_bytes), group=group)
@@ -102,13 +97,8 @@ class PeerCollectives:
         """In-place sum over the ranks of a bf16 view of the buffer (same view on every rank)."""
         if t.dtype != torch.bfloat16:
             raise TypeError("all_reduce_ takes bfloat16")
-        if self.push and t.numel() * 2 <= self.data_bytes:
-            _lib.check(self.lib.fa_peer_allreduce_push_sum_bf16(self._data, self._flags, self._state, self.rank,
-                                                                self.world, self._offset_of(t), t.numel(),
-                                                                self._staging_off, self._stream()))
-        else:
-            _lib.check(self.lib.fa_peer_allreduce_sum_bf16(self._data, self._flags, self._state, self.rank, self.world,
-                                                           self._offset_of(t), t.numel(), self._stream()))
+        _lib.check(self.lib.fa_peer_allreduce_sum_bf16(self._data, self._flags, self._state, self.rank, self.world,
+                                                       self._offset_of(t), t.numel(), self._stream()))
         return t
 
     def all_reduce_add_rmsnorm_(self, part: torch.Tensor, x: torch.Tensor, h: torch.Tensor, weight: torch.Tensor,
@@ -125,16 +115,10 @@ class PeerCollectives:
             raise ValueError("rows must be a multiple of the world size")
         if not weight.is_contiguous() or weight.device != self.device:
             raise ValueError("weight must be contiguous on this rank's device")
-        if self.push:
-            _lib.check(self.lib.fa_peer_allreduce_push_add_rmsnorm_bf16(
-                self._data, self._flags, self._state, self.rank, self.world, self._offset_of(part), self._offset_of(x),
-                self._offset_of(h), part.size(0), part.size(1), ctypes.c_void_p(weight.data_ptr()), float(eps),
-                self._staging_off, self._stream()))
-        else:
-            _lib.check(self.lib.fa_peer_allreduce_add_rmsnorm_bf16(
-                self._data, self._flags, self._state, self.rank, self.world, self._offset_of(part), self._offset_of(x),
-                self._offset_of(h), part.size(0), part.size(1), ctypes.c_void_p(weight.data_ptr()), float(eps),
-                self._stream()))
+        _lib.check(self.lib.fa_peer_allreduce_add_rmsnorm_bf16(
+            self._data, self._flags, self._state, self.rank, self.world, self._offset_of(part), self._offset_of(x),
+            self._offset_of(h), part.size(0), part.size(1), ctypes.c_void_p(weight.data_ptr()), float(eps),
+            self._stream()))
         return h
 
     def all_gather_into(self, out: torch.Tensor, src: torch.Tensor) -> torch.Tensor:

@@ -933,52 +933,6 @@ int fa_peer_allreduce_add_rmsnorm_bf16(void* const* data_ptrs, void* const* flag
   return FA_OK;
 }
 
-int fa_peer_allreduce_push_sum_bf16(void* const* data_ptrs, void* const* flag_ptrs, void* state, int rank, int world,
-                                    int64_t offset_bytes, int64_t n_elems, int64_t staging_offset_bytes, void* stream) {
-  fa::PeerPointers pp;
-  fa::PeerState st;
-  int rc = fill_peer_args(data_ptrs, flag_ptrs, state, rank, world, &pp, &st);
-  if (rc != FA_OK) return rc;
-  FA_REQUIRE(offset_bytes >= 0 && offset_bytes % 16 == 0, "offset_bytes must be a non-negative multiple of 16");
-  FA_REQUIRE(n_elems > 0 && n_elems % (8 * world) == 0, "n_elems must be a positive multiple of 8 * world");
-  FA_REQUIRE(staging_offset_bytes >= 0 && staging_offset_bytes % 16 == 0,
-             "staging_offset_bytes must be a non-negative multiple of 16");
-  FA_REQUIRE(staging_offset_bytes >= offset_bytes + n_elems * 2 || staging_offset_bytes + n_elems * 2 <= offset_bytes,
-             "the staging area must not overlap the message");
-  const long long vec_per_slice = n_elems / 8 / world;
-  const int ctas = (int)((vec_per_slice + 511) / 512);
-  FA_CUDA(fa::launch_peer_allreduce_push_bf16(pp, st, rank, world, offset_bytes, staging_offset_bytes, n_elems, ctas,
-                                              static_cast<cudaStream_t>(stream)));
-  return FA_OK;
-}
-
-int fa_peer_allreduce_push_add_rmsnorm_bf16(void* const* data_ptrs, void* const* flag_ptrs, void* state, int rank,
-                                            int world, int64_t part_offset_bytes, int64_t x_offset_bytes,
-                                            int64_t h_offset_bytes, int64_t rows, int cols, const void* weight, float eps,
-                                            int64_t staging_offset_bytes, void* stream) {
-  fa::PeerPointers pp;
-  fa::PeerState st;
-  int rc = fill_peer_args(data_ptrs, flag_ptrs, state, rank, world, &pp, &st);
-  if (rc != FA_OK) return rc;
-  FA_REQUIRE(weight, "null weight pointer");
-  FA_REQUIRE(part_offset_bytes >= 0 && x_offset_bytes >= 0 && h_offset_bytes >= 0 && staging_offset_bytes >= 0 &&
-                 part_offset_bytes % 16 == 0 && x_offset_bytes % 16 == 0 && h_offset_bytes % 16 == 0 &&
-                 staging_offset_bytes % 16 == 0,
-             "region offsets must be non-negative multiples of 16");
-  FA_REQUIRE(rows > 0 && rows % world == 0 && rows <= (1 << 24), "rows must be a positive multiple of world");
-  FA_REQUIRE(cols > 0 && cols % 8 == 0 && cols <= 16384, "cols must be a multiple of 8, at most 16384");
-  const int64_t bytes = rows * (int64_t)cols * 2;
-  auto apart = [bytes](int64_t a, int64_t b) { return a + bytes <= b || b + bytes <= a; };
-  FA_REQUIRE(apart(part_offset_bytes, x_offset_bytes) && apart(part_offset_bytes, h_offset_bytes) &&
-                 apart(x_offset_bytes, h_offset_bytes) && apart(staging_offset_bytes, part_offset_bytes) &&
-                 apart(staging_offset_bytes, x_offset_bytes) && apart(staging_offset_bytes, h_offset_bytes),
-             "the regions and the staging area must not overlap");
-  FA_CUDA(fa::launch_peer_allreduce_push_add_rmsnorm(pp, st, rank, world, part_offset_bytes, x_offset_bytes,
-                                                     h_offset_bytes, staging_offset_bytes, (int)rows, cols, weight, eps,
-                                                     static_cast<cudaStream_t>(stream)));
-  return FA_OK;
-}
-
 int fa_peer_allgather(void* const* data_ptrs, void* const* flag_ptrs, void* state, int rank, int world, const void* src,
                       int64_t offset_bytes, int64_t chunk_bytes, void* stream) {
   fa::PeerPointers pp;

@@ -215,193 +215,6 @@ peer_allreduce_add_rmsnorm_kernel(const PeerPointers pp, const PeerState st, int
   end_epoch(st, e);
 }
 
-// ---- push variants ------------------------------------------------------------------------------------
-// The same two collectives with every wait on the path replaced by a one-way trip.  The kernels above cost
-// five NVLink latencies in a row (barrier, remote loads = request + reply, remote stores, barrier); here a
-// rank PUSHES the part of its input that another rank reduces into a staging area of that rank and raises
-// a flag behind it, the reducer waits for the flags of all sources, sums (in rank order: bit-identical to
-// the kernels above), pushes the result to every rank and raises a second flag there; a rank is done when
-// the result flags of all reducers have arrived.  Two latencies, and a flag that has arrived says that the
-// data in front of it has.  The staging area (one message: world slices, one per source, at the same
-// offset of every rank's buffer) is free again when the call returns: a reducer has read its sources
-// before it pushes a result, and every rank waits for the results of all reducers.
-// Flags: the arrays of the barriers above, phase 0 = "source's CTA c has pushed", phase 1 = "reducer's CTA c
-// has stored its results"; CTA c of a rank only ever waits for CTA c of the others.
-__device__ __forceinline__ void raise_flags(const PeerPointers& pp, int rank, int world, int phase, uint32_t e) {
-  __syncthreads();   // the CTA's stores are ordered before the flag by the cumulative release below
-  if (threadIdx.x < world) st_release_sys(pp.flags[threadIdx.x] + flag_index(phase, blockIdx.x, rank), e);
-}
-__device__ __forceinline__ void await_flags(const PeerPointers& pp, int rank, int world, int phase, uint32_t e,
-                                            int32_t* status, unsigned int max_polls) {
-  const int tid = threadIdx.x;
-  if (tid < world) {
-    const uint32_t* mine = pp.flags[rank] + flag_index(phase, blockIdx.x, tid);
-    bool ok = false;
-    if (*reinterpret_cast<volatile int32_t*>(status) == 0) {
-      for (unsigned int i = 0; i < max_polls; ++i) {
-        if (ld_acquire_sys(mine) == e) { ok = true; break; }
-        if (i >= 64u) __nanosleep(100);
-      }
-    }
-    if (!ok) atomicOr(status, kPeerStatusTimeout);
-  }
-  __syncthreads();
-}
-
-__global__ void __launch_bounds__(512)
-peer_allreduce_push_kernel(const PeerPointers pp, const PeerState st, int rank, int world, long long offset_bytes,
-                           long long staging_bytes_off, long long n_vec_per_slice) {
-  const uint32_t e = begin_epoch(st);
-  const long long slice_bytes = n_vec_per_slice * 16;
-  const uint8_t* mine = pp.data[rank] + offset_bytes;
-  // push: my values of slice d go to slot `rank` of rank d's staging area
-  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec_per_slice;
-       v += (long long)gridDim.x * blockDim.x) {
-#pragma unroll
-    for (int d = 0; d < kPeerMaxWorld; ++d) {
-      if (d < world && d != rank) {
-        const uint4 x = *reinterpret_cast<const uint4*>(mine + (long long)d * slice_bytes + v * 16);
-        *reinterpret_cast<uint4*>(pp.data[d] + staging_bytes_off + (long long)rank * slice_bytes + v * 16) = x;
-      }
-    }
-  }
-  raise_flags(pp, rank, world, 0, e);
-  await_flags(pp, rank, world, 0, e, st.status, st.max_polls);
-  // reduce slice `rank` in rank order and push the result
-  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec_per_slice;
-       v += (long long)gridDim.x * blockDim.x) {
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-#pragma unroll
-    for (int p = 0; p < kPeerMaxWorld; ++p) {
-      if (p < world) {
-        const uint4 in = p == rank ? *reinterpret_cast<const uint4*>(mine + (long long)rank * slice_bytes + v * 16)
-                                   : __ldcg(reinterpret_cast<const uint4*>(pp.data[rank] + staging_bytes_off +
-                                                                           (long long)p * slice_bytes + v * 16));
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&in);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __bfloat1622float2(h[i]);
-          acc[2 * i] += f.x;
-          acc[2 * i + 1] += f.y;
-        }
-      }
-    }
-    uint4 out;
-    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-#pragma unroll
-    for (int p = 0; p < kPeerMaxWorld; ++p)
-      if (p < world) *reinterpret_cast<uint4*>(pp.data[p] + offset_bytes + (long long)rank * slice_bytes + v * 16) = out;
-  }
-  raise_flags(pp, rank, world, 1, e);
-  await_flags(pp, rank, world, 1, e, st.status, st.max_polls);
-  end_epoch(st, e);
-}
-
-// Push variant of peer_allreduce_add_rmsnorm_kernel: same thread layout and arithmetic, bit-identical results.
-__global__ void __launch_bounds__(256)
-peer_allreduce_push_add_rmsnorm_kernel(const PeerPointers pp, const PeerState st, int rank, int world,
-                                       long long part_off, long long x_off, long long h_off,
-                                       long long staging_bytes_off, int rows_per_rank, int cols,
-                                       const __nv_bfloat16* __restrict__ w, float eps) {
-  __shared__ float red[8];
-  const uint32_t e = begin_epoch(st);
-  const int nchunk = cols >> 3;
-  const long long slice_bytes = (long long)rows_per_rank * cols * 2;
-  const uint8_t* mine = pp.data[rank] + part_off;
-  for (int r = blockIdx.x; r < rows_per_rank; r += gridDim.x) {
-    const long long in_slice = (long long)r * cols * 2;
-    for (int c = threadIdx.x; c < nchunk; c += blockDim.x) {
-#pragma unroll
-      for (int d = 0; d < kPeerMaxWorld; ++d) {
-        if (d < world && d != rank) {
-          const uint4 x = *reinterpret_cast<const uint4*>(mine + (long long)d * slice_bytes + in_slice + (long long)c * 16);
-          *reinterpret_cast<uint4*>(pp.data[d] + staging_bytes_off + (long long)rank * slice_bytes + in_slice +
-                                    (long long)c * 16) = x;
-        }
-      }
-    }
-  }
-  raise_flags(pp, rank, world, 0, e);
-  await_flags(pp, rank, world, 0, e, st.status, st.max_polls);
-  for (int r = blockIdx.x; r < rows_per_rank; r += gridDim.x) {
-    const long long in_slice = (long long)r * cols * 2;
-    const long long row_bytes = (long long)rank * slice_bytes + in_slice;
-    uint4 keep[8];
-    float ss = 0.f;
-    int n = 0;
-    for (int c = threadIdx.x; c < nchunk; c += blockDim.x, ++n) {
-      const long long off = row_bytes + (long long)c * 16;
-      float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      uint4 xv = __ldcg(reinterpret_cast<const uint4*>(pp.data[rank] + x_off + off));
-#pragma unroll
-      for (int p = 0; p < kPeerMaxWorld; ++p) {
-        if (p < world) {
-          const uint4 in = p == rank ? *reinterpret_cast<const uint4*>(mine + off)
-                                     : __ldcg(reinterpret_cast<const uint4*>(pp.data[rank] + staging_bytes_off +
-                                                                             (long long)p * slice_bytes + in_slice +
-                                                                             (long long)c * 16));
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&in);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(h2[i]);
-            acc[2 * i] += f.x;
-            acc[2 * i + 1] += f.y;
-          }
-        }
-      }
-      __nv_bfloat16* xh = reinterpret_cast<__nv_bfloat16*>(&xv);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float d = __bfloat162float(__float2bfloat16(acc[i]));
-        xh[i] = __float2bfloat16(__bfloat162float(xh[i]) + d);
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float f = __bfloat162float(xh[i]);
-        ss += f * f;
-      }
-      keep[n] = xv;
-#pragma unroll
-      for (int p = 0; p < kPeerMaxWorld; ++p)
-        if (p < world) *reinterpret_cast<uint4*>(pp.data[p] + x_off + off) = xv;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.f;
-    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
-    const float inv = rsqrtf(tot / (float)cols + eps);
-    n = 0;
-    for (int c = threadIdx.x; c < nchunk; c += blockDim.x, ++n) {
-      const long long off = row_bytes + (long long)c * 16;
-      const uint4 wv = *reinterpret_cast<const uint4*>(w + (long long)c * 8);
-      const __nv_bfloat16* wh = reinterpret_cast<const __nv_bfloat16*>(&wv);
-      const __nv_bfloat16* xh = reinterpret_cast<const __nv_bfloat16*>(&keep[n]);
-      uint4 ov;
-      __nv_bfloat16* oh = reinterpret_cast<__nv_bfloat16*>(&ov);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const __nv_bfloat16 nb = __float2bfloat16(__bfloat162float(xh[i]) * inv);
-        oh[i] = __float2bfloat16(__bfloat162float(wh[i]) * __bfloat162float(nb));
-      }
-#pragma unroll
-      for (int p = 0; p < kPeerMaxWorld; ++p)
-        if (p < world) *reinterpret_cast<uint4*>(pp.data[p] + h_off + off) = ov;
-    }
-  }
-  raise_flags(pp, rank, world, 1, e);
-  await_flags(pp, rank, world, 1, e, st.status, st.max_polls);
-  end_epoch(st, e);
-}
-
 __global__ void __launch_bounds__(256)
 peer_allgather_kernel(const PeerPointers pp, const PeerState st, int rank, int world, const uint8_t* src,
                       long long offset_bytes, long long chunk_bytes) {
@@ -437,30 +250,6 @@ cudaError_t launch_peer_allreduce_add_rmsnorm(const PeerPointers& pp, const Peer
   peer_allreduce_add_rmsnorm_kernel<<<ctas, 256, 0, stream>>>(pp, st, rank, world, part_off, x_off, h_off,
                                                               rows_per_rank, cols,
                                                               static_cast<const __nv_bfloat16*>(w), eps);
-  return cudaGetLastError();
-}
-
-cudaError_t launch_peer_allreduce_push_bf16(const PeerPointers& pp, const PeerState& st, int rank, int world,
-                                            long long offset_bytes, long long staging_offset_bytes, long long n_elems,
-                                            int ctas, cudaStream_t stream) {
-  const long long n_vec_per_slice = n_elems / 8 / world;
-  if (ctas < 1) ctas = 1;
-  if (ctas > kPeerMaxCtas) ctas = kPeerMaxCtas;
-  peer_allreduce_push_kernel<<<ctas, 512, 0, stream>>>(pp, st, rank, world, offset_bytes, staging_offset_bytes,
-                                                       n_vec_per_slice);
-  return cudaGetLastError();
-}
-
-cudaError_t launch_peer_allreduce_push_add_rmsnorm(const PeerPointers& pp, const PeerState& st, int rank, int world,
-                                                   long long part_off, long long x_off, long long h_off,
-                                                   long long staging_offset_bytes, int rows, int cols, const void* w,
-                                                   float eps, cudaStream_t stream) {
-  const int rows_per_rank = rows / world;
-  int ctas = rows_per_rank < kPeerMaxCtas ? rows_per_rank : kPeerMaxCtas;
-  if (ctas < 1) ctas = 1;
-  peer_allreduce_push_add_rmsnorm_kernel<<<ctas, 256, 0, stream>>>(pp, st, rank, world, part_off, x_off, h_off,
-                                                                   staging_offset_bytes, rows_per_rank, cols,
-                                                                   static_cast<const __nv_bfloat16*>(w), eps);
   return cudaGetLastError();
 }
 

@@ -33,17 +33,6 @@ cudaError_t launch_peer_allreduce_add_rmsnorm(const PeerPointers& pp, const Peer
                                               long long part_off, long long x_off, long long h_off, int rows, int cols,
                                               const void* w, float eps, cudaStream_t stream);
 
-// Push variants of the two all-reduces (same results, fewer NVLink latencies in a row): they need a staging
-// area of the message's size (n_elems * 2, or rows * cols * 2 bytes) at staging_offset_bytes of every rank's
-// buffer, apart from the regions of the call.
-cudaError_t launch_peer_allreduce_push_bf16(const PeerPointers& pp, const PeerState& st, int rank, int world,
-                                            long long offset_bytes, long long staging_offset_bytes, long long n_elems,
-                                            int ctas, cudaStream_t stream);
-cudaError_t launch_peer_allreduce_push_add_rmsnorm(const PeerPointers& pp, const PeerState& st, int rank, int world,
-                                                   long long part_off, long long x_off, long long h_off,
-                                                   long long staging_offset_bytes, int rows, int cols, const void* w,
-                                                   float eps, cudaStream_t stream);
-
 // Rank r's `chunk_bytes` at `src` (local memory) end up at offset_bytes + r * chunk_bytes of every
 // rank's data buffer.  chunk_bytes must be a multiple of 4.
 cudaError_t launch_peer_allgather(const PeerPointers& pp, const PeerState& st, int rank, int world, const void* src,

@@ -422,20 +422,6 @@ int fa_peer_allreduce_add_rmsnorm_bf16(void* const* data_ptrs, void* const* flag
                                        int rank, int world, int64_t part_offset_bytes,
                                        int64_t x_offset_bytes, int64_t h_offset_bytes, int64_t rows,
                                        int cols, const void* weight, float eps, void* stream);
-/* Push variants of the two all-reduces: the same results bit for bit with fewer NVLink latencies in a row
- * (every rank stores the part of its input that another rank reduces into a staging area of that rank and
- * raises a flag behind it; the reducer stores its results to all ranks and raises a second flag).  They
- * need a staging area of the message's size (n_elems * 2, or rows * cols * 2 bytes) at
- * staging_offset_bytes of every rank's data buffer, apart from the regions of the call; its contents are
- * scratch. */
-int fa_peer_allreduce_push_sum_bf16(void* const* data_ptrs, void* const* flag_ptrs, void* state,
-                                    int rank, int world, int64_t offset_bytes, int64_t n_elems,
-                                    int64_t staging_offset_bytes, void* stream);
-int fa_peer_allreduce_push_add_rmsnorm_bf16(void* const* data_ptrs, void* const* flag_ptrs, void* state,
-                                            int rank, int world, int64_t part_offset_bytes,
-                                            int64_t x_offset_bytes, int64_t h_offset_bytes, int64_t rows,
-                                            int cols, const void* weight, float eps,
-                                            int64_t staging_offset_bytes, void* stream);
 int fa_peer_allgather(void* const* data_ptrs, void* const* flag_ptrs, void* state,
                       int rank, int world, const void* src, int64_t offset_bytes,
                       int64_t chunk_bytes, void* stream);

@@ -30,25 +30,20 @@ def main():
         return acc.bfloat16()
 
     # ---- all-reduce: several sizes, exact against the fp32 rank-order sum, identical on all ranks ----
-    # (both kernels: the push variant with its staging area, and the barrier + remote-load one)
-    for push in (True, False):
-        pc.push = push
-        for rows, cols in [(1, 8 * world), (256, 4096), (3, 64 * world), (512, 4096)]:
-            x = torch.randn(rows, cols, generator=g, device=dev).bfloat16()
-            want = expected_sum(x)
-            v = pc.view(0, (rows, cols), torch.bfloat16)
-            v.copy_(x)
-            pc.all_reduce_(v)
-            torch.cuda.synchronize()
-            same = torch.equal(v, want)
-            allr = [torch.empty_like(v) for _ in range(world)]
-            dist.all_gather(allr, v.clone())
-            ident = all(torch.equal(allr[0], a) for a in allr)
-            ok &= same and ident
-            if rank == 0:
-                print(f"all-reduce ({'push' if push else 'pull'}) {rows}x{cols}: exact {same}, identical across ranks {ident}",
-                      flush=True)
-    pc.push = True
+    for rows, cols in [(1, 8 * world), (256, 4096), (3, 64 * world), (512, 4096)]:
+        x = torch.randn(rows, cols, generator=g, device=dev).bfloat16()
+        want = expected_sum(x)
+        v = pc.view(0, (rows, cols), torch.bfloat16)
+        v.copy_(x)
+        pc.all_reduce_(v)
+        torch.cuda.synchronize()
+        same = torch.equal(v, want)
+        allr = [torch.empty_like(v) for _ in range(world)]
+        dist.all_gather(allr, v.clone())
+        ident = all(torch.equal(allr[0], a) for a in allr)
+        ok &= same and ident
+        if rank == 0:
+            print(f"all-reduce {rows}x{cols}: exact {same}, identical across ranks {ident}", flush=True)
 
     # ---- all-reduce + residual add + RMS norm in one kernel: bit-identical to the separate kernels ----
     lib = _lib.load()
@@ -71,21 +66,17 @@ def main():
                                            1e-6, torch.cuda.current_stream(dev).cuda_stream))
         torch.cuda.synchronize()
         dist.barrier()
-        # one kernel (push and pull variants)
-        for push in (True, False):
-            pc.push = push
-            part.copy_(p0)
-            xr.copy_(x0)
-            hr.zero_()
-            pc.all_reduce_add_rmsnorm_(part, xr, hr, wn, 1e-6)
-            torch.cuda.synchronize()
-            okf = torch.equal(xr, x_ref) and torch.equal(hr, h_ref) and torch.equal(part, p0)
-            ok &= okf
-            if rank == 0:
-                print(f"all-reduce + add + rmsnorm ({'push' if push else 'pull'}) {rows}x{cols}: bit-identical to the "
-                      f"separate kernels {okf}", flush=True)
-            dist.barrier()
-        pc.push = True
+        # one kernel
+        part.copy_(p0)
+        xr.copy_(x0)
+        hr.zero_()
+        pc.all_reduce_add_rmsnorm_(part, xr, hr, wn, 1e-6)
+        torch.cuda.synchronize()
+        okf = torch.equal(xr, x_ref) and torch.equal(hr, h_ref) and torch.equal(part, p0)
+        ok &= okf
+        if rank == 0:
+            print(f"all-reduce + add + rmsnorm {rows}x{cols}: bit-identical to the separate kernels {okf}", flush=True)
+        dist.barrier()
 
     # ---- all-gather ----
     src = torch.randn(64, 2, generator=g, device=dev)
