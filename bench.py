@@ -428,7 +428,29 @@ class HeadShardedPagedDecode:
         return fa.forward_paged_decode_gqa_fp16(self.q, k, v, self.bt, self.sl, self.max_blocks)
 
 
-WORKLOADS = {w.name: w for w in (PagedDecode, ContigDecode, Int8Decode, Int8KVDecode, SlidingWindowDecode, VarlenPrefill)}
+class PagedDecodeBF16(PagedDecode):
+    """The headline workload through the bfloat16 twin of the operator (the same bytes, bfloat16 q / pages / out)."""
+    name = "paged_decode_bf16"
+    dtype = "bf16"
+
+    def __init__(self, device, seed):
+        super().__init__(device, seed)
+        self.k_cache = self.k_cache.bfloat16()
+        self.v_cache = self.v_cache.bfloat16()
+        self.q = self.q.bfloat16()
+        self.step_e2e = None
+
+    def step(self, fa):
+        return fa.forward_paged_decode_gqa_bf16(self.q, self.k_cache, self.v_cache, self.bt, self.sl, self.max_blocks)
+
+    def config(self):
+        c = super().config()
+        c["workload"] = c["workload"].replace("paged_gqa_decode", "paged_gqa_decode (bfloat16 twin)")
+        return c
+
+
+WORKLOADS = {w.name: w for w in (PagedDecode, PagedDecodeBF16, ContigDecode, Int8Decode, Int8KVDecode,
+                                 SlidingWindowDecode, VarlenPrefill)}
 
 
 def run_engine(args):
