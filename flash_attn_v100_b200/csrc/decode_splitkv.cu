@@ -383,15 +383,59 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
     b = lo;
   }
 
+  // A piece: the pages [p0, p0 + cnt) of one (sequence, KV-head block) unit, the part of this CTA's range
+  // [u, u1) that lies in that unit.
+  struct Piece {
+    int b, np, hv, p0, cnt;
+  };
+  auto locate = [&](long long uu, int bb) -> Piece {
+    Piece q;
+    while ((long long)p.HV * pre[bb + 1] <= uu) ++bb;  // also skips empty sequences
+    q.b = bb;
+    q.np = pre[bb + 1] - pre[bb];
+    const long long rel = uu - (long long)p.HV * pre[bb];
+    q.hv = (int)(rel / q.np);
+    q.p0 = (int)(rel - (long long)q.hv * q.np);
+    const long long left = u1 - uu;
+    q.cnt = (q.np - q.p0) < left ? (q.np - q.p0) : (int)left;
+    return q;
+  };
+  // One page copy (K and V rows of unit page `upage`) into the next ring stage of this warp; lane 0 issues.
+  auto issue_page = [&](int upage, int pid, int h_kv_, long long contig_row0_) {
+    if (lane == 0) {
+      const int page = upage < p.sink_pages ? upage : p.win_first_page + (upage - p.sink_pages);
+      long long row;
+      if (p.mode == kModePaged) {
+        if (pid < 0 || (long long)pid >= p.num_pages) {
+          atomicOr(p.status, kStatusBadPageId);
+          pid = 0;
+        }
+        row = ((long long)pid * p.H_KV + h_kv_) * 16;
+      } else {
+        row = contig_row0_ + (long long)page * 16;
+      }
+      const uint32_t st = st_issue;
+      const uint32_t bar = bar0 + st * 8;
+      const uint32_t dst = stage0 + st * (2 * PAGE_BYTES);
+      mbar_expect_tx(bar, 2 * PAGE_BYTES);
+#pragma unroll
+      for (int sl = 0; sl < NSLAB; ++sl) {
+        tma_load_2d(dst + sl * SLAB_BYTES, &kmap, sl * SLAB_COLS, (int)row, bar, policy);
+        tma_load_2d(dst + PAGE_BYTES + sl * SLAB_BYTES, &vmap, sl * SLAB_COLS, (int)row, bar, policy);
+      }
+    }
+    st_issue = (st_issue + 1 == (uint32_t)S) ? 0u : st_issue + 1;
+  };
+  // Pages of the NEXT piece that this warp has already put in flight while it finished the current one
+  // (the ring never runs empty across a piece boundary: the copies of the next piece's first pages overlap
+  // the merge of this one).
+  int pre_issued = 0;
+
   int piece = 0;
   while (u < u1) {
-    while ((long long)p.HV * pre[b + 1] <= u) ++b;  // also skips empty sequences
-    const int np = pre[b + 1] - pre[b];
-    const long long rel = u - (long long)p.HV * pre[b];
-    const int hv = (int)(rel / np);
-    const int p0 = (int)(rel - (long long)hv * np);
-    const long long left = u1 - u;
-    const int cnt = (np - p0) < left ? (np - p0) : (int)left;
+    const Piece pc = locate(u, b);
+    b = pc.b;
+    const int np = pc.np, hv = pc.hv, p0 = pc.p0, cnt = pc.cnt;
     const bool complete = (p0 == 0) && (cnt == np);
     const int len = seq_len_of(p, b);
     const int h_kv = hv / p.n_gblk;
@@ -497,34 +541,27 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
 
     auto issue = [&](int n) {
       // every lane takes part in the shuffle; lane 0 issues the copies
-      int pid = __shfl_sync(0xffffffffu, tbl_cur, n & 31);
-      if (lane == 0) {
-        const int upage = p0 + warp + n * W;
-        const int page = upage < p.sink_pages ? upage : p.win_first_page + (upage - p.sink_pages);
-        long long row;
-        if (p.mode == kModePaged) {
-          if (pid < 0 || (long long)pid >= p.num_pages) {
-            atomicOr(p.status, kStatusBadPageId);
-            pid = 0;
-          }
-          row = ((long long)pid * p.H_KV + h_kv) * 16;
-        } else {
-          row = contig_row0 + (long long)page * 16;
-        }
-        const uint32_t st = st_issue;
-        const uint32_t bar = bar0 + st * 8;
-        const uint32_t dst = stage0 + st * (2 * PAGE_BYTES);
-        mbar_expect_tx(bar, 2 * PAGE_BYTES);
-#pragma unroll
-        for (int sl = 0; sl < NSLAB; ++sl) {
-          tma_load_2d(dst + sl * SLAB_BYTES, &kmap, sl * SLAB_COLS, (int)row, bar, policy);
-          tma_load_2d(dst + PAGE_BYTES + sl * SLAB_BYTES, &vmap, sl * SLAB_COLS, (int)row, bar, policy);
-        }
-      }
-      st_issue = (st_issue + 1 == (uint32_t)S) ? 0u : st_issue + 1;
+      const int pid = __shfl_sync(0xffffffffu, tbl_cur, n & 31);
+      issue_page(p0 + warp + n * W, pid, h_kv, contig_row0);
     };
 
-    int issued = 0;
+    // The piece after this one (if this CTA has one): where it lies, this warp's share of it and the
+    // block-table entries of its first pages, fetched now so that they are at hand when the ring has room.
+    const bool has_next = u + cnt < u1;
+    Piece nx = pc;
+    int nx_n_my = 0, nx_tbl = 0, nx_h_kv = 0;
+    long long nx_row0 = 0;
+    if (has_next) {
+      nx = locate(u + cnt, b);
+      nx_n_my = nx.cnt > warp ? (nx.cnt - warp + W - 1) / W : 0;
+      nx_h_kv = nx.hv / p.n_gblk;
+      nx_row0 = ((long long)nx.b * p.H_KV + nx_h_kv) * (long long)p.N;
+      if (p.mode == kModePaged && lane < nx_n_my && lane < S)
+        nx_tbl = __ldg(p.block_table + (size_t)nx.b * p.bt_stride + nx.p0 + warp + lane * W);
+    }
+
+    int issued = pre_issued;   // pages of this piece that were put in flight during the previous one
+    pre_issued = 0;
     for (; issued < S && issued < n_my; ++issued) issue(issued);
 
     // bit t of the result: token page*16 + t is attended (inside the length, and in the sink or the window)
@@ -878,6 +915,11 @@ decode_splitkv_kernel(const __grid_constant__ CUtensorMap kmap,
         }
         issue(issued);
         ++issued;
+      } else if (pre_issued < nx_n_my && pre_issued < S) {
+        // nothing left to fetch for this piece: the freed stage takes a page of the next piece
+        const int pid = __shfl_sync(0xffffffffu, nx_tbl, pre_issued);
+        issue_page(nx.p0 + warp + pre_issued * W, pid, nx_h_kv, nx_row0);
+        ++pre_issued;
       }
     }
 
