@@ -427,6 +427,22 @@ class HeadShardedPagedDecode:
         self.turn += 1
         return fa.forward_paged_decode_gqa_fp16(self.q, k, v, self.bt, self.sl, self.max_blocks)
 
+    def graph_of_one_rotation(self, fa, device):
+        """One launch per pool, captured into a CUDA graph (how a serving loop replays its decode step): at 8 ranks
+        a launch is short enough for the eager call's host time to show in `step`."""
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(len(self.pools)):
+                self.step(fa)
+            self.turn = 0
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                for _ in range(len(self.pools)):
+                    self.step(fa)
+        torch.cuda.current_stream(device).wait_stream(side)
+        return graph, len(self.pools)
+
 
 class PagedDecodeBF16(PagedDecode):
     """The headline workload through the bfloat16 twin of the operator (the same bytes, bfloat16 q / pages / out)."""
@@ -748,6 +764,17 @@ def run_b200(args):
                        one_gpu_ms_per_step=t1_ms)
             rec["roofline"] = roofline_of(hs, ms, peaks, peak_src)
             rec["roofline"]["traffic"] = None
+            # the same launches replayed from a CUDA graph (one rotation over the pools per replay)
+            graph, per_replay = hs.graph_of_one_rotation(fa, device)
+            for _ in range(3):
+                graph.replay()
+            mg = measure(graph.replay, max(args.steps // per_replay, 1), world, device, min_seconds=MIN_SECONDS / 2)
+            ms_g = mg["ms_block"] / max(args.steps // per_replay, 1) / per_replay
+            flash_attn_v100_b200.check_async_errors()
+            rec.update(us_per_rank_step_graph_replay=ms_g * 1e3,
+                       hbm_gbs_per_gpu_graph_replay=hs.alg_bytes / (ms_g * 1e-3) / 1e9,
+                       strong_scaling_efficiency_graph_replay_vs_one_gpu=t1_ms / (world * ms_g))
+            del graph
             extra["head_sharded"] = rec
             del hs
             torch.cuda.empty_cache()
