@@ -374,6 +374,24 @@ class VarlenPrefill:
     step_e2e = None
 
 
+class VarlenPrefillBF16(VarlenPrefill):
+    """configs[2] through the bfloat16 twin of the operator."""
+    name = "varlen_prefill_bf16"
+    dtype = "bf16"
+
+    def __init__(self, device, seed):
+        super().__init__(device, seed)
+        self.q, self.k, self.v = self.q.bfloat16(), self.k.bfloat16(), self.v.bfloat16()
+
+    def config(self):
+        c = super().config()
+        c["workload"] = c["workload"].replace("varlen_causal_gqa_prefill", "varlen_causal_gqa_prefill (bfloat16 twin)")
+        return c
+
+    def step(self, fa):
+        return fa.forward_varlen_prefill_bf16(self.q, self.k, self.v, self.cu, max(self.lens), True)
+
+
 class HeadShardedPagedDecode:
     """ONE paged-decode batch of the headline shape split over the ranks by KV-head group (the reference's
     multi-GPU partition, tensor_parallel.py:435-457 and :553-571): rank r holds KV heads
@@ -466,7 +484,7 @@ class PagedDecodeBF16(PagedDecode):
 
 
 WORKLOADS = {w.name: w for w in (PagedDecode, PagedDecodeBF16, ContigDecode, Int8Decode, Int8KVDecode,
-                                 SlidingWindowDecode, VarlenPrefill)}
+                                 SlidingWindowDecode, VarlenPrefill, VarlenPrefillBF16)}
 
 
 def run_engine(args):
